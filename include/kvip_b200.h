@@ -1,0 +1,337 @@
+/* C ABI of libkvip_b200.so: the DeepSeek-sparse-attention selection-and-fetch path
+ * (lightning-indexer score -> TopK-2048 -> slot resolver -> KV fetch -> Index update)
+ * as hand-written CUDA for sm_100a.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; no torch types;
+ *   - every pointer inside an argument struct is a DEVICE pointer unless the field
+ *     comment says "host";
+ *   - `stream` is a cudaStream_t passed as void*; work is only enqueued, nothing
+ *     synchronises, allocates or copies to the host;
+ *   - return value 0 = enqueued, 100000 = bad argument (the reference's launch
+ *     convention, csrc/operators/lightning_indexer_with_fetch/op_host/launch.cpp:77-78),
+ *     any other value = 200000 + cudaError_t of the failed launch;
+ *   - device-side failures are reported through int32 status words, never by a trap.
+ *
+ * Citations name files of the reference project (zxdgongjue-spec/KVIP) by their
+ * path inside that project.
+ */
+#ifndef KVIP_B200_H_
+#define KVIP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVIP_TOPK 2048u              /* context.h:6 kTop */
+#define KVIP_MAX_QUERIES 4u          /* adapters/vllm/inputs.py:11 */
+#define KVIP_SLOTS 8192u             /* context.h:6 kSlots = 4 * 2048 */
+#define KVIP_LRU_SLOTS 2048u         /* common/lifetch/cache_metadata.h:2 */
+#define KVIP_CHANGE_CAPACITY 10240u  /* common/lifetch/cache_metadata.h:3 */
+#define KVIP_BLOCK_TOKENS 128u       /* paged Index cache block */
+#define KVIP_INDEX_WIDTH 128u        /* d_I */
+#define KVIP_BAD_ARGUMENT 100000u
+#define KVIP_CUDA_ERROR_BASE 200000u
+
+/* device status bits (row_status / update.status words) */
+#define KVIP_ERR_TOKEN_RANGE 1u      /* selected position >= history (resolver_staged_dma2.h:63) */
+#define KVIP_ERR_NO_SLOT 4u          /* victims exhausted / bad candidate (resolver_staged_dma2.h:150,185) */
+#define KVIP_ERR_HASH 8u             /* hash probe overflow, also the wait-limit code (streaming.cpp:191) */
+#define KVIP_ERR_EXCHANGE 16u        /* Index exchange plan invalid (shadow_exchange_parallel.h:40) */
+#define KVIP_ERR_PIPELINE 32u        /* a bounded mbarrier wait inside the LI kernel gave up */
+
+enum { KVIP_KEY_FP8_E4M3 = 0, KVIP_KEY_BF16 = 1 };
+enum { KVIP_WEIGHT_BF16 = 0, KVIP_WEIGHT_FP32 = 1 };
+enum { KVIP_SCORE_FP32 = 0, KVIP_SCORE_BF16_AWAY = 1 };
+
+/* Geometry bound before graph capture. Same size (80 bytes, 20 x u32) and the same
+ * leading fields as rotating::RuntimeShape (include/runtime_shape.h:5-27); the fields
+ * that described Ascend core scheduling carry the CUDA tiling instead. */
+typedef struct KvipRuntimeShape {
+  uint32_t batch;          /* requests per launch (reference limit 16 lifted) */
+  uint32_t history;        /* Index positions per owner, multiple of 128 */
+  uint32_t resident;       /* hot KV slots per owner, multiple of 128, >= 2048 */
+  uint32_t indexHeads;     /* 32 or 64 */
+  uint32_t smCount;        /* persistent CTAs for the LI kernel (0 = query the device) */
+  uint32_t queries;        /* query slots per request, 1..4 */
+  uint32_t keyDtype;       /* KVIP_KEY_* */
+  uint32_t weightDtype;    /* KVIP_WEIGHT_* */
+  uint32_t scoreMode;      /* KVIP_SCORE_* */
+  uint32_t pagesPerRequest;/* derived: history / 128 */
+  uint32_t finalWorkers;   /* kept for ABI parity, always 4 */
+  uint32_t scoreStride;    /* derived: floats per score row (= history) */
+  uint32_t outputStride;   /* KV slots per owner in the resident pool (0 -> resident) */
+  uint32_t owners;         /* stable owners in the Index storage (0 -> batch) */
+  uint32_t tokenBytes;     /* bytes per KV row, multiple of 16 (same index as the reference) */
+  uint32_t keyRows;        /* rows of the paged key tensor = owners * history */
+  uint32_t gatherRows;     /* 1 = also write the dense [T,2048,tokenBytes] gather */
+  uint32_t liVariant;      /* 0 = tcgen05 kernel, 1 = CUDA-core cross-check kernel */
+  uint32_t reserved0;
+  uint32_t reserved1;
+} KvipRuntimeShape;
+
+/* ---- stage 1: lightning-indexer score ------------------------------------------
+ * score[t,s] = kscale[s] * sum_h W[t,h] * relu(q[t,h,:] . k[s,:]),
+ * W = float(w) * qscale (bf16 weights) or W = w (fp32 weights).
+ * Replaces QLIMatmul::ComputeMm1 + the score epilogue
+ * (op_kernel/indexer/indexer_cube.h:161-322, indexer_score.h:59-140,384-426). */
+typedef struct KvipLiArgs {
+  const void* query;          /* [batch*queries, heads, 128] fp8 e4m3 or bf16 */
+  const void* keys;           /* [keyRows, 128] paged, 128-token blocks */
+  const void* weights;        /* [batch*queries, heads] bf16 or fp32 */
+  const float* query_scale;   /* [batch*queries, heads] or NULL (= 1) */
+  const float* key_scale;     /* [keyRows] or NULL (= 1) */
+  const int32_t* key_lengths; /* [batch] */
+  const int32_t* query_ends;  /* [batch, queries] exclusive causal bound, 0 = padding row */
+  const int32_t* block_table; /* [batch, pagesPerRequest] page -> 128-row block of keys */
+  float* scores;              /* [batch*queries, scoreStride] */
+  int32_t* status;            /* [1] OR-ed KVIP_ERR_* */
+  uint32_t batch, queries, heads, pagesPerRequest;
+  uint32_t keyRows, scoreStride, keyDtype, weightDtype;
+  uint32_t scoreMode, ctas, reserved0, reserved1;
+} KvipLiArgs;
+uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
+/* CUDA-core restatement of the same formula with the oracle's accumulation order;
+ * an on-GPU cross-check for small shapes, not the product path. */
+uint32_t kvip_b200_li_score_simt(const KvipLiArgs* args, void* stream);
+
+/* ---- stage 2: per-query TopK-2048 -----------------------------------------------
+ * Valid length L = min(key_length[b], query_end[t]); L<=0 -> 2048 x -1; L<2048 ->
+ * 0..L-1 then -1; otherwise every position with key > v (v = 2048th largest) in
+ * ascending position, then positions with key == v in ascending position, cut at 2048.
+ * Replaces LITopk / LiTopKVF (op_kernel/indexer/topk.h:155-187,
+ * topk_common.h:1136-1187; bounds indexer_vector.h:826-957). */
+typedef struct KvipTopkArgs {
+  const float* scores;        /* [rows, scoreStride] */
+  const int32_t* key_lengths; /* [batch] */
+  const int32_t* query_ends;  /* [batch*queries] */
+  int32_t* topk;              /* [rows, 2048] */
+  float* topk_scores;         /* [rows, 2048] or NULL: score of each output */
+  uint32_t rows, queries, scoreStride, base_index; /* base_index added to every output index */
+} KvipTopkArgs;
+uint32_t kvip_b200_topk(const KvipTopkArgs* args, void* stream);
+
+/* Merge of sequence-sharded candidates: rows x shards x 2048 (score,index) pairs ->
+ * global top-2048 under the same total order. New on B200 (no reference counterpart;
+ * precedent: the on-chip sequence split, common/lifetch/sequence_schedule.h:9-37). */
+typedef struct KvipMergeArgs {
+  const float* cand_scores;   /* [rows, shards*2048] */
+  const int32_t* cand_index;  /* [rows, shards*2048], -1 = empty */
+  int32_t* topk;              /* [rows, 2048] */
+  uint32_t rows, shards;
+} KvipMergeArgs;
+uint32_t kvip_b200_topk_merge(const KvipMergeArgs* args, void* stream);
+
+/* ---- stage 3: classification + resolver + service outputs + fetch descriptors ---
+ * Replaces ClassifyTopkHalf / StagedInitializeReady / StagedQuery / PackStagedUrmaQuery /
+ * PublishQueryOutputs (op_kernel/staged_topk_classify.h:9-46,
+ * resolver_staged_dma2.h:83-237, staged_urma_pack.h:6-71, streaming.cpp:66-90). */
+typedef struct KvipResolveArgs {
+  const int32_t* topk;          /* [batch, queries, 2048] selected physical positions */
+  const int32_t* row_owners;    /* [batch] or NULL (owner = row) */
+  const int32_t* hot_valid;     /* [owners, resident] */
+  const int32_t* reserved_hot;  /* [batch, resident] candidate ordinal or -1 */
+  const int32_t* lru_slots;     /* [batch, 2048] victim candidates, oldest first */
+  const int32_t* tail_bounds;   /* [batch, 2] or NULL */
+  const int64_t* logical_ids;   /* [owners, history] (pre-update ids) */
+  const int64_t* addresses;     /* [owners, address_stride] source address of each position */
+  int32_t* locations;           /* [batch, queries, 2048] out */
+  int32_t* changes;             /* [batch, 10240] out: token per record, -1 = none */
+  int32_t* change_slots;        /* [batch, 10240] out */
+  int32_t* change_count;        /* [batch] out: 2048 + new slots */
+  int32_t* events_src;          /* [batch, 8192] out: position per new slot, rank order */
+  int32_t* events_dst;          /* [batch, 8192] out */
+  int32_t* query_counts;        /* [batch, 8]: [0..3] new slots per query, [4] total */
+  int64_t* fetch_sources;       /* [batch, 8192] out: address snapshot per new slot */
+  int32_t* fetch_destinations;  /* [batch, 8192] out: owner*outputStride + slot */
+  int32_t* logical_output;      /* [batch*queries, 2048] or NULL */
+  int32_t* slot_output;         /* [batch*queries, 2048] or NULL */
+  const int64_t* unpack_indices;/* [batch*queries] output row -> source query row, or NULL (identity) */
+  const int64_t* output_valid;  /* [batch*queries] 0 = padding output row (-1 fill), or NULL */
+  const int32_t* query_ends;    /* [batch*queries]; rows with 0 publish -1 when no routing is bound */
+  int32_t* row_status;          /* [batch, 32] */
+  uint32_t batch, queries, history, resident;
+  uint32_t address_stride, outputStride, reserved0, reserved1;
+} KvipResolveArgs;
+uint32_t kvip_b200_resolve(const KvipResolveArgs* args, void* stream);
+
+/* ---- stage 4: fetch ----------------------------------------------------------------
+ * output[dest*tokenBytes : +tokenBytes] = source_base[address : +tokenBytes] for every
+ * descriptor, then hot_valid[owner, slot] = 1. The source is the device alias of a
+ * pinned, mapped host pool (or any device-visible memory). Replaces FetchQueryGroup ->
+ * kvaf_device::KvafBatchGetDevice (streaming.cpp:365-500; arithmetic in
+ * patches/kvaf-ubmem-device-get.patch, fused_batch_get_device.h:21-61) and
+ * PublishQueryCompletion (streaming.cpp:300-328). */
+typedef struct KvipFetchArgs {
+  const uint8_t* source_base;      /* device-visible base the addresses are relative to */
+  const int64_t* fetch_sources;    /* [batch, 8192] byte offsets from source_base */
+  const int32_t* fetch_destinations;/* [batch, 8192] row index into pool */
+  const int32_t* query_counts;     /* [batch, 8], word 4 = descriptors of the request */
+  const int32_t* row_owners;       /* [batch] or NULL */
+  int32_t* row_status;             /* [batch, 32]; a failed request moves nothing; word 2 = fetch error */
+  uint8_t* pool;                   /* [owners*outputStride, tokenBytes] resident KV pool */
+  int32_t* hot_valid;              /* [owners, resident] */
+  uint64_t source_bytes;           /* size of the source window, for the bounds check */
+  uint32_t batch, resident, outputStride, tokenBytes;
+} KvipFetchArgs;
+uint32_t kvip_b200_fetch(const KvipFetchArgs* args, void* stream);
+
+/* Dense gather of the selected rows: out[t, k, :] = pool[owner*outputStride + slot[t,k], :],
+ * zero rows where slot < 0. (The north-star "fetch" output; the reference hands slot
+ * indices to its attention kernel instead, streaming.cpp:66-90.) */
+typedef struct KvipGatherArgs {
+  const uint8_t* pool;
+  const int32_t* slots;        /* [rows, 2048] */
+  const int32_t* row_owners;   /* [batch] or NULL */
+  uint8_t* out;                /* [rows, 2048, tokenBytes] */
+  uint32_t rows, queries, outputStride, tokenBytes;
+} KvipGatherArgs;
+uint32_t kvip_b200_gather(const KvipGatherArgs* args, void* stream);
+
+/* ---- stage 5: Index exchange (hot-slot permutation) -------------------------------
+ * Applies the (position, slot) events of one round so that physical position p < resident
+ * describes hot slot p. Replaces ApplyBatch/ApplyDenseBatch/Commit*Metadata
+ * (op_kernel/shadow_exchange_parallel.h:27-198; driver streaming.cpp:205-274). */
+typedef struct KvipExchangeArgs {
+  uint8_t* keys;               /* [owners, history, 128] (row bytes = 128 * key element size) */
+  float* scales;               /* [owners, history] */
+  int64_t* addresses;          /* [owners, address_stride] */
+  int64_t* logical_ids;        /* [owners, history] */
+  int32_t* hot_valid;          /* [owners, resident] */
+  const int32_t* events_src;   /* [batch, 8192] */
+  const int32_t* events_dst;   /* [batch, 8192] */
+  const int32_t* query_counts; /* [batch, 8] */
+  const int32_t* row_owners;   /* [batch] or NULL */
+  const int32_t* row_status;   /* [batch, 32] or NULL: word 0 != 0 -> the request failed upstream */
+  uint32_t* shadow;            /* [batch, 2*history] identity maps, restored on exit */
+  int32_t* status;             /* [batch] update status */
+  uint32_t batch, queries, history, resident;
+  uint32_t address_stride, key_row_bytes, reserved0, reserved1;
+} KvipExchangeArgs;
+uint32_t kvip_b200_exchange(const KvipExchangeArgs* args, void* stream);
+
+/* ---- paged Index-cache update (new tokens) -----------------------------------------
+ * keys[owner, query_end-1] = src[slot_mapping[gather[row]]], same for scales; invalid rows
+ * write row `row` of owner 0. With bf16 sources the row is quantised to FP8 e4m3 with a
+ * per-token scale amax/448. Replaces VllmIndexCacheStorage.ingest_decode
+ * (python/kvip/adapters/vllm/index_import.py:38-52). */
+typedef struct KvipIngestArgs {
+  const void* source_keys;       /* [source_rows, 128] u8 (fp8) or bf16 */
+  const float* source_scales;    /* [source_rows] or NULL when quantising */
+  const int64_t* slot_mapping;   /* [tokens] */
+  const int64_t* gather_indices; /* [batch*queries] */
+  const int32_t* query_ends;     /* [batch*queries] */
+  const int32_t* row_owners;     /* [batch] */
+  uint8_t* keys;                 /* [owners, history, 128] */
+  float* scales;                 /* [owners, history] */
+  uint32_t batch, queries, history, source_is_bf16;
+} KvipIngestArgs;
+uint32_t kvip_b200_ingest(const KvipIngestArgs* args, void* stream);
+
+/* ---- SlotLRU commit on the device -------------------------------------------------
+ * Same list semantics as _commit_lru_rows / _write_oldest_victims
+ * (python/kvip/cache/_lru_kernel.py:32-199): unique touched slots move to the tail in
+ * ascending slot order, then the first min(2048, active) nodes are listed as victims.
+ * The list is held as an array (`order`, oldest first) instead of next/previous links, so
+ * a commit is one parallel stream compaction per row; `reserved_hot` is rewritten as the
+ * inverse of the victim list. One CTA per row. */
+typedef struct KvipLruArgs {
+  int32_t* order;              /* [rows, capacity] slots, oldest first; in/out */
+  int32_t* slots;              /* [rows, 2048] victims; in (previous victims) / out */
+  int32_t* bitmap;             /* [rows, words] out: victim bitmap (also dedup scratch) */
+  int32_t* unique;             /* [rows] out: distinct touched slots */
+  int32_t* reserved_hot;       /* [rows, resident] in/out or NULL */
+  const int32_t* touched;      /* [rows, touched_stride] slots; <0 or >= active ignored */
+  const int32_t* active;       /* [rows] committed slots in the list */
+  uint32_t rows, capacity, words, touched_stride;
+  uint32_t resident, reserved0, reserved1, reserved2;
+} KvipLruArgs;
+uint32_t kvip_b200_lru_commit(const KvipLruArgs* args, void* stream);
+
+/* ---- ABC tail maps (python/kvip/cache/abc.py:5-33) ---------------------------------- */
+uint32_t kvip_b200_update_abc(int32_t* token_to_slot, int32_t* slot_to_token,
+                              const int32_t* descriptors, uint32_t groups, uint32_t rows_per_group,
+                              uint32_t requests, uint32_t pool, uint32_t tokens,
+                              uint32_t slots, uint32_t history, uint32_t tail, void* stream);
+
+/* ---- LIDU: the serial-chain slot resolver -------------------------------------------
+ * Same 24 arguments, in the same order, as
+ * nanovllm_dsa::lidu_fused_batch_get_prepare_mtp_out
+ * (csrc/operators/lidu/torch_extension/csrc/lidu_fused_batch_get_prepare_mtp_ops.cpp:195-270,
+ * 385-398), tensors replaced by pointers plus the sizes the checks need. */
+typedef struct KvipLiduArgs {
+  const int32_t* topk_indices;            /* [T,1,2048] */
+  const int32_t* actual_seq_lengths_query;/* [B] cumulative ends */
+  const int32_t* req_pool_entries;        /* [B] */
+  int32_t* token_to_slot_pool;            /* [pool, source_capacity] in/out */
+  int32_t* slot_to_token_pool;            /* [pool, resident_capacity] in/out */
+  int32_t* eviction_cursors;              /* [pool] in/out */
+  const int32_t* cache_tokens;            /* [B] resident budget per request */
+  const int32_t* candidate_lens;          /* [B] */
+  const int32_t* miss_slots;              /* [B,2048] */
+  const int32_t* miss_slot_bitmap;        /* [B,4176] */
+  const int32_t* resident_block_table;    /* [B, resident_blocks] */
+  const int32_t* logical_seq_lengths;     /* [B] */
+  const int32_t* profile_enabled;         /* [1] */
+  int32_t* destination_slots;             /* [T,1,2048] out */
+  int32_t* miss_counts;                   /* [B+1] out */
+  int32_t* indices;                       /* [B*8192] out */
+  int32_t* offsets;                       /* [B*8192] out */
+  int32_t* output_indices;                /* [B*8192] out */
+  int32_t* resident_seq_lengths;          /* [B] out */
+  int64_t* profiling;                     /* [B,8,32] out */
+  int64_t layer_id, num_layers, max_num_reqs, qcap;
+  uint32_t packed_queries, batch, pool_size, source_capacity;
+  uint32_t resident_capacity, resident_blocks, bitmap_words, reserved0;
+  int32_t* scratch;                       /* [B, 8192*3 + 64] device work area */
+} KvipLiduArgs;
+uint32_t kvip_b200_lidu(const KvipLiduArgs* args, void* stream);
+uint32_t kvip_b200_lidu_scratch_words(uint32_t batch);
+
+/* ---- the fused forward -------------------------------------------------------------
+ * Same call shape as the reference's
+ *   uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,
+ *                                           void* stream, const RuntimeShape* shape, uint32_t workers)
+ * (include/api.h:7; op_host/launch.cpp:76-83). `bindings` = 16 x u64 (the 14 operator
+ * arguments of python/kvip/operators/lifetch/workspace.py:105-123, then the context and the
+ * workspace blob), `update` = 28 x i64 (python/kvip/operators/lifetch/index_update.py:12-24),
+ * `workspace` = KvipWorkspace. The three blobs live in HOST memory (pinned or pageable): they
+ * are read on the host at enqueue time and their values become kernel parameters, so a CUDA
+ * graph captured around the call replays them without touching the blobs again.
+ * Enqueues: round init -> LI score -> TopK -> resolve -> fetch -> exchange (-> gather). */
+typedef struct KvipContext {          /* reference: rotating::Context, include/context.h:36-52 */
+  uint64_t locations, lru_slots, reserved_hot, changes, change_slots, change_count;
+  uint64_t query_ends, fetch_sources, fetch_destinations, hot_valid, row_owners;
+  uint64_t token_addresses, address_stride, output_stride, tail_bounds, row_status;
+  uint64_t query_counts, pool, source_base, source_bytes;
+  KvipRuntimeShape shape;
+} KvipContext;
+
+typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_types.h:17-22 */
+  uint64_t context, keys, scales, addresses, logical_ids, hot_valid;
+  uint64_t flags, events_src, events_dst, worker_status, times;
+  uint32_t history, resident, options, max_events;      /* options word at byte 96 */
+  uint64_t query_bitmaps, query_errors, update_bindings;
+  uint64_t dense_shadow, packed_fetch;
+  uint64_t gather_out, topk_scores, li_status;
+  uint8_t reserved[88];
+} KvipWorkspace;
+
+uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,
+                                        void* stream, const KvipRuntimeShape* shape,
+                                        uint32_t workers);
+uint32_t kvip_prepare_shape(KvipRuntimeShape* shape);    /* include/api.h:9 */
+uint32_t kvip_streaming_resolver_cores(void);            /* == 3, streaming.py:41-47 */
+uint32_t kvip_streaming_flag_count(void);                /* == 16 */
+uint32_t kvip_b200_abi_version(void);
+uint32_t kvip_b200_context_bytes(void);
+uint32_t kvip_b200_workspace_bytes(void);
+uint32_t kvip_b200_launch_count(void);                   /* kernels enqueued so far by this library */
+const char* kvip_b200_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVIP_B200_H_ */

@@ -1,0 +1,272 @@
+// Byte movers and cache-state kernels: miss fetch from the host-mapped pool, dense gather of
+// the selected KV rows, paged Index-cache ingest, SlotLRU commit and the ABC tail maps.
+#include <cuda_fp8.h>
+#include "common.cuh"
+
+namespace kvip {
+namespace {
+
+// ---- fetch -------------------------------------------------------------------------------
+// One warp per descriptor row, 16 bytes per lane per step: a 1152-byte row is 72 pieces, so a
+// warp issues three fully coalesced 512-byte requests (the last one 128 bytes). The source is
+// read through the device alias of pinned, mapped host memory; each request crosses the host
+// link once and lands in the resident HBM slot.
+constexpr uint32_t kFetchThreads = 256;
+constexpr uint32_t kFetchBlocksPerRequest = 16;
+
+__device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, uint32_t bytes, uint32_t lane) {
+  const uint32_t pieces = bytes >> 4;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  uint4 v[3];
+#pragma unroll
+  for (uint32_t k = 0; k < 3; ++k)
+    if (lane + 32u * k < pieces) v[k] = __ldcs(s + lane + 32u * k);
+#pragma unroll
+  for (uint32_t k = 0; k < 3; ++k)
+    if (lane + 32u * k < pieces) d[lane + 32u * k] = v[k];
+  for (uint32_t p = lane + 96u; p < pieces; p += 32u) d[p] = __ldcs(s + p);
+}
+
+__global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs a) {
+  const uint32_t b = blockIdx.y, lane = threadIdx.x & 31u;
+  if (a.row_status[b * 32u] != 0) return;
+  const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
+  const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+  const uint32_t warps = gridDim.x * (kFetchThreads / 32u);
+  for (uint32_t i = blockIdx.x * (kFetchThreads / 32u) + (threadIdx.x >> 5); i < count; i += warps) {
+    const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
+    const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
+    const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
+    const bool ok = source >= 0 && static_cast<uint64_t>(source) + a.tokenBytes <= a.source_bytes &&
+                    (source & 15) == 0 && dest >= 0 && slot < a.outputStride;
+    if (!ok) {  // record and skip the access (streaming.cpp:399-400 does the same range check)
+      if (lane == 0) atomicOr(a.row_status + b * 32u + 2, 1);
+      continue;
+    }
+    copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
+    if (lane == 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
+  }
+}
+
+// ---- dense gather --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gather_rows(const KvipGatherArgs a) {
+  const uint32_t row = blockIdx.y, lane = threadIdx.x & 31u;
+  const uint32_t k = blockIdx.x * 8u + (threadIdx.x >> 5);
+  const uint32_t b = row / a.queries;
+  const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+  const int32_t slot = a.slots[static_cast<uint64_t>(row) * kTop + k];
+  uint8_t* dst = a.out + (static_cast<uint64_t>(row) * kTop + k) * a.tokenBytes;
+  if (slot < 0 || static_cast<uint32_t>(slot) >= a.outputStride) {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    for (uint32_t p = lane; p < (a.tokenBytes >> 4); p += 32u) d[p] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint8_t* src = a.pool + (static_cast<uint64_t>(owner) * a.outputStride + static_cast<uint32_t>(slot)) * a.tokenBytes;
+  copy_row_warp(dst, src, a.tokenBytes, lane);
+}
+
+// ---- paged Index-cache ingest ----------------------------------------------------------------
+__global__ void __launch_bounds__(128) ingest_rows(const KvipIngestArgs a) {
+  const uint32_t row = blockIdx.x, d = threadIdx.x;
+  const bool live = a.query_ends[row] > 0;
+  int64_t source = 0;
+  uint64_t target = row;  // padding rows land in owner 0 at distinct positions
+  if (live) {
+    source = a.slot_mapping[a.gather_indices[row]];
+    target = static_cast<uint64_t>(a.row_owners[row / a.queries]) * a.history + static_cast<uint32_t>(a.query_ends[row] - 1);
+  }
+  if (!a.source_is_bf16) {
+    a.keys[target * 128u + d] = reinterpret_cast<const uint8_t*>(a.source_keys)[static_cast<uint64_t>(source) * 128u + d];
+    if (d == 0) a.scales[target] = a.source_scales[source];
+    return;
+  }
+  // bf16 row -> FP8 e4m3 with one scale per token: scale = amax / 448 (1 for an all-zero row)
+  __shared__ float warp_max[4];
+  const float x = __uint_as_float(static_cast<uint32_t>(
+                      reinterpret_cast<const uint16_t*>(a.source_keys)[static_cast<uint64_t>(source) * 128u + d]) << 16);
+  float m = fabsf(x);
+#pragma unroll
+  for (uint32_t o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((d & 31u) == 0) warp_max[d >> 5] = m;
+  __syncthreads();
+  const float amax = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  a.keys[target * 128u + d] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x / scale, __NV_SATFINITE, __NV_E4M3));
+  if (d == 0) a.scales[target] = scale;
+}
+
+// ---- SlotLRU commit ---------------------------------------------------------------------------
+constexpr uint32_t kLruThreads = 1024;
+
+__global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
+  __shared__ uint32_t scan[33];
+  __shared__ uint32_t unique_count;
+  const uint32_t row = blockIdx.x, tid = threadIdx.x;
+  const uint32_t active = min(static_cast<uint32_t>(max(a.active[row], 0)), a.capacity);
+  int32_t* order = a.order + static_cast<uint64_t>(row) * a.capacity;
+  uint32_t* bitmap = reinterpret_cast<uint32_t*>(a.bitmap) + static_cast<uint64_t>(row) * a.words;
+  int32_t* slots = a.slots + static_cast<uint64_t>(row) * kLruSlots;
+  int32_t* reserved = a.reserved_hot ? a.reserved_hot + static_cast<uint64_t>(row) * a.resident : nullptr;
+  const int32_t* touched = a.touched + static_cast<uint64_t>(row) * a.touched_stride;
+
+  if (tid == 0) unique_count = 0;
+  for (uint32_t w = tid; w < a.words; w += kLruThreads) bitmap[w] = 0;
+  if (reserved)
+    for (uint32_t i = tid; i < kLruSlots; i += kLruThreads) {
+      const int32_t old = slots[i];
+      if (old >= 0 && static_cast<uint32_t>(old) < a.resident) reserved[old] = -1;
+    }
+  __syncthreads();
+  // 1. distinct touched slots -> bitmap
+  uint32_t mine = 0;
+  for (uint32_t i = tid; i < a.touched_stride; i += kLruThreads) {
+    const int32_t s = touched[i];
+    if (s < 0 || static_cast<uint32_t>(s) >= active) continue;
+    const uint32_t bit = 1u << (s & 31);
+    if (!(atomicOr(bitmap + (s >> 5), bit) & bit)) ++mine;
+  }
+  if (mine) atomicAdd(&unique_count, mine);
+  __syncthreads();
+  const uint32_t unique = unique_count;
+  if (unique) {
+    // 2. drop the touched slots from the list, keeping the order of the rest (in place: a chunk
+    //    is fully in registers before anything is written, and writes never pass the reads)
+    uint32_t kept_total = 0;
+    for (uint32_t start = 0; start < active; start += kLruThreads * 4u) {
+      int32_t v[4];
+      uint32_t keep = 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t p = start + tid * 4u + j;
+        v[j] = p < active ? order[p] : -1;
+        if (v[j] >= 0 && !((bitmap[v[j] >> 5] >> (v[j] & 31)) & 1u)) keep |= 1u << j;
+      }
+      uint32_t total;
+      uint32_t offset = kept_total + block_exclusive_scan(__popc(keep), scan, &total);
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j)
+        if ((keep >> j) & 1u) order[offset++] = v[j];
+      kept_total += total;
+      __syncthreads();
+    }
+    // 3. append the touched slots in ascending slot number
+    const uint32_t active_words = (active + 31u) >> 5;
+    const uint32_t per = (active_words + kLruThreads - 1u) / kLruThreads;
+    uint32_t local = 0;
+    for (uint32_t w = tid * per; w < (tid + 1u) * per && w < active_words; ++w) local += __popc(bitmap[w]);
+    uint32_t out = kept_total + block_exclusive_scan(local, scan, nullptr);
+    for (uint32_t w = tid * per; w < (tid + 1u) * per && w < active_words; ++w) {
+      uint32_t bits = bitmap[w];
+      while (bits) {
+        order[out++] = static_cast<int32_t>(w * 32u + __ffs(bits) - 1u);
+        bits &= bits - 1u;
+      }
+    }
+    __syncthreads();
+  }
+  // 4. victims = the oldest min(2048, active) slots, their bitmap and inverse map
+  for (uint32_t w = tid; w < a.words; w += kLruThreads) bitmap[w] = 0;
+  __syncthreads();
+  for (uint32_t i = tid; i < kLruSlots; i += kLruThreads) {
+    const int32_t s = i < active ? order[i] : -1;
+    slots[i] = s;
+    if (s >= 0) {
+      atomicOr(bitmap + (s >> 5), 1u << (s & 31));
+      if (reserved && static_cast<uint32_t>(s) < a.resident) reserved[s] = static_cast<int32_t>(i);
+    }
+  }
+  if (tid == 0) a.unique[row] = static_cast<int32_t>(unique);
+}
+
+// ---- ABC tail maps -------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) abc_rows(int32_t* t2s, int32_t* s2t, const int32_t* descriptors,
+                                               uint32_t rows_per_group, uint32_t pool, uint32_t tokens,
+                                               uint32_t slots, uint32_t history, uint32_t tail) {
+  const int32_t* d = descriptors + (static_cast<uint64_t>(blockIdx.x) * rows_per_group + blockIdx.y) * 4u;
+  const int32_t layer = d[0], owner = d[1], begin = d[2], end = d[3];
+  int32_t* forward = t2s + (static_cast<uint64_t>(layer) * pool + owner) * tokens;
+  int32_t* reverse = s2t + (static_cast<uint64_t>(layer) * pool + owner) * slots + history;
+  for (int32_t t = begin + static_cast<int32_t>(threadIdx.x); t < end; t += 256)
+    forward[t] = static_cast<int32_t>(history) + t % static_cast<int32_t>(tail);
+  // reverse[j] = the last token of [begin, end) that maps to ring slot j, or -1
+  for (uint32_t j = threadIdx.x; j < tail; j += 256) {
+    int32_t value = -1;
+    if (end > begin) {
+      const int32_t last = end - 1;
+      const int32_t back = ((last - static_cast<int32_t>(j)) % static_cast<int32_t>(tail) + static_cast<int32_t>(tail)) %
+                           static_cast<int32_t>(tail);
+      const int32_t t = last - back;
+      if (t >= begin) value = t;
+    }
+    reverse[j] = value;
+  }
+}
+
+}  // namespace
+
+uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream) {
+  dim3 grid(kFetchBlocksPerRequest, a.batch);
+  fetch_rows<<<grid, kFetchThreads, 0, stream>>>(a);
+  count_launch();
+  return check_launch("fetch_rows");
+}
+
+uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream) {
+  dim3 grid(kTop / 8u, a.rows);
+  gather_rows<<<grid, 256, 0, stream>>>(a);
+  count_launch();
+  return check_launch("gather_rows");
+}
+
+}  // namespace kvip
+
+extern "C" uint32_t kvip_b200_fetch(const KvipFetchArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->source_base && a->fetch_sources && a->fetch_destinations && a->query_counts &&
+                   a->row_status && a->pool && a->hot_valid, "fetch: null pointer");
+  KVIP_REQUIRE(a->tokenBytes >= 16 && a->tokenBytes % 16 == 0, "fetch: token bytes must be a multiple of 16");
+  KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->pool) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->source_base) & 15u) == 0,
+               "fetch: pool and source base must be 16-byte aligned");
+  KVIP_REQUIRE(a->batch >= 1 && a->outputStride >= a->resident, "fetch: geometry");
+  return kvip::launch_fetch(*a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" uint32_t kvip_b200_gather(const KvipGatherArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->pool && a->slots && a->out, "gather: null pointer");
+  KVIP_REQUIRE(a->tokenBytes >= 16 && a->tokenBytes % 16 == 0, "gather: token bytes must be a multiple of 16");
+  KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->pool) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0,
+               "gather: pool and output must be 16-byte aligned");
+  KVIP_REQUIRE(a->rows >= 1 && a->queries >= 1 && a->rows % a->queries == 0, "gather: rows must be batch*queries");
+  return kvip::launch_gather(*a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" uint32_t kvip_b200_ingest(const KvipIngestArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->source_keys && a->slot_mapping && a->gather_indices && a->query_ends && a->row_owners &&
+                   a->keys && a->scales, "ingest: null pointer");
+  KVIP_REQUIRE(a->source_is_bf16 || a->source_scales, "ingest: FP8 sources need their scales");
+  KVIP_REQUIRE(a->batch >= 1 && a->queries >= 1 && a->queries <= KVIP_MAX_QUERIES, "ingest: bad batch/queries");
+  kvip::ingest_rows<<<a->batch * a->queries, 128, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::count_launch();
+  return kvip::check_launch("ingest_rows");
+}
+
+extern "C" uint32_t kvip_b200_lru_commit(const KvipLruArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->order && a->slots && a->bitmap && a->unique && a->touched && a->active, "lru_commit: null pointer");
+  KVIP_REQUIRE(a->rows >= 1 && a->capacity >= 1 && a->words * 32u >= a->capacity, "lru_commit: bitmap too small");
+  kvip::lru_commit<<<a->rows, kvip::kLruThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::count_launch();
+  return kvip::check_launch("lru_commit");
+}
+
+extern "C" uint32_t kvip_b200_update_abc(int32_t* token_to_slot, int32_t* slot_to_token, const int32_t* descriptors,
+                                         uint32_t groups, uint32_t rows_per_group, uint32_t requests, uint32_t pool,
+                                         uint32_t tokens, uint32_t slots, uint32_t history, uint32_t tail, void* stream) {
+  KVIP_REQUIRE(token_to_slot && slot_to_token && descriptors, "update_abc: null pointer");
+  KVIP_REQUIRE(groups >= 1 && requests >= 1 && requests <= rows_per_group && tail >= 1 && history + tail <= slots,
+               "update_abc: geometry");
+  dim3 grid(groups, requests);
+  kvip::abc_rows<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(token_to_slot, slot_to_token, descriptors,
+                                                                      rows_per_group, pool, tokens, slots, history, tail);
+  kvip::count_launch();
+  return kvip::check_launch("abc_rows");
+}

@@ -1,0 +1,524 @@
+// Lightning-indexer score on tcgen05 tensor cores.
+//
+//   score[t, s] = kscale[s] * sum_h W[t, h] * relu( q[t, h, :] . k[s, :] )
+//
+// What the reference computes in QLIMatmul::ComputeMm1 + ProcessVec1
+// (op_kernel/indexer/indexer_cube.h:161-322, indexer_vector.h:513-662,
+// indexer_score.h:59-140, 384-426), re-designed for sm_100a:
+//
+//   * the 128-token key page is the M operand (one TMA box per page of the paged Index
+//     cache, 128-byte swizzle), the request's query heads are the N operand, so the
+//     accumulator in tensor memory has one LANE per token and one COLUMN per
+//     (query, head). The ReLU * W reduction over heads is then a per-thread loop over
+//     columns: no cross-lane shuffle, no shared-memory transpose;
+//   * persistent CTAs (one per SM) walk a flat list of (request, page) tiles, so a
+//     request's keys and scales are streamed from HBM exactly once for all of its
+//     query rows;
+//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-5 =
+//     epilogue; key stages and two accumulator buffers are handed over with mbarriers;
+//   * every mbarrier wait is bounded: when a wait gives up the CTA sets
+//     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
+//     is released and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include "common.cuh"
+
+namespace kvip {
+namespace {
+
+constexpr uint32_t kLiThreads = 192;
+constexpr uint32_t kMaxBatch = 1024;
+constexpr uint32_t kMaxN = 256;            // query slots * heads
+constexpr uint32_t kAtomBytes = 128 * 128; // one 128-row x 128-byte swizzle atom
+constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
+
+template <bool kBf16> struct LiCfg {
+  static constexpr uint32_t kAtoms = kBf16 ? 2 : 1;           // 128-byte K slices per row
+  static constexpr uint32_t kTileBytes = kAtomBytes * kAtoms; // one key page in smem
+  static constexpr uint32_t kStages = kBf16 ? 4 : 8;
+  static constexpr uint32_t kQBytes = kMaxN * 128 * kAtoms;
+  static constexpr uint32_t kSmemBytes =
+      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 4 * kMaxN * 4 /*W per epilogue warp*/ +
+      (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 256 /*barriers*/;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait. Returns false when the CTA is aborting (this wait or another one gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  const long long start = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - start > kWaitCycles) break;
+    }
+  }
+  *abort_flag = 1u;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+template <bool kBf16>
+__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kBf16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 32 lanes x 32 columns of fp32: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);  // start address
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused here)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+struct TileCursor {  // walks the flat (request, page) list shared by the three roles
+  const uint32_t* prefix;
+  uint32_t batch, request;
+  __device__ TileCursor(const uint32_t* p, uint32_t b) : prefix(p), batch(b), request(0) {}
+  __device__ uint32_t seek(uint32_t tile) {
+    while (request + 1 < batch && tile >= prefix[request + 1]) ++request;
+    return request;
+  }
+};
+
+__device__ __forceinline__ float load_weight(const KvipLiArgs& a, uint32_t index) {
+  float w;
+  if (a.weightDtype == KVIP_WEIGHT_FP32) {
+    w = reinterpret_cast<const float*>(a.weights)[index];
+  } else {
+    w = __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(a.weights)[index]) << 16);
+  }
+  if (a.query_scale) w *= a.query_scale[index];
+  return w;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kLiThreads, 1)
+li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap query_map,
+                 const __grid_constant__ KvipLiArgs a) {
+  using Cfg = LiCfg<kBf16>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t key_smem = base;
+  const uint32_t q_smem = key_smem + Cfg::kStages * Cfg::kTileBytes;
+  float* w_smem = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kMaxN);
+  uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(active_q + kMaxBatch);
+  // barrier map: [0,S) full, [S,2S) empty, 2S..2S+1 tmem_full, 2S+2..2S+3 tmem_empty,
+  // 2S+4 q_full, 2S+5 q_empty; then the tmem base word and the abort flag.
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
+  constexpr uint32_t S = Cfg::kStages;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 6);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t H = a.heads, Q = a.queries, pages = a.pagesPerRequest;
+
+  // ---- per-CTA schedule: tiles per request -> prefix sums (warp 0) -------------------
+  if (warp == 0) {
+    uint32_t carry = 0;
+    if (lane == 0) prefix[0] = 0;
+    for (uint32_t b0 = 0; b0 < a.batch; b0 += 32) {
+      const uint32_t b = b0 + lane;
+      uint32_t tiles = 0, nq = 0;
+      if (b < a.batch) {
+        int32_t longest = 0;
+        for (uint32_t q = 0; q < Q; ++q) {
+          const int32_t end = a.query_ends[b * Q + q];
+          if (end > 0) { nq = q + 1; longest = max(longest, end); }
+        }
+        int32_t len = min(a.key_lengths[b], longest);
+        len = min(len, static_cast<int32_t>(pages * kBlockTokens));
+        if (nq && len > 0) tiles = (static_cast<uint32_t>(len) + kBlockTokens - 1) / kBlockTokens;
+        active_q[b] = static_cast<uint8_t>(tiles ? nq : 0);
+      }
+      uint32_t scan = tiles;
+#pragma unroll
+      for (uint32_t d = 1; d < 32; d <<= 1) {
+        uint32_t v = __shfl_up_sync(0xffffffffu, scan, d);
+        if (lane >= d) scan += v;
+      }
+      if (b < a.batch) prefix[b + 1] = carry + scan;
+      carry += __shfl_sync(0xffffffffu, scan, 31);
+    }
+  }
+  if (threadIdx.x == 64) {
+    for (uint32_t i = 0; i < S; ++i) { mbar_init(bar(i), 1); mbar_init(bar(S + i), 1); }
+    mbar_init(bar(2 * S + 0), 1); mbar_init(bar(2 * S + 1), 1);
+    mbar_init(bar(2 * S + 2), 128); mbar_init(bar(2 * S + 3), 128);
+    mbar_init(bar(2 * S + 4), 1); mbar_init(bar(2 * S + 5), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory: all 512 columns (one CTA per SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_slot)))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t total_tiles = prefix[a.batch];
+  const uint32_t tile_begin = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * blockIdx.x) / gridDim.x);
+  const uint32_t tile_end = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * (blockIdx.x + 1)) / gridDim.x);
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      TileCursor cur(prefix, a.batch);
+      uint32_t stage = 0, phase = 0, loaded_q = 0;
+      int32_t bound = -1;
+      for (uint32_t t = tile_begin; t < tile_end; ++t) {
+        const uint32_t b = cur.seek(t);
+        if (static_cast<int32_t>(b) != bound) {
+          if (!mbar_wait(bar(2 * S + 5), (loaded_q & 1u) ^ 1u, abort_flag)) break;
+          const uint32_t rows = active_q[b] * H;
+          mbar_expect_tx(bar(2 * S + 4), rows * 128u * Cfg::kAtoms);
+          for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
+            for (uint32_t r = 0; r < rows; r += 32)
+              tma_load_2d(q_smem + atom * (kMaxN * 128u) + r * 128u, &query_map,
+                          static_cast<int32_t>(atom * 64u), static_cast<int32_t>(b * Q * H + r),
+                          bar(2 * S + 4));
+          ++loaded_q;
+          bound = static_cast<int32_t>(b);
+        }
+        if (!mbar_wait(bar(S + stage), phase ^ 1u, abort_flag)) break;
+        const int32_t page = a.block_table[static_cast<uint64_t>(b) * pages + (t - prefix[b])];
+        mbar_expect_tx(bar(stage), Cfg::kTileBytes);
+        for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
+          tma_load_2d(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes, &key_map,
+                      static_cast<int32_t>(atom * 64u), page * static_cast<int32_t>(kBlockTokens), bar(stage));
+        if (++stage == S) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      TileCursor cur(prefix, a.batch);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, seen_q = 0, idesc = 0;
+      int32_t bound = -1;
+      for (uint32_t t = tile_begin; t < tile_end; ++t) {
+        const uint32_t b = cur.seek(t);
+        if (static_cast<int32_t>(b) != bound) {
+          if (!mbar_wait(bar(2 * S + 4), seen_q & 1u, abort_flag)) break;
+          ++seen_q;
+          bound = static_cast<int32_t>(b);
+          const uint32_t n = active_q[b] * H;
+          const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
+          idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+        }
+        if (!mbar_wait(bar(stage), phase, abort_flag)) break;
+        if (!mbar_wait(bar(2 * S + 2 + acc), acc_phase ^ 1u, abort_flag)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kMaxN;
+#pragma unroll
+        for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
+          const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
+          const uint64_t db = umma_desc(q_smem + atom * (kMaxN * 128u));
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k)  // 32 bytes of K per instruction
+            tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
+        }
+        tcgen05_commit(bar(S + stage));        // key stage free once these MMAs retire
+        tcgen05_commit(bar(2 * S + acc));      // accumulator ready for the epilogue
+        const bool last_of_request = (t + 1 == tile_end) || (t + 1 >= prefix[b + 1]);
+        if (last_of_request) tcgen05_commit(bar(2 * S + 5));  // query operand may be replaced
+        if (++stage == S) { stage = 0; phase ^= 1u; }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ================= epilogue: 4 warps, one token row per thread =================
+    const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
+    const uint32_t row = quad * 32u + lane;       // token row inside the page
+    float* w_warp = w_smem + (warp - 2u) * kMaxN;  // private copy: no cross-warp barrier needed
+    TileCursor cur(prefix, a.batch);
+    uint32_t acc = 0, acc_phase = 0, live_mask = 0;
+    int32_t bound = -1;
+    for (uint32_t t = tile_begin; t < tile_end; ++t) {
+      const uint32_t b = cur.seek(t);
+      const uint32_t nq = active_q[b];
+      if (static_cast<int32_t>(b) != bound) {
+        __syncwarp();
+        for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
+        live_mask = 0;
+        for (uint32_t q = 0; q < nq; ++q) live_mask |= (a.query_ends[b * Q + q] > 0 ? 1u : 0u) << q;
+        __syncwarp();
+        bound = static_cast<int32_t>(b);
+      }
+      const uint32_t tile = t - prefix[b];
+      const uint32_t token = tile * kBlockTokens + row;
+      const int32_t page = a.block_table[static_cast<uint64_t>(b) * pages + tile];
+      const float kscale = a.key_scale ? a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row] : 1.0f;
+      // warp-uniform outcome: the tensor-memory loads below need the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(2 * S + acc), acc_phase, abort_flag))) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * kMaxN;
+      for (uint32_t q = 0; q < nq; ++q) {
+        float even = 0.f, odd = 0.f;
+        for (uint32_t c = 0; c < H; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + q * H + c, v);
+          tmem_ld_wait();
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const float4 w = w4[j];
+            even = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, even);
+            odd = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, odd);
+            even = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, even);
+            odd = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, odd);
+          }
+        }
+        if ((live_mask >> q) & 1u) {
+          float score = (even + odd) * kscale;
+          if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
+          a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(bar(2 * S + 2 + acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(a.status, static_cast<int32_t>(KVIP_ERR_PIPELINE));
+    // give copies and MMAs that may still be in flight time to land before the CTA's
+    // shared and tensor memory are released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---- CUDA-core cross-check ------------------------------------------------------------
+// One thread per (query row, token). Products are accumulated over d = 0..127 with fmaf in
+// ascending order, heads with the even/odd fmaf chains of indexer_score.h:59-140: the same
+// arithmetic, in the same order, as the CPU oracle.
+__device__ __forceinline__ float decode_e4m3(uint8_t code) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(code), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+__global__ void __launch_bounds__(128) li_score_simt(const KvipLiArgs a) {
+  extern __shared__ float q_f32[];  // [heads * 128]
+  const uint32_t t = blockIdx.y, b = t / a.queries;
+  const int32_t end = a.query_ends[t];
+  const int32_t len = min(min(a.key_lengths[b], end), static_cast<int32_t>(a.pagesPerRequest * kBlockTokens));
+  const uint32_t token = blockIdx.x * 128u + threadIdx.x;
+  if (end <= 0 || static_cast<int32_t>(blockIdx.x * 128u) >= len) return;
+  const uint32_t H = a.heads;
+  for (uint32_t i = threadIdx.x; i < H * 128u; i += 128u) {
+    const uint64_t src = static_cast<uint64_t>(t) * H * 128u + i;
+    q_f32[i] = a.keyDtype == KVIP_KEY_BF16
+                   ? __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(a.query)[src]) << 16)
+                   : decode_e4m3(reinterpret_cast<const uint8_t*>(a.query)[src]);
+  }
+  __syncthreads();
+  const int32_t page = a.block_table[static_cast<uint64_t>(b) * a.pagesPerRequest + blockIdx.x];
+  const uint64_t key_row = static_cast<uint64_t>(page) * kBlockTokens + threadIdx.x;
+  float even = 0.f, odd = 0.f;
+  for (uint32_t h = 0; h < H; ++h) {
+    float dot = 0.f;
+    for (uint32_t d = 0; d < 128u; ++d) {
+      const float k = a.keyDtype == KVIP_KEY_BF16
+                          ? __uint_as_float(static_cast<uint32_t>(
+                                reinterpret_cast<const uint16_t*>(a.keys)[key_row * 128u + d]) << 16)
+                          : decode_e4m3(reinterpret_cast<const uint8_t*>(a.keys)[key_row * 128u + d]);
+      dot = fmaf(q_f32[h * 128u + d], k, dot);
+    }
+    const float w = load_weight(a, t * H + h);
+    if (h & 1u) odd = fmaf(fmaxf(dot, 0.f), w, odd);
+    else even = fmaf(fmaxf(dot, 0.f), w, even);
+  }
+  float score = (even + odd) * (a.key_scale ? a.key_scale[key_row] : 1.0f);
+  if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
+  a.scores[static_cast<uint64_t>(t) * a.scoreStride + token] = score;
+}
+
+// ---- host side -------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault, &qres) !=
+            cudaSuccess || qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+bool encode_rows_map(CUtensorMap* map, const void* base, uint64_t rows, bool bf16, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {128, rows};
+  const cuuint64_t strides[1] = {bf16 ? 256u : 128u};
+  const cuuint32_t box[2] = {bf16 ? 64u : 128u, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+            const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint32_t validate(const KvipLiArgs* a) {
+  KVIP_REQUIRE(a, "li_score: null argument struct");
+  KVIP_REQUIRE(a->query && a->keys && a->weights && a->key_lengths && a->query_ends && a->block_table &&
+                   a->scores && a->status, "li_score: null tensor pointer");
+  KVIP_REQUIRE(a->batch >= 1 && a->batch <= kMaxBatch, "li_score: batch must be in 1..1024");
+  KVIP_REQUIRE(a->queries >= 1 && a->queries <= KVIP_MAX_QUERIES, "li_score: 1..4 query slots per request");
+  KVIP_REQUIRE(a->heads == 32 || a->heads == 64, "li_score: 32 or 64 index heads");
+  KVIP_REQUIRE(a->pagesPerRequest >= 1 && a->scoreStride >= a->pagesPerRequest * kBlockTokens,
+               "li_score: score rows must cover every page");
+  KVIP_REQUIRE(a->keyRows >= kBlockTokens && a->keyRows % kBlockTokens == 0, "li_score: key rows must be whole pages");
+  KVIP_REQUIRE(a->keyDtype <= KVIP_KEY_BF16 && a->weightDtype <= KVIP_WEIGHT_FP32 && a->scoreMode <= KVIP_SCORE_BF16_AWAY,
+               "li_score: unknown dtype or score mode");
+  KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->keys) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->query) & 15u) == 0,
+               "li_score: keys and query must be 16-byte aligned");
+  return 0;
+}
+
+template <bool kBf16>
+uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
+  using Cfg = LiCfg<kBf16>;
+  CUtensorMap key_map, query_map;
+  if (!encode_rows_map(&key_map, a.keys, a.keyRows, kBf16, 128) ||
+      !encode_rows_map(&query_map, a.query, static_cast<uint64_t>(a.batch) * a.queries * a.heads, kBf16, 32)) {
+    set_error("li_score: cuTensorMapEncodeTiled failed");
+    return KVIP_BAD_ARGUMENT;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(li_score_tcgen05<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Cfg::kSmemBytes));
+    if (e != cudaSuccess) return check_launch("li_score attribute");
+    configured = true;
+  }
+  uint32_t ctas = a.ctas;
+  if (!ctas) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    ctas = static_cast<uint32_t>(sms);
+  }
+  li_score_tcgen05<kBf16><<<ctas, kLiThreads, Cfg::kSmemBytes, stream>>>(key_map, query_map, a);
+  count_launch();
+  return check_launch("li_score_tcgen05");
+}
+
+}  // namespace
+
+uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream) {
+  return a.keyDtype == KVIP_KEY_BF16 ? launch_tcgen05<true>(a, stream) : launch_tcgen05<false>(a, stream);
+}
+
+uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream) {
+  dim3 grid(a.pagesPerRequest, a.batch * a.queries);
+  li_score_simt<<<grid, 128, a.heads * 128 * sizeof(float), stream>>>(a);
+  count_launch();
+  return check_launch("li_score_simt");
+}
+
+}  // namespace kvip
+
+extern "C" uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream) {
+  if (uint32_t bad = kvip::validate(args)) return bad;
+  return kvip::launch_li_score(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" uint32_t kvip_b200_li_score_simt(const KvipLiArgs* args, void* stream) {
+  if (uint32_t bad = kvip::validate(args)) return bad;
+  return kvip::launch_li_score_simt(*args, static_cast<cudaStream_t>(stream));
+}
