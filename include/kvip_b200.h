@@ -323,6 +323,14 @@ uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* work
                                         void* stream, const KvipRuntimeShape* shape,
                                         uint32_t workers);
 uint32_t kvip_prepare_shape(KvipRuntimeShape* shape);    /* include/api.h:9 */
+
+/* ---- host-DDR KV pool ---------------------------------------------------------------
+ * Pins `bytes` of host memory at `host` (page-aligned, owned by the caller) and maps it into the
+ * device address space; *device_alias receives the pointer kernels read it through. The pool
+ * and its registration must outlive every graph that was captured with it. Replaces the KVAF
+ * UBmem lease (python/kvip/adapters/kvaf.py: UbmemLease; lifetch_ubmem/include/ubmem_abi.h:15-19). */
+uint32_t kvip_b200_host_register(void* host, uint64_t bytes, uint64_t* device_alias);
+uint32_t kvip_b200_host_unregister(void* host);
 uint32_t kvip_streaming_resolver_cores(void);            /* == 3, streaming.py:41-47 */
 uint32_t kvip_streaming_flag_count(void);                /* == 16 */
 uint32_t kvip_b200_abi_version(void);

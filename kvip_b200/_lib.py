@@ -115,7 +115,8 @@ _STAGES = {
 EXPORTS = tuple(_STAGES) + (
     "kvip_b200_update_abc", "kvip_b200_lidu_scratch_words", "kvip_lifetch_streaming_forward", "kvip_prepare_shape",
     "kvip_streaming_resolver_cores", "kvip_streaming_flag_count", "kvip_b200_abi_version",
-    "kvip_b200_context_bytes", "kvip_b200_workspace_bytes", "kvip_b200_launch_count", "kvip_b200_last_error")
+    "kvip_b200_context_bytes", "kvip_b200_workspace_bytes", "kvip_b200_launch_count", "kvip_b200_last_error",
+    "kvip_b200_host_register", "kvip_b200_host_unregister")
 
 _library = None
 
@@ -145,6 +146,9 @@ def load_library(path=None):
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = [], u32
     lib.kvip_b200_last_error.argtypes, lib.kvip_b200_last_error.restype = [], ctypes.c_char_p
+    lib.kvip_b200_host_register.argtypes = [vp, u64, ctypes.POINTER(u64)]
+    lib.kvip_b200_host_register.restype = u32
+    lib.kvip_b200_host_unregister.argtypes, lib.kvip_b200_host_unregister.restype = [vp], u32
     if path is None:
         _library = lib
     return lib

@@ -59,6 +59,28 @@ extern "C" uint32_t kvip_prepare_shape(KvipRuntimeShape* s) {
   return 0;
 }
 
+extern "C" uint32_t kvip_b200_host_register(void* host, uint64_t bytes, uint64_t* device_alias) {
+  using namespace kvip;
+  KVIP_REQUIRE(host && bytes && device_alias, "host_register: null argument");
+  cudaError_t e = cudaHostRegister(host, bytes, cudaHostRegisterMapped | cudaHostRegisterPortable);
+  if (e != cudaSuccess) return check_launch("cudaHostRegister");
+  void* alias = nullptr;
+  e = cudaHostGetDevicePointer(&alias, host, 0);
+  if (e != cudaSuccess) {
+    cudaHostUnregister(host);
+    return check_launch("cudaHostGetDevicePointer");
+  }
+  *device_alias = reinterpret_cast<uint64_t>(alias);
+  return 0;
+}
+
+extern "C" uint32_t kvip_b200_host_unregister(void* host) {
+  using namespace kvip;
+  KVIP_REQUIRE(host, "host_unregister: null argument");
+  if (cudaHostUnregister(host) != cudaSuccess) return check_launch("cudaHostUnregister");
+  return 0;
+}
+
 extern "C" uint32_t kvip_streaming_resolver_cores(void) { return 3; }
 extern "C" uint32_t kvip_streaming_flag_count(void) { return 16; }
 extern "C" uint32_t kvip_b200_abi_version(void) { return 1; }
@@ -82,7 +104,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   const KvipContext* ctx = ptr<const KvipContext>(bind[14]);
   KVIP_REQUIRE(ctx && ptr<const void>(bind[15]) == workspace_v, "forward: bindings do not name this context/workspace");
   KVIP_REQUIRE(std::memcmp(&ctx->shape, shape, sizeof(*shape)) == 0, "forward: shape differs from the bound context");
-  KVIP_REQUIRE(ws->history == shape->history && ws->resident == shape->resident && ws->max_events >= KVIP_CHANGE_CAPACITY,
+  KVIP_REQUIRE(ws->history == shape->history && ws->resident == shape->resident && ws->max_events >= KVIP_SLOTS,
                "forward: workspace geometry differs from the shape");
   KVIP_REQUIRE(static_cast<uint64_t>(upd[24]) == shape->history && static_cast<uint64_t>(upd[25]) == shape->resident,
                "forward: update bindings geometry differs from the shape");

@@ -40,7 +40,7 @@ template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kQBytes = kMaxN * 128 * kAtoms;
   static constexpr uint32_t kSmemBytes =
       1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 4 * kMaxN * 4 /*W per epilogue warp*/ +
-      (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 256 /*barriers*/;
+      (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 1024 /*barriers*/;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------
@@ -172,12 +172,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
 
-  const uint32_t key_smem = base;
+  // layout from the 1024-byte aligned base: [barriers + control, 1024 B][key stages][query tile]
+  // [W per epilogue warp][tile prefix][active queries]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  const uint32_t key_smem = base + 1024u;
   const uint32_t q_smem = key_smem + Cfg::kStages * Cfg::kTileBytes;
-  float* w_smem = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
+  float* w_smem = reinterpret_cast<float*>(smem + 1024u + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
   uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kMaxN);
   uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(active_q + kMaxBatch);
   // barrier map: [0,S) full, [S,2S) empty, 2S..2S+1 tmem_full, 2S+2..2S+3 tmem_empty,
   // 2S+4 q_full, 2S+5 q_empty; then the tmem base word and the abort flag.
   const uint32_t bar0 = smem_u32(bars);

@@ -130,9 +130,9 @@ def li_scores(query, keys, weights, query_scale, key_scale, key_lengths, query_e
                 continue
             t = b * queries + qi
             for begin in range(0, padded, chunk):
-                dots = np.einsum("hd,nd->hn", q[t], k[begin : begin + chunk], optimize=True)
-                s = (np.maximum(dots, 0) * w[t][:, None]).sum(0, dtype=np.float32) * ks[begin : begin + chunk]
-                out[t, begin : begin + chunk] = s
+                end = min(begin + chunk, padded)
+                dots = np.einsum("hd,nd->hn", q[t], k[begin:end], optimize=True)
+                out[t, begin:end] = (np.maximum(dots, 0) * w[t][:, None]).sum(0, dtype=np.float32) * ks[begin:end]
     if score_mode == 1:
         out = bf16_away(out)
     return out

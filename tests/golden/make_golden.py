@@ -1,0 +1,186 @@
+"""Regenerates the golden vectors under tests/golden/ by RUNNING THE REFERENCE's own CPU code.
+
+Run it only where the reference checkout is mounted (default /root/reference):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+What is imported and executed (paths inside the reference project):
+  * tests/operators/lifetch/support/workloads.py: prepare_fixture, prepare_full_chain_fixture,
+    prepare_compact_fixture (their logical_scores.npy are the reference's score goldens);
+  * tests/operators/lifetch/support/correctness.py: validate_topk (kept as a cross-check here);
+  * python/kvip/cache/lru.py (+ numba kernels), python/kvip/cache/abc.py (CPU branch);
+  * python/kvip/adapters/vllm/inputs.py + index_import.py (QueryInputs, ingest_decode on CPU);
+  * oracle/_ref/hot_slot_ref: the reference's csrc/operators/lidu/op_kernel/hot_slot_selection.h
+    compiled by oracle/Makefile, fed the cases of tests/operators/lidu/test_hot_slot_selection.py.
+Only inputs the CUDA path needs and the reference's outputs are stored (compressed .npz); the
+reference sources themselves are not copied.
+"""
+import json
+import random
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+from types import SimpleNamespace
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+
+
+def li_fixture(workloads, maker, **kwargs):
+    with tempfile.TemporaryDirectory() as tmp:
+        root = Path(tmp) / "fixture"
+        info = maker(root, **kwargs)
+        config = json.loads((root / "fixture.json").read_text())
+        history, queries, storage = config["history"], config["queries"], config["storage"]
+        heads = kwargs.get("index_heads", 64)
+        weights_dtype = np.float32
+        out = dict(
+            query=np.fromfile(root / "arg0.bin", np.uint8).reshape(queries, heads, 128),
+            keys=np.fromfile(root / "arg1.bin", np.uint8).reshape(-1, 128)[:storage],
+            weights=np.fromfile(root / "arg2.bin", weights_dtype).reshape(queries, heads),
+            query_scale=np.fromfile(root / "arg3.bin", np.float32).reshape(queries, heads),
+            key_scale=np.fromfile(root / "arg4.bin", np.float32)[:storage],
+            logical_scores=np.load(root / "logical_scores.npy"),
+            physical_to_logical=np.load(root / "physical_to_logical.npy"),
+            history=np.int64(history), resident=np.int64(config["resident"]),
+            visible=np.asarray(config["visible_lengths"], np.int64),
+        )
+        if isinstance(info, dict):
+            out["info"] = np.frombuffer(json.dumps(info).encode(), np.uint8)
+        return out
+
+
+def lru_trace(SlotLRU):
+    rng = np.random.default_rng(7)
+    lru = SlotLRU()
+    steps, snapshots = [], []
+
+    def order_of(l):
+        out, slot = [], int(l.head[0])
+        while slot >= 0:
+            out.append(slot)
+            slot = int(l.next[0, slot])
+        return np.asarray(out, np.int32)
+
+    def snap():
+        snapshots.append(dict(slots=lru.slots[0].copy(), order=order_of(lru), version=lru.version, active=lru.active,
+                              unique=int(lru.unique[0])))
+
+    for op, a, b in (("resize", 6000, 3000), ("commit", 500, 0), ("commit", 4096, 0), ("resize", 6000, 5000),
+                     ("commit", 2048, 0), ("commit", 8192, 0), ("resize", 20000, 16384), ("commit", 8192, 0),
+                     ("commit", 3, 0), ("resize", 20000, 100), ("commit", 64, 0), ("resize", 20000, 4000),
+                     ("commit", 8192, 0)):
+        if op == "resize":
+            lru.resize(a, b)
+            steps.append(dict(op=op, capacity=a, committed=b, touched=np.zeros(0, np.int32)))
+        else:
+            touched = rng.integers(0, max(lru.active, 1) + 50, a).astype(np.int32)  # in-contract: no negative slots
+            lru.commit(touched)
+            steps.append(dict(op=op, capacity=0, committed=0, touched=touched))
+        snap()
+    return steps, snapshots
+
+
+def main():
+    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    sys.path[:0] = [str(reference / "python"), str(reference / "tests/operators/lifetch/support")]
+    import torch
+    import workloads
+    from correctness import validate_topk
+
+    # ---- LI score / TopK fixtures ------------------------------------------------------------
+    exact = li_fixture(workloads, workloads.prepare_fixture, history=4096, resident=2048, queries=4)
+    np.savez_compressed(HERE / "li_exact_fixture.npz", **exact)
+    causal = li_fixture(workloads, workloads.prepare_fixture, history=4096, resident=2048, queries=4, causal=True)
+    np.savez_compressed(HERE / "li_exact_causal_fixture.npz", **causal)
+    chain = li_fixture(workloads, workloads.prepare_full_chain_fixture, history=8192, resident=4096, miss_percent=10)
+    np.savez_compressed(HERE / "li_full_chain_fixture.npz", **chain)
+    # cross-check with the reference's own validity oracle: the unique-cutoff fixture selects a unique set
+    bits = chain["logical_scores"].astype(np.uint32) << 16
+    scores = bits.view(np.float32)
+    ids = np.argsort(-scores, axis=1, kind="stable")[:, :2048]
+    validate_topk(ids, scores)
+    compact = li_fixture(workloads, workloads.prepare_compact_fixture, history=16384, resident=8192, miss_percent=10,
+                         index_heads=32)
+    np.savez_compressed(HERE / "li_compact_fixture.npz", **compact)
+
+    # ---- SlotLRU ------------------------------------------------------------------------------
+    from kvip.cache.lru import SlotLRU
+    steps, snaps = lru_trace(SlotLRU)
+    flat = {}
+    for i, (step, snapshot) in enumerate(zip(steps, snaps)):
+        flat[f"s{i}_op"] = np.frombuffer(step["op"].encode(), np.uint8)
+        flat[f"s{i}_args"] = np.asarray([step["capacity"], step["committed"], snapshot["version"], snapshot["active"],
+                                         snapshot["unique"]], np.int64)
+        flat[f"s{i}_touched"] = step["touched"]
+        flat[f"s{i}_slots"] = snapshot["slots"]
+        flat[f"s{i}_order"] = snapshot["order"]
+    flat["steps"] = np.int64(len(steps))
+    np.savez_compressed(HERE / "slot_lru_trace.npz", **flat)
+
+    # ---- ABC maps -------------------------------------------------------------------------------
+    from kvip.cache.abc import update_abc
+    descriptors = torch.tensor([[[2, 4, 350, 734], [2, 1, 768, 768]], [[0, 3, 383, 390], [0, 2, 128, 140]]],
+                               dtype=torch.int32)
+    t2s = torch.full((3, 5, 2048), 99, dtype=torch.int32)
+    s2t = t2s.clone()
+    stages = []
+    for shift in (0, 128):
+        descriptors[:, :, 2:] += shift
+        update_abc(t2s, s2t, descriptors, 2, 1024, 384)
+        stages.append((descriptors.numpy().copy(), t2s.numpy().copy(), s2t.numpy().copy()))
+    np.savez_compressed(HERE / "abc_maps.npz", d0=stages[0][0], t0=stages[0][1], s0=stages[0][2], d1=stages[1][0],
+                        t1=stages[1][1], s1=stages[1][2])
+
+    # ---- QueryInputs + paged Index ingest --------------------------------------------------------
+    from kvip.adapters.vllm.index_import import VllmIndexCacheStorage
+    from kvip.adapters.vllm.inputs import QueryInputs
+    rng = np.random.default_rng(11)
+    batch, history, owners = 3, 512, 6
+    inputs = QueryInputs(torch, batch, torch.device("cpu"), pin_memory=False, history=history)
+    counts, starts, row_owners = (2, 0, 4), (5, 0, 9), (4, 0, 2)
+    inputs.prepare(counts, query_starts=starts, query_owners=row_owners)
+    positions = torch.from_numpy(rng.integers(10, history - 1, 32).astype(np.int64))
+    inputs.bind_positions(positions)
+    storage = VllmIndexCacheStorage(torch, owners, history, 256, torch.device("cpu"))
+    cache_keys = torch.from_numpy(rng.integers(0, 256, (8, 128, 1, 128), dtype=np.uint8))
+    cache_scales = torch.from_numpy(rng.random((8, 128, 1), dtype=np.float32))
+    metadata = SimpleNamespace(slot_mapping=torch.from_numpy(rng.permutation(8 * 128)[:32].astype(np.int64)))
+    storage.keys.copy_(torch.from_numpy(rng.integers(0, 256, tuple(storage.keys.shape), dtype=np.uint8)))
+    before_keys, before_scales = storage.keys.numpy().copy(), storage.scales.numpy().copy()
+    storage.ingest_decode((cache_keys, cache_scales), metadata, inputs, inputs.row_owners)
+    np.savez_compressed(
+        HERE / "ingest_decode.npz", counts=np.asarray(counts), starts=np.asarray(starts), owners=np.asarray(row_owners),
+        metadata=inputs.metadata.numpy(), query_ends=inputs.query_ends.numpy(), positions=positions.numpy(),
+        block_table=inputs.block_table.numpy(), cache_keys=cache_keys.numpy(), cache_scales=cache_scales.numpy(),
+        slot_mapping=metadata.slot_mapping.numpy(), before_keys=before_keys, before_scales=before_scales,
+        after_keys=storage.keys.numpy(), after_scales=storage.scales.numpy(), token_count=np.int64(inputs.token_count))
+
+    # ---- hot-slot bitmap scan, with the reference's own header ---------------------------------------
+    binary = ROOT / "oracle" / "_ref" / "hot_slot_ref"
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "ref", f"REFERENCE={reference}"], check=True)
+    rnd = random.Random(21)  # the case list of tests/operators/lidu/test_hot_slot_selection.py:43-51
+    cases = []
+    for budget in (1, 31, 32, 33, 8192, 16384, 32768):
+        for begin in (0, budget // 2, budget - 1):
+            protected = {i for i in range(budget) if rnd.random() < 0.65}
+            free = sum(1 for i in range(budget) if i not in protected)
+            n = min(free, 4096)
+            words = [sum(1 << (i % 32) for i in protected if i // 32 == w) for w in range((budget + 31) // 32)]
+            cases.append((budget, begin, n, words))
+    data = "".join(" ".join(map(str, [b, c, n, *w])) + "\n" for b, c, n, w in cases)
+    result = subprocess.run([str(binary)], input=data, text=True, capture_output=True, check=True)
+    store = {"cases": np.int64(len(cases))}
+    for i, ((budget, begin, n, words), line) in enumerate(zip(cases, result.stdout.splitlines())):
+        store[f"c{i}_args"] = np.asarray([budget, begin, n], np.int64)
+        store[f"c{i}_words"] = np.asarray(words, np.uint32)
+        store[f"c{i}_slots"] = np.asarray(list(map(int, line.split())), np.int32)
+    np.savez_compressed(HERE / "hot_slot_scan.npz", **store)
+    print("golden vectors written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

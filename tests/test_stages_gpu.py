@@ -173,10 +173,10 @@ def test_topk_merge_equals_unsharded(device):
 
 
 RESOLVER_CASES = [
-    dict(seed=0, batch=3, queries=4, history=8192, resident=4096, hot_fraction=0.5, overlap=0.5),
+    dict(seed=0, batch=3, queries=4, history=16384, resident=8192, hot_fraction=0.5, overlap=0.5),
     dict(seed=1, batch=2, queries=1, history=16384, resident=2048, hot_fraction=0.0, overlap=0.0),   # all miss
     dict(seed=2, batch=2, queries=2, history=8192, resident=8192, hot_fraction=1.0, overlap=0.3),    # mostly hits
-    dict(seed=3, batch=2, queries=4, history=32768, resident=4096, hot_fraction=0.1, overlap=0.2,
+    dict(seed=3, batch=2, queries=4, history=32768, resident=16384, hot_fraction=0.3, overlap=0.5,
          lru_valid=1024),                                                                            # fallback scan
     dict(seed=4, batch=1, queries=4, history=32768, resident=2048, hot_fraction=0.0, overlap=0.0),   # no slots: error 4
 ]
