@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the LI -> TopK -> resolve -> Index exchange -> fetch -> gather decode step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line. Metric: query tokens/s of the decode step at 128k context (workload
+`decode_128k_b64`: batch 64 per GPU, 1 query token per request, 64 heads x 128, FP8 Index keys with
+per-token scales, TopK 2048, 25 % resident pool of 1152-byte KV rows, dense gather of the selected rows).
+Requests are partitioned over GPUs (one process per GPU, no data-path collective): weak scaling.
+`value` times CUDA-graph replays of the step with every input resident in HBM; `e2e` times the public
+API with host inputs (pinned H2D of the step's queries and positions, D2H of the slot/logical outputs).
+`--impl reference` times the reference's CPU golden path (the oracle restatement) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # the headline: BASELINE.json metric (128k context, batch 64 on one B200)
+    "decode_128k_b64": dict(batch=64, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
+                            len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+    # configs[1]: decode LI+TopK, B=64, 2 MTP tokens, ctx U[16k,32k]
+    "decode_32k_b64_mtp2": dict(batch=64, queries=2, heads=64, history=32768, resident=8192, len_lo=16384,
+                                len_hi=32768, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+    # small cases for profiler captures and smoke runs
+    "decode_16k_b16": dict(batch=16, queries=1, heads=64, history=16384, resident=4096, len_lo=16384, len_hi=16384,
+                           key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+    "decode_128k_b8": dict(batch=8, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
+                           len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+}
+METRIC = "LI+TopK+Fetch query tokens/s at 128k ctx"
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, maxes, reasons = [], [], set()
+        for line in out.splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 9:
+                continue
+            try:
+                clocks.append(float(cells[1]))
+                maxes.append(float(cells[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), cells[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
+                           "samples": len(clocks)}
+
+
+def li_algorithmic_bytes(lengths, queries, heads, key_bytes):
+    """Bytes the LI kernel must move per launch: every request's keys and key scales once, the query rows with
+    their head weights and query scales, and the fp32 score rows it writes."""
+    keys = sum(int(n) * (128 * key_bytes + 4) for n in lengths)
+    tokens = len(lengths) * queries
+    query = tokens * heads * (128 * key_bytes + 2 + 4)
+    scores = sum(int(n) * 4 * queries for n in lengths)
+    return keys + query + scores
+
+
+def time_region(torch, stream, fn, steps):
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop) / 1e3
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from kvip_b200 import _lib, ops
+    from kvip_b200.synthetic import DecodePipeline
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = dict(WORKLOADS[args.workload])
+    if args.batch:
+        cfg["batch"] = args.batch
+    lib = _lib.load_library()
+    p = DecodePipeline(device, seed=rank, gather=True, host_pool=not args.device_source, **cfg)
+    stream = torch.cuda.Stream(device)
+    tokens = p.query_tokens()
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    with torch.cuda.stream(stream):
+        # cold start: the first step fetches every selected row from the host pool
+        t0 = time.perf_counter()
+        p.step()
+        stream.synchronize()
+        cold_s = time.perf_counter() - t0
+        cold_reads = int(p.rotating.query_counts[:, 4].sum().item())
+        for _ in range(max(args.warmup - 1, 2)):
+            p.step()
+        stream.synchronize()
+        status = int(p.forward.li_status.item()) | int(p.update.status.max().item())
+        if status:
+            raise RuntimeError(f"device status {status} during warm-up")
+        before = lib.kvip_b200_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            p.step()
+        launches_per_step = lib.kvip_b200_launch_count() - before
+        for _ in range(2):
+            graph.replay()
+        barrier()
+
+        def soak(seconds):  # the same replays, long enough for the 100 ms clock sampler to see the load
+            end = time.perf_counter() + seconds
+            while time.perf_counter() < end:
+                for _ in range(20):
+                    graph.replay()
+                stream.synchronize()
+
+        with ClockSampler(local) as clocks:
+            soak(0.7)
+            barrier()
+            elapsed = time_region(torch, stream, graph.replay, args.steps)
+            barrier()
+            soak(0.7)
+        steady_reads = int(p.rotating.query_counts[:, 4].sum().item())
+
+        # ---- per-stage device time (each stage alone, K launches, inputs larger than L2) ------------
+        inputs, s, r, ws = p.workspace.inputs, p.storage, p.rotating, p.workspace
+        stages = {}
+        qe2d = inputs.query_ends.view(p.batch, p.queries)
+        keys_view = s.keys.view(torch.float8_e4m3fn) if p.key_dtype == "fp8" else s.keys
+        li = lambda: ops.li_score(inputs.query, keys_view.view(-1, 128), inputs.weights,  # noqa: E731
+                                  inputs.scale if p.key_dtype == "fp8" else None,
+                                  s.scales.view(-1) if p.key_dtype == "fp8" else None, ws.key_lengths, qe2d,
+                                  inputs.block_table, ws.scores, status=p.forward.li_status)
+        tk = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048))  # noqa: E731
+        ga = lambda: ops.gather(p.pool_hbm, p.update.slot_output.view(-1, 2048), p.gather_out,  # noqa: E731
+                                queries=p.queries, output_stride=p.output_stride, token_bytes=p.token_bytes,
+                                row_owners=inputs.row_owners)
+        for name, fn in (("li_score", li), ("topk", tk), ("gather", ga)):
+            for _ in range(2):
+                fn()
+            stream.synchronize()
+            stages[name] = time_region(torch, stream, fn, args.steps) / args.steps
+        stages["step_graph"] = elapsed / args.steps
+        stages["resolve_exchange_fetch_lru"] = max(0.0, stages["step_graph"] - stages["li_score"] - stages["topk"]
+                                                   - stages["gather"])
+
+        # ---- end to end: host inputs in, host outputs out, through the public objects ----------------
+        heads, T = p.heads, tokens
+        host_q = torch.empty((T, heads, 128), dtype=torch.uint8).pin_memory()
+        host_q.copy_(inputs.query.view(torch.uint8).cpu())
+        host_w = inputs.weights.cpu().pin_memory()
+        host_s = inputs.scale.cpu().pin_memory()
+        host_pos = p.positions.cpu().pin_memory()
+        dev_q = torch.empty_like(host_q, device=device).view(torch.float8_e4m3fn)
+        dev_w, dev_s, dev_pos = (torch.empty_like(x, device=device) for x in (host_w, host_s, host_pos))
+        host_out = torch.empty((2, T, 1, 2048), dtype=torch.int32).pin_memory()
+
+        def e2e_step():
+            dev_q.view(torch.uint8).copy_(host_q, non_blocking=True)
+            dev_w.copy_(host_w, non_blocking=True)
+            dev_s.copy_(host_s, non_blocking=True)
+            dev_pos.copy_(host_pos, non_blocking=True)
+            inputs.bind_positions(dev_pos)
+            inputs.pack(dev_q, dev_w, dev_s)
+            graph.replay()  # the captured step: forward + LRU feedback
+            host_out.copy_(p.update.outputs, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e2e_elapsed = time_region(torch, stream, e2e_step, args.steps)
+        barrier()
+        h2d = sum(x.numel() * x.element_size() for x in (host_q, host_w, host_s, host_pos))
+        d2h = host_out.numel() * host_out.element_size()
+
+    worst = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    elapsed, e2e_elapsed = (float(x) for x in worst.tolist())
+    hbm_peak, peak_kind = peaks()
+    key_bytes = 1 if p.key_dtype == "fp8" else 2
+    li_bytes = li_algorithmic_bytes(p.lengths, p.queries, p.heads, key_bytes)
+    achieved = li_bytes / stages["li_score"] / 1e9
+    step_bytes = li_bytes + 2 * tokens * 2048 * p.token_bytes  # + dense gather read and write
+    line = {
+        "metric": METRIC, "value": world * tokens * args.steps / elapsed, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": p.batch, "queries_per_request": p.queries,
+                   "context": int(p.lengths.max()), "index_heads": p.heads, "topk": 2048,
+                   "resident_slots": p.resident, "token_bytes": p.token_bytes, "cuda_graph": True,
+                   "partition": "by request, no collective",
+                   "l2": "inputs larger than L2 (keys %.0f MB per step)" % (li_bytes / 1e6),
+                   "miss_source": "device tensor" if args.device_source else "pinned mapped host pool"},
+        "e2e": {"value": world * tokens * args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": li_bytes, "us_per_launch": stages["li_score"] * 1e6,
+                     "traffic": None,
+                     "step_frac": step_bytes / stages["step_graph"] / 1e9 / hbm_peak},
+        "stages_us": {k: v * 1e6 for k, v in stages.items()},
+        "fetch": {"cold_step_reads": cold_reads, "cold_step_ms": cold_s * 1e3,
+                  "cold_host_link_gbs": cold_reads * p.token_bytes / cold_s / 1e9, "steady_reads_per_step": steady_reads},
+        "clocks": clocks.result,
+    }
+    if rank == 0:
+        if not args.no_cpu and world == 1:
+            line["cpu_baseline"] = cpu_baseline(cfg, args.cpu_requests)
+        print(json.dumps(line), flush=True)
+    p.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_step(cfg, requests, seed=0, budget_s=1e9):
+    """One pass of the reference's CPU golden path over `requests` requests of the workload:
+    NumPy einsum LI (tests/operators/lifetch/support/workloads.py:406-413 in the reference), canonical
+    TopK, resolver, Index exchange, row fetch and gather. Returns (seconds, query tokens)."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import kvip_oracle as oracle
+
+    rng = np.random.default_rng(seed)
+    heads, history, resident, queries = cfg["heads"], cfg["history"], cfg["resident"], cfg["queries"]
+    token_bytes = cfg["token_bytes"]
+    keys = oracle.encode_e4m3(np.clip(rng.standard_normal((history, 128), dtype=np.float32) * 8, -448, 448))
+    key_scale = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), history)).astype(np.float32)
+    query = oracle.encode_e4m3(np.clip(rng.standard_normal((queries, heads, 128), dtype=np.float32) * 8, -448, 448))
+    qscale = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), (queries, heads))).astype(np.float32)
+    weights = oracle.f32_to_bf16_rne((rng.standard_normal((queries, heads)) / 8).astype(np.float32))
+    length = cfg["len_hi"]
+    ends = np.array([[max(1, length - (queries - 1 - q)) for q in range(queries)]], np.int32)
+    table = np.arange(history // 128, dtype=np.int32).reshape(1, -1)
+    pool = np.zeros((resident, token_bytes), np.uint8)
+    host = np.zeros((history, token_bytes), np.uint8)
+    scales = key_scale.copy()
+    addresses = np.arange(history, dtype=np.int64) * token_bytes
+    logical = np.arange(history, dtype=np.int64)
+    lru = oracle.SlotLRUOracle()
+    lru.resize(resident, resident)
+    hot_valid = np.ones(resident, np.int32)
+    start = time.perf_counter()
+    done = 0
+    while done < requests and (done == 0 or time.perf_counter() - start < budget_s):
+        done += 1
+        scores = oracle.li_scores(query, keys, weights, qscale, scales, np.array([length], np.int32), ends, table)
+        selected = oracle.topk(scores, np.array([length], np.int32), ends)
+        ref = oracle.resolve_request(selected, hot_valid, lru.reserved_hot(resident), lru.slots, history, resident)
+        sources = addresses[ref["events_src"]]
+        oracle.exchange_request(keys, scales, addresses, logical, hot_valid, ref["events_src"], ref["events_dst"],
+                                ref["counts"], history, resident)
+        oracle.fetch_request(pool, hot_valid, host.reshape(-1), sources, ref["events_dst"], 0, resident, resident,
+                             token_bytes)
+        oracle.gather(pool, ref["locations"], np.zeros(1, np.int64), queries, resident)
+        lru.commit(ref["locations"].reshape(-1))
+    return time.perf_counter() - start, done * queries
+
+
+def cpu_baseline(cfg, requests):
+    seconds, tokens = cpu_step(cfg, requests, budget_s=15.0)
+    return {"value": tokens / seconds, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{tokens // cfg['queries']} requests of the workload (1 step each, about 15 s of CPU work), NumPy "
+                      f"golden LI + TopK + resolver + exchange + fetch + gather, {seconds:.2f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(WORKLOADS[args.workload])
+    for _ in range(min(args.warmup, 1)):
+        cpu_step(cfg, 1)
+    seconds, tokens = 0.0, 0
+    for step in range(args.steps):
+        s, t = cpu_step(cfg, args.cpu_requests_per_step, seed=step)
+        seconds, tokens = seconds + s, tokens + t
+    value = tokens / seconds
+    sample = (f"{args.cpu_requests_per_step} request(s) of the workload per step instead of {cfg['batch']}; "
+              f"NumPy golden LI + TopK + resolver + exchange + fetch + gather")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (NumPy)", "data": "synthetic",
+        "config": {"workload": args.workload, "context": cfg["len_hi"], "queries_per_request": cfg["queries"],
+                   "index_heads": cfg["heads"], "topk": 2048, "resident_slots": cfg["resident"],
+                   "token_bytes": cfg["token_bytes"]},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="decode_128k_b64")
+    parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")
+    parser.add_argument("--device-source", action="store_true", help="serve misses from HBM instead of the host pool")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--cpu-requests", type=int, default=4096, help="upper bound; the leg stops after ~15 s")
+    parser.add_argument("--cpu-requests-per-step", type=int, default=2)
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

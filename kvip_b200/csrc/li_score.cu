@@ -313,12 +313,28 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
     const uint32_t row = quad * 32u + lane;       // token row inside the page
     float* w_warp = w_smem + (warp - 2u) * kMaxN;  // private copy: no cross-warp barrier needed
-    TileCursor cur(prefix, a.batch);
+    TileCursor cur(prefix, a.batch), ahead(prefix, a.batch);
     uint32_t acc = 0, acc_phase = 0, live_mask = 0;
     int32_t bound = -1;
+    // The page index and the key scale of a tile are two dependent global loads. They are issued two
+    // and one tile ahead, so their latency is hidden behind the tile being reduced.
+    auto page_of = [&](uint32_t t) -> int32_t {
+      if (t >= tile_end) return 0;
+      const uint32_t b = ahead.seek(t);
+      return a.block_table[static_cast<uint64_t>(b) * pages + (t - prefix[b])];
+    };
+    auto scale_of = [&](uint32_t t, int32_t page) -> float {
+      if (t >= tile_end || !a.key_scale) return 1.0f;
+      return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
+    };
+    int32_t page_next = page_of(tile_begin);
+    float kscale = scale_of(tile_begin, page_next);
+    page_next = page_of(tile_begin + 1);
     for (uint32_t t = tile_begin; t < tile_end; ++t) {
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
+      const float kscale_next = scale_of(t + 1, page_next);   // consumed next iteration
+      page_next = page_of(t + 2);
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
         for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
@@ -327,21 +343,40 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         __syncwarp();
         bound = static_cast<int32_t>(b);
       }
-      const uint32_t tile = t - prefix[b];
-      const uint32_t token = tile * kBlockTokens + row;
-      const int32_t page = a.block_table[static_cast<uint64_t>(b) * pages + tile];
-      const float kscale = a.key_scale ? a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row] : 1.0f;
+      const uint32_t token = (t - prefix[b]) * kBlockTokens + row;
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(bar(2 * S + acc), acc_phase, abort_flag))) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * kMaxN;
       for (uint32_t q = 0; q < nq; ++q) {
         float even = 0.f, odd = 0.f;
-        for (uint32_t c = 0; c < H; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + q * H + c, v);
+        if (H == 64) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(taddr + q * 64u, v0);
+          tmem_ld_32x32(taddr + q * 64u + 32u, v1);
           tmem_ld_wait();
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * 64u);
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const float4 w = w4[j];
+            even = fmaf(fmaxf(__uint_as_float(v0[4 * j + 0]), 0.f), w.x, even);
+            odd = fmaf(fmaxf(__uint_as_float(v0[4 * j + 1]), 0.f), w.y, odd);
+            even = fmaf(fmaxf(__uint_as_float(v0[4 * j + 2]), 0.f), w.z, even);
+            odd = fmaf(fmaxf(__uint_as_float(v0[4 * j + 3]), 0.f), w.w, odd);
+          }
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const float4 w = w4[8 + j];
+            even = fmaf(fmaxf(__uint_as_float(v1[4 * j + 0]), 0.f), w.x, even);
+            odd = fmaf(fmaxf(__uint_as_float(v1[4 * j + 1]), 0.f), w.y, odd);
+            even = fmaf(fmaxf(__uint_as_float(v1[4 * j + 2]), 0.f), w.z, even);
+            odd = fmaf(fmaxf(__uint_as_float(v1[4 * j + 3]), 0.f), w.w, odd);
+          }
+        } else {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + q * 32u, v);
+          tmem_ld_wait();
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * 32u);
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j) {
             const float4 w = w4[j];
@@ -360,6 +395,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       tcgen05_fence_before();
       mbar_arrive(bar(2 * S + 2 + acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      kscale = kscale_next;
     }
   }
 

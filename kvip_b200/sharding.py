@@ -1,0 +1,69 @@
+"""Multi-GPU partitioning of the path. One process per GPU.
+
+* Requests are independent (per-request Index rows, resident pool, LRU and host-pool slice), so a batch is
+  split over ranks with no data-path collective: `partition_requests` balances the LI cost, which is
+  proportional to the context length.
+* The one exception is a single very long request: its keys are sharded along the sequence, every rank
+  scores its shard with the replicated query and takes a local top-2048 with global indices, the
+  (score, index) candidates are exchanged with ONE all-gather (16 KiB per rank) and every rank merges them
+  with the same total order (score descending, index ascending) - the result equals the unsharded TopK.
+  The reference has no multi-device code; its on-chip two-shard sequence split is the precedent
+  (csrc/operators/common/lifetch/sequence_schedule.h:9-37)."""
+import torch
+
+TOPK = 2048
+
+
+def partition_requests(lengths, world):
+    """Longest-processing-time-first assignment of request indices to `world` ranks.
+    Returns a list of index lists; deterministic (ties by request index)."""
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    bins, loads = [[] for _ in range(world)], [0] * world
+    for i in order:
+        target = min(range(world), key=lambda r: (loads[r], len(bins[r]), r))
+        bins[target].append(i)
+        loads[target] += int(lengths[i])
+    return [sorted(b) for b in bins]
+
+
+def shard_bounds(total_tokens, world, rank, block=128):
+    """Contiguous, block-aligned key range [begin, end) of a rank for a sequence-sharded request."""
+    blocks = (total_tokens + block - 1) // block
+    per, extra = divmod(blocks, world)
+    begin_block = rank * per + min(rank, extra)
+    end_block = begin_block + per + (1 if rank < extra else 0)
+    return min(begin_block * block, total_tokens), min(end_block * block, total_tokens)
+
+
+def gather_candidates(local_scores, local_index, group=None):
+    """All-gather of the per-rank candidates: [rows, 2048] each -> [rows, world*2048] in rank order."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    scores = [torch.empty_like(local_scores) for _ in range(world)]
+    index = [torch.empty_like(local_index) for _ in range(world)]
+    dist.all_gather(scores, local_scores.contiguous(), group=group)
+    dist.all_gather(index, local_index.contiguous(), group=group)
+    return torch.cat(scores, dim=1).contiguous(), torch.cat(index, dim=1).contiguous()
+
+
+def sequence_sharded_topk(local_scores, local_length, base_index, *, queries=1, group=None, local_topk=None,
+                          merge=None):
+    """Global TopK-2048 of a request whose score rows are sharded along the sequence.
+
+    local_scores [rows, shard_stride] fp32 on this rank, `local_length` valid keys in the shard, `base_index`
+    the global position of the shard's first key. `local_topk` / `merge` default to the CUDA kernels; the
+    CPU tests of the exchange logic inject host functions instead."""
+    from . import ops
+
+    rows = local_scores.shape[0]
+    device = local_scores.device
+    if local_topk is None:
+        lengths = torch.full((rows // queries,), local_length, dtype=torch.int32, device=device)
+        ends = torch.full((rows,), local_length, dtype=torch.int32, device=device)
+        cand_scores = torch.zeros((rows, TOPK), dtype=torch.float32, device=device)
+        cand_index = ops.topk(local_scores, lengths, ends, out_scores=cand_scores, base_index=base_index)
+    else:
+        cand_index, cand_scores = local_topk(local_scores, local_length, base_index)
+    all_scores, all_index = gather_candidates(cand_scores, cand_index, group)
+    return (merge or ops.topk_merge)(all_scores, all_index)

@@ -1,0 +1,144 @@
+"""Seeded synthetic decode workloads with the shapes and value distributions of the benchmark
+configs, built directly in device memory, and a `DecodePipeline` that wires the public objects
+(IndexCacheStorage, LIFetchWorkspace, HostKVPool, CudaBinding, IndexUpdate, SlotLRU, LIFetch) the way
+a serving adapter would. Used by bench.py, the smoke check and the end-to-end tests.
+
+The reference measures on captured decode traces and a calibrated generator that are not shipped;
+these inputs stand in for them: q_I / k_I ~ N(0,1) (bf16, or FP8 e4m3 with per-token key scales and
+per-(token, head) query scales drawn log-uniformly from [1e-3, 1e-1]), head weights ~ N(0, 1/64),
+context lengths uniform in [len_lo, len_hi], KV rows that identify (owner, token) in every 8-byte word."""
+import numpy as np
+import torch
+
+from . import _lib
+from .cache.index_storage import IndexCacheStorage
+from .cache.lru import SlotLRU
+from .operators.lifetch import CudaBinding, HostKVPool, IndexUpdate, LIFetch, LIFetchWorkspace
+
+TOPK = 2048
+
+
+def payload_rows(owner, tokens, token_bytes):
+    """Self-identifying KV rows (NumPy, host): word w of row (owner, token) mixes all three."""
+    tokens = np.asarray(tokens, dtype=np.uint64).reshape(-1, 1)
+    words = np.arange(token_bytes // 8, dtype=np.uint64)[None, :]
+    value = ((np.uint64(owner + 1) << np.uint64(48)) ^ (tokens << np.uint64(16)) ^ words
+             ^ (tokens * np.uint64(0x9E3779B97F4A7C15)))
+    return value.view(np.uint8).reshape(len(tokens), token_bytes)
+
+
+def _log_uniform(shape, lo, hi, generator, device):
+    u = torch.rand(shape, generator=generator, device=device, dtype=torch.float32)
+    return torch.exp(u * (np.log(hi) - np.log(lo)) + np.log(lo))
+
+
+class DecodePipeline:
+    def __init__(self, device, *, batch, queries=1, heads=64, history, resident, len_lo, len_hi, key_dtype="fp8",
+                 weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
+                 score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0):
+        self.device = device = torch.device(device)
+        self.batch, self.queries, self.heads, self.history, self.resident = batch, queries, heads, history, resident
+        self.token_bytes, self.key_dtype = token_bytes, key_dtype
+        owners = owners or batch
+        self.owners = owners
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        rng = np.random.default_rng(seed)
+        bf16 = key_dtype == "bf16"
+        self.storage = IndexCacheStorage(torch, owners, history, resident, device,
+                                         key_dtype=torch.bfloat16 if bf16 else torch.uint8)
+        self.workspace = LIFetchWorkspace(
+            torch, batch=batch, history=history, device=device, index_heads=heads, queries=queries,
+            query_dtype=torch.bfloat16 if bf16 else torch.float8_e4m3fn,
+            weight_dtype=torch.float32 if weight_dtype == "fp32" else torch.bfloat16)
+        # ---- Index keys and scales, one owner at a time to bound temporaries ------------------------
+        for owner in range(owners):
+            if bf16:
+                self.storage.keys[owner].copy_(torch.randn((history, 128), generator=g, device=device).to(torch.bfloat16))
+            else:
+                scale = _log_uniform((history,), 1e-3, 1e-1, g, device)
+                values = (torch.randn((history, 128), generator=g, device=device) * 8).clamp_(-448, 448)
+                self.storage.keys[owner].copy_(values.to(torch.float8_e4m3fn).view(torch.uint8))
+                self.storage.scales[owner].copy_(scale)
+        # ---- requests --------------------------------------------------------------------------------
+        self.lengths = rng.integers(len_lo, len_hi + 1, batch).astype(np.int32)
+        owner_order = rng.permutation(owners)[:batch] if permute_owners else np.arange(batch)
+        self.row_owner_list = [int(o) for o in owner_order]
+        inputs = self.workspace.inputs
+        inputs.prepare((queries,) * batch, query_owners=tuple(self.row_owner_list))
+        positions = np.zeros(batch * queries, dtype=np.int64)
+        for b in range(batch):
+            for q in range(queries):
+                positions[b * queries + q] = max(0, int(self.lengths[b]) - (queries - q))  # MTP: len-Q .. len-1
+        self.positions = torch.from_numpy(positions).to(device)
+        inputs.bind_positions(self.positions)
+        self.workspace.key_lengths.copy_(torch.from_numpy(self.lengths))
+        self.new_queries(seed)
+        # ---- KV pools ----------------------------------------------------------------------------------
+        self.output_stride = resident
+        self.pool_hbm = torch.zeros((owners * self.output_stride, token_bytes), dtype=torch.uint8, device=device)
+        self.host_pool = None
+        source = None
+        if host_pool:
+            self.host_pool = HostKVPool(torch, owners, history, token_bytes, device)
+            if fill_payload:
+                for owner in range(owners):
+                    self.host_pool.tensor[owner].copy_(torch.from_numpy(payload_rows(owner, np.arange(history), token_bytes)))
+            for owner in range(owners):
+                self.storage.addresses[owner].copy_(self.host_pool.addresses(owner))
+        else:
+            source = torch.zeros((owners * history, token_bytes), dtype=torch.uint8, device=device)
+            if fill_payload:
+                for owner in range(owners):
+                    source[owner * history:(owner + 1) * history].copy_(
+                        torch.from_numpy(payload_rows(owner, np.arange(history), token_bytes)))
+            identity = torch.arange(history, dtype=torch.int64, device=device)
+            for owner in range(owners):
+                self.storage.addresses[owner].copy_((identity + owner * history) * token_bytes)
+        self.source = source
+        self.gather_out = (torch.zeros((batch * queries, TOPK, token_bytes), dtype=torch.uint8, device=device)
+                           if gather else None)
+        # ---- bindings -----------------------------------------------------------------------------------
+        self.workspace.allocate_rotation(torch, batch=batch, history=history, resident=resident)
+        self.rotating = CudaBinding(
+            torch, self.workspace.arguments(self.storage), self.host_pool, self.pool_hbm, batch=batch, history=history,
+            resident=resident, query_ends=inputs.query_ends, hot_valid=self.storage.hot_valid,
+            token_addresses=self.storage.addresses, row_owners=inputs.row_owners, scratch=self.workspace.scratch,
+            token_bytes=token_bytes, queries=queries, score_mode=score_mode, gather_output=self.gather_out,
+            li_variant=li_variant, source=source, sm_count=sm_count)
+        self.update = IndexUpdate(
+            torch, keys=self.storage.keys, scales=self.storage.scales, addresses=self.storage.addresses,
+            logical_ids=self.storage.logical_ids, row_owners=inputs.row_owners, rotating=self.rotating,
+            query_inputs=inputs)
+        self.lru = SlotLRU(device, rows=batch, slots=self.rotating.lru_slots, reserved_hot=self.rotating.reserved_hot)
+        self.lru.resize(resident, resident)
+        self.forward = LIFetch(self.rotating, self.update)
+
+    def new_queries(self, seed):
+        """Fresh projected queries / head weights for all rows, packed through QueryInputs.pack."""
+        device, heads = self.device, self.heads
+        tokens = self.batch * self.queries
+        g = torch.Generator(device=device)
+        g.manual_seed(1000003 + seed)
+        inputs = self.workspace.inputs
+        w = torch.randn((tokens, heads), generator=g, device=device) / 8
+        weights = w if inputs.weights.dtype == torch.float32 else w.to(torch.bfloat16)
+        if self.key_dtype == "bf16":
+            query = torch.randn((tokens, heads, 128), generator=g, device=device).to(torch.bfloat16)
+            scale = None
+        else:
+            query = (torch.randn((tokens, heads, 128), generator=g, device=device) * 8).clamp_(-448, 448).to(torch.float8_e4m3fn)
+            scale = _log_uniform((tokens, heads), 1e-3, 1e-1, g, device)
+        inputs.pack(query, weights, scale)
+
+    def step(self):
+        """One decode step of the path: the fused forward, then the LRU feedback of the slots it used."""
+        self.forward()
+        self.lru.commit(self.update.slot_output.view(self.batch, -1))
+
+    def query_tokens(self):
+        return self.batch * self.queries
+
+    def close(self):
+        if self.host_pool is not None:
+            self.host_pool.close()

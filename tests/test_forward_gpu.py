@@ -1,0 +1,207 @@
+"""End-to-end parity of `kvip_b200.LIFetch` (one C call per step) with the oracle chain, on the
+benchmark's CPU-golden configuration and on FP8/MTP variants, plus CUDA-graph replay (B200 only)."""
+import numpy as np
+import pytest
+import torch
+
+import kvip_oracle as oracle
+import oracle_c
+from kvip_b200 import _lib
+from kvip_b200.synthetic import DecodePipeline, payload_rows
+
+pytestmark = pytest.mark.gpu
+TOPK = 2048
+
+
+def snapshot(p):
+    s = p.storage
+    keys = s.keys.view(torch.int16) if s.keys.dtype == torch.bfloat16 else s.keys
+    return dict(
+        keys=keys.cpu().numpy().copy(), scales=s.scales.cpu().numpy().copy(),
+        addresses=s.addresses.cpu().numpy().copy(), logical=s.logical_ids.cpu().numpy().copy(),
+        hot_valid=s.hot_valid.cpu().numpy().copy(), pool=p.pool_hbm.cpu().numpy().copy(),
+        lru_slots=p.rotating.lru_slots.cpu().numpy().copy(), reserved=p.rotating.reserved_hot.cpu().numpy().copy(),
+        order=p.lru.order.cpu().numpy().copy())
+
+
+def oracle_step(p, before, scores):
+    """The whole step on the CPU, from the device's own fp32 scores (so that everything downstream of
+    the LI tolerance is compared bit for bit)."""
+    batch, queries, history, resident = p.batch, p.queries, p.history, p.resident
+    key_lengths = p.workspace.key_lengths.cpu().numpy()
+    query_ends = p.workspace.inputs.query_ends.cpu().numpy()
+    owners = p.workspace.inputs.row_owners.cpu().numpy()
+    topk = oracle_c.topk(scores, key_lengths, query_ends).reshape(batch, queries, TOPK)
+    state = {k: v.copy() for k, v in before.items()}
+    host = p.host_pool.flat.numpy() if p.host_pool is not None else p.source.cpu().numpy().reshape(-1)
+    logical_out = np.full((batch * queries, TOPK), -1, np.int32)
+    slot_out = np.full((batch * queries, TOPK), -1, np.int32)
+    reads = []
+    for b in range(batch):
+        owner = int(owners[b])
+        ref = oracle.resolve_request(topk[b], state["hot_valid"][owner], state["reserved"][b], state["lru_slots"][b],
+                                     history, resident)
+        assert ref["error"] == 0
+        for q in range(queries):
+            live = topk[b, q] >= 0
+            logical_out[b * queries + q, live] = state["logical"][owner][topk[b, q][live]]
+            slot_out[b * queries + q] = ref["locations"][q]
+        sources = state["addresses"][owner][ref["events_src"]]
+        err = oracle.exchange_request(state["keys"][owner], state["scales"][owner], state["addresses"][owner],
+                                      state["logical"][owner], state["hot_valid"][owner], ref["events_src"],
+                                      ref["events_dst"], ref["counts"], history, resident)
+        assert err == 0
+        oracle.fetch_request(state["pool"], state["hot_valid"][owner], host, sources,
+                             owner * p.output_stride + ref["events_dst"], owner, p.output_stride, resident,
+                             p.token_bytes)
+        reads.append(ref["total"])
+    gathered = oracle.gather(state["pool"], slot_out, owners, queries, p.output_stride)
+    # LRU feedback: touched slots move to the tail in ascending slot order
+    for b in range(batch):
+        lru = oracle.SlotLRUOracle()
+        lru.order, lru.active = state["order"][b][:resident].copy(), resident
+        lru.commit(slot_out[b * queries:(b + 1) * queries].reshape(-1))
+        state["order"][b][:resident] = lru.order
+        state["lru_slots"][b] = lru.slots
+        state["reserved"][b] = lru.reserved_hot(resident)
+    return state, topk, logical_out, slot_out, gathered, reads
+
+
+def li_tolerance_check(p, scores):
+    """Device LI scores against the NumPy golden formula, on the valid prefix of every row."""
+    inputs, s = p.workspace.inputs, p.storage
+    bf16 = p.key_dtype == "bf16"
+    as_np = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else (  # noqa: E731
+        t.cpu().view(torch.uint8).numpy() if t.element_size() == 1 else t.cpu().numpy())
+    query_ends = inputs.query_ends.cpu().numpy().reshape(p.batch, p.queries)
+    expected = oracle.li_scores(
+        as_np(inputs.query), as_np(s.keys).reshape(-1, 128), as_np(inputs.weights),
+        None if bf16 else inputs.scale.cpu().numpy(), None if bf16 else s.scales.cpu().numpy().reshape(-1),
+        p.workspace.key_lengths.cpu().numpy(), query_ends, inputs.block_table.cpu().numpy(), key_is_bf16=bf16,
+        weight_is_bf16=inputs.weights.dtype == torch.bfloat16)
+    rtol = 2e-3 if bf16 else 1e-2
+    for t in range(scores.shape[0]):
+        n = int(min(query_ends.reshape(-1)[t], p.workspace.key_lengths[t // p.queries]))
+        if n <= 0:
+            continue
+        ref, out = expected[t, :n], scores[t, :n]
+        assert (np.abs(out - ref) <= rtol * np.abs(ref) + rtol * 1e-2 * np.abs(ref).max()).all()
+    return expected
+
+
+CONFIGS = [
+    # C1, the CPU-golden decode: B=4, 1 query, ctx U[2048,4096], 64 heads bf16, fp32 weights, 576-dim bf16 KV rows,
+    # 8192-slot resident pool that starts empty, SlotLRU fresh, seed 0
+    dict(batch=4, queries=1, heads=64, history=16384, resident=8192, len_lo=2048, len_hi=4096, key_dtype="bf16",
+         weight_dtype="fp32", token_bytes=1152, seed=0),
+    # FP8 keys + per-token scales, 2 MTP queries, cold context beyond the resident prefix, more owners than rows
+    dict(batch=3, queries=2, heads=64, history=12288, resident=4096, len_lo=9000, len_hi=12288, key_dtype="fp8",
+         weight_dtype="bf16", token_bytes=1152, seed=1, owners=5),
+    # the reference's 4 query slots, 32 heads, 656-byte rows, misses served from a device-resident source
+    dict(batch=2, queries=4, heads=32, history=8192, resident=6144, len_lo=7000, len_hi=8192, key_dtype="fp8",
+         weight_dtype="bf16", token_bytes=656, seed=2, host_pool=False),
+]
+
+
+@pytest.mark.parametrize("config", CONFIGS, ids=["c1_bf16", "fp8_mtp2", "q4_h32"])
+def test_forward_matches_oracle_over_steps(config, device):
+    p = DecodePipeline(device, fill_payload=True, **config)
+    try:
+        total_reads = []
+        for step in range(3):
+            if step == 2:
+                p.new_queries(config["seed"])      # repeat the first step's queries: mostly hits now
+            elif step:
+                p.new_queries(config["seed"] + 100 * step)
+            before = snapshot(p)
+            p.step()
+            torch.cuda.synchronize()
+            assert int(p.forward.li_status.item()) == 0
+            assert (p.update.status.cpu().numpy() == 0).all() and (p.rotating.row_status[:, 0].cpu().numpy() == 0).all()
+            scores = p.workspace.scores.cpu().numpy()
+            li_tolerance_check(p, scores)
+            state, topk, logical_out, slot_out, gathered, reads = oracle_step(p, before, scores)
+            total_reads.append(reads)
+            assert np.array_equal(p.workspace.topk.cpu().numpy(), topk)
+            assert np.array_equal(p.update.logical_output.cpu().numpy().reshape(-1, TOPK), logical_out)
+            assert np.array_equal(p.update.slot_output.cpu().numpy().reshape(-1, TOPK), slot_out)
+            after = snapshot(p)
+            for name in ("keys", "scales", "addresses", "logical", "hot_valid", "pool", "lru_slots", "reserved"):
+                assert np.array_equal(after[name], state[name]), (step, name)
+            assert np.array_equal(after["order"][:, :p.resident], state["order"][:, :p.resident])
+            assert np.array_equal(p.gather_out.cpu().numpy(), gathered)
+            assert np.array_equal(p.rotating.query_counts[:, 4].cpu().numpy(), np.asarray(reads))
+            # fetched bytes identify the selected logical token of the right owner
+            owners = p.workspace.inputs.row_owners.cpu().numpy()
+            got = p.gather_out.cpu().numpy()
+            for t in range(p.batch * p.queries):
+                live = logical_out[t] >= 0
+                want = payload_rows(int(owners[t // p.queries]), logical_out[t][live], p.token_bytes)
+                assert np.array_equal(got[t][live], want)
+            # Index rows stay a permutation of the logical tokens
+            for owner in set(int(o) for o in owners):
+                assert np.array_equal(np.sort(after["logical"][owner]), np.arange(p.history))
+        assert sum(total_reads[2]) < sum(total_reads[0]), "a repeated query must mostly hit the resident pool"
+    finally:
+        p.close()
+
+
+def test_forward_is_graph_capturable_and_allocation_free(device):
+    config = dict(batch=3, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=5, host_pool=False)
+    eager = DecodePipeline(device, fill_payload=True, **config)
+    graphed = DecodePipeline(device, fill_payload=True, **config)
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        graphed.step()                       # warm-up outside capture (lazy function attributes)
+        eager.step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = torch.cuda.memory_allocated(device)
+        launches = _lib.load_library().kvip_b200_launch_count()
+        with torch.cuda.graph(graph, stream=stream):
+            graphed.step()
+        assert _lib.load_library().kvip_b200_launch_count() - launches == 8  # LI, TopK, resolve, outputs, exchange, fetch, gather, LRU
+        for replay in range(3):
+            for p in (eager, graphed):
+                p.new_queries(40 + replay)   # in-place update of the captured input buffers
+            eager.step()
+            graph.replay()
+            stream.synchronize()
+            assert torch.equal(eager.workspace.topk, graphed.workspace.topk)
+            assert torch.equal(eager.update.slot_output, graphed.update.slot_output)
+            assert torch.equal(eager.update.logical_output, graphed.update.logical_output)
+            assert torch.equal(eager.gather_out, graphed.gather_out)
+            assert torch.equal(eager.storage.logical_ids, graphed.storage.logical_ids)
+            assert torch.equal(eager.rotating.lru_slots, graphed.rotating.lru_slots)
+        after = torch.cuda.memory_allocated(device)
+        eager.forward()
+        assert torch.cuda.memory_allocated(device) == after, "forward() must not allocate"
+        assert after - before < (64 << 20)
+
+
+def test_forward_rejects_mismatched_shape(device):
+    config = dict(batch=2, queries=1, heads=64, history=4096, resident=2048, len_lo=3000, len_hi=4096, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=3, host_pool=False, gather=False)
+    p = DecodePipeline(device, **config)
+    p.forward()
+    other = _lib.RuntimeShape.prepare(p.rotating.library, batch=2, history=8192, resident=2048, indexHeads=64, queries=1,
+                                      tokenBytes=1152)
+    import ctypes
+    p.forward.shape_pointer = ctypes.byref(other)
+    with pytest.raises(RuntimeError, match="100000"):
+        p.forward()
+    torch.cuda.synchronize()
+
+
+def test_status_reports_exhausted_pool(device):
+    """All-miss rounds larger than the pool: the request fails closed - error 4, outputs -1, residency dropped."""
+    config = dict(batch=1, queries=4, heads=32, history=32768, resident=2048, len_lo=32768, len_hi=32768,
+                  key_dtype="fp8", weight_dtype="bf16", token_bytes=656, seed=9, host_pool=False, gather=False)
+    p = DecodePipeline(device, **config)
+    p.forward()
+    torch.cuda.synchronize()
+    assert int(p.rotating.row_status[0, 0]) == oracle.ERR_NO_SLOT
+    assert int(p.update.status[0]) == oracle.ERR_NO_SLOT
+    assert (p.update.slot_output.cpu().numpy() == -1).all()
+    assert int(p.storage.hot_valid.sum()) == 0

@@ -1,0 +1,183 @@
+"""CPU tests of the host side: the C ABI loads and exports every declared symbol, geometry validation,
+ABI record layouts, QueryInputs packing against the reference's golden, request partitioning, and the
+sequence-shard exchange among two gloo ranks. No kernel is launched here."""
+import ctypes
+import json
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import kvip_oracle as oracle
+from golden_cases import GOLDEN
+from kvip_b200 import _lib, sharding
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def library():
+    from kvip_b200.build import build_library
+    build_library()
+    return _lib.load_library()
+
+
+def test_library_exports_every_declared_symbol(library):
+    header = (ROOT / "include" / "kvip_b200.h").read_text()
+    declared = set(re.findall(r"\b(kvip_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
+    for name in declared:
+        assert hasattr(library, name), name
+
+
+def test_abi_record_sizes(library):
+    assert ctypes.sizeof(_lib.RuntimeShape) == 80
+    assert ctypes.sizeof(_lib.Workspace) == 256 == library.kvip_b200_workspace_bytes()
+    assert ctypes.sizeof(_lib.Context) == library.kvip_b200_context_bytes()
+    assert _lib.Workspace.options.offset == 96            # reference streaming.py:146 writes the options word there
+    assert _lib.RuntimeShape.tokenBytes.offset == 14 * 4  # same index as the reference's tokenBytes
+    assert library.kvip_streaming_resolver_cores() == 3 and library.kvip_streaming_flag_count() == 16
+
+
+def test_prepare_shape_accepts_benchmark_geometries_and_derives_fields(library):
+    for batch, history, resident, queries in ((4, 16384, 8192, 1), (64, 32768, 8192, 2), (64, 131072, 32768, 1),
+                                              (256, 131072, 65536, 1), (1, 1 << 20, 2048, 4)):
+        shape = _lib.RuntimeShape.prepare(library, batch=batch, history=history, resident=resident, indexHeads=64,
+                                          queries=queries, tokenBytes=1152)
+        assert (shape.pagesPerRequest, shape.scoreStride, shape.outputStride, shape.owners, shape.finalWorkers) == (
+            history // 128, history, resident, batch, 4)
+        assert shape.keyRows == batch * history
+
+
+@pytest.mark.parametrize("bad", [
+    dict(batch=0), dict(batch=1025), dict(indexHeads=16), dict(queries=0), dict(queries=5), dict(history=131073),
+    dict(resident=16385), dict(resident=1024), dict(resident=262144, history=262144), dict(history=8192, resident=16384),
+    dict(tokenBytes=100), dict(tokenBytes=0), dict(keyDtype=2), dict(outputStride=1000)])
+def test_prepare_shape_rejects(bad, library):
+    """Same contract failures as the reference's check suite (correctness.py:68-109): ValueError, no launch."""
+    fields = dict(batch=2, history=131072, resident=16384, indexHeads=64, queries=4, tokenBytes=656)
+    fields.update(bad)
+    with pytest.raises(ValueError):
+        _lib.RuntimeShape.prepare(library, **fields)
+
+
+def test_stage_entry_points_reject_null_arguments(library):
+    """Argument checks run before any CUDA call, so they are testable without a device."""
+    for name, struct in _lib._STAGES.items():
+        assert getattr(library, name)(ctypes.byref(struct()), None) == _lib.BAD_ARGUMENT, name
+    assert library.kvip_lifetch_streaming_forward(None, None, None, None, None, 2) == _lib.BAD_ARGUMENT
+    assert b"null" in library.kvip_b200_last_error()
+
+
+def test_product_has_no_cpu_fallback():
+    from kvip_b200 import ops
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.topk(torch.zeros((1, 4096)), torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="missing"):
+        _lib.load_library(ROOT / "kvip_b200" / "no_such_library.so")
+    for path in (ROOT / "kvip_b200").rglob("*.py"):
+        text = path.read_text()
+        assert "import kvip_oracle" not in text and "oracle_c" not in text and "oracle/" not in text, (
+            f"{path} must not reach into the oracle")
+
+
+def test_query_inputs_packing_matches_reference_golden():
+    """QueryInputs.prepare / bind_positions on CPU tensors against the metadata the reference produced
+    (python/kvip/adapters/vllm/inputs.py:73-126; tests/adapters/test_inputs.py)."""
+    from kvip_b200 import QueryInputs
+    d = np.load(GOLDEN / "ingest_decode.npz")
+    inputs = QueryInputs(torch, 3, torch.device("cpu"), pin_memory=False, history=512)
+    inputs.prepare(tuple(int(x) for x in d["counts"]), query_starts=tuple(int(x) for x in d["starts"]),
+                   query_owners=tuple(int(x) for x in d["owners"]))
+    ends = inputs.bind_positions(torch.from_numpy(d["positions"]))
+    assert np.array_equal(inputs.metadata.numpy(), d["metadata"])
+    assert np.array_equal(ends.numpy().reshape(-1), d["query_ends"])
+    assert np.array_equal(inputs.block_table.numpy(), d["block_table"])
+    assert inputs.token_count == int(d["token_count"])
+    with pytest.raises(ValueError):
+        inputs.prepare((5,))
+    with pytest.raises(ValueError):
+        QueryInputs(torch, 1, torch.device("cpu"), index_heads=48)
+
+
+def test_query_inputs_generalised_slots():
+    from kvip_b200 import QueryInputs
+    inputs = QueryInputs(torch, 4, torch.device("cpu"), pin_memory=False, history=256, queries=2)
+    inputs.prepare((2, 1, 0, 2), query_owners=(3, 1, 0, 2))
+    assert inputs.gather_indices.tolist() == [0, 1, 2, 0, 0, 0, 3, 4]
+    assert inputs.query_valid.tolist() == [1, 1, 1, 0, 0, 0, 1, 1]
+    assert inputs.unpack_indices.tolist()[:5] == [0, 1, 2, 6, 7] and inputs.output_valid.tolist() == [1] * 5 + [0] * 3
+    assert inputs.block_table[:, 0].tolist() == [6, 2, 0, 4]
+
+
+def test_partition_requests_balances_cost():
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(65536, 131073, 256)
+    bins = sharding.partition_requests(lengths, 8)
+    assert sorted(i for b in bins for i in b) == list(range(256))
+    loads = [int(lengths[b].sum()) for b in bins]
+    assert max(loads) - min(loads) <= int(lengths.max())
+    assert sharding.partition_requests([5, 5, 5], 2) == [[0, 2], [1]]
+    assert sharding.partition_requests([], 4) == [[], [], [], []]
+
+
+def test_shard_bounds_cover_the_sequence():
+    for total, world in ((1 << 20, 8), (1000003, 8), (300, 4), (128, 2)):
+        spans = [sharding.shard_bounds(total, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all(begin % 128 == 0 for begin, _ in spans)
+
+
+_WORKER = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path[:0] = [{root!r}, {root!r} + "/oracle", {root!r} + "/tests"]
+import kvip_oracle as oracle
+from kvip_b200 import sharding
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+rng = np.random.default_rng(42)
+total = 5 * 4096 + 77
+whole = rng.integers(-40, 40, (2, total)).astype(np.float32)       # heavy ties across shard borders
+begin, end = sharding.shard_bounds(total, world, rank)
+def local_topk(scores, length, base):
+    idx = oracle.topk(scores.numpy(), np.full(2, length, np.int32), np.full(2, length, np.int32), base)
+    sc = np.where(idx >= 0, np.take_along_axis(whole, np.maximum(idx, 0), 1), 0).astype(np.float32)
+    return torch.from_numpy(idx), torch.from_numpy(sc)
+merge = lambda s, i: torch.from_numpy(oracle.topk_merge(s.numpy(), i.numpy()))
+local = torch.from_numpy(np.ascontiguousarray(whole[:, begin:end]))
+got = sharding.sequence_sharded_topk(local, end - begin, begin, local_topk=local_topk, merge=merge)
+expected = oracle.topk(whole, np.full(2, total, np.int32), np.full(2, total, np.int32))
+assert np.array_equal(got.numpy(), expected), "sharded TopK differs from the unsharded one"
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_sequence_shard_exchange_two_gloo_ranks(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER.format(root=str(ROOT)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29613", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    for proc in procs:
+        out, _ = proc.communicate(timeout=240)
+        assert proc.returncode == 0, out
+
+
+def test_reference_arm_prints_one_json_line():
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--workload", "decode_16k_b16",
+                          "--steps", "1", "--warmup", "3", "--cpu-requests-per-step", "1"], capture_output=True, text=True,
+                         timeout=300, check=True).stdout.strip().splitlines()
+    assert len(out) == 1
+    line = json.loads(out[0])
+    assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
