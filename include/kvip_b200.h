@@ -109,6 +109,8 @@ typedef struct KvipTopkArgs {
   const int32_t* query_ends;  /* [batch*queries] */
   int32_t* topk;              /* [rows, 2048] */
   float* topk_scores;         /* [rows, 2048] or NULL: score of each output */
+  uint32_t* histogram;        /* [rows, 4096] all-zero scratch (left all-zero) or NULL: with it the first
+                                 radix pass runs on the whole GPU in a kernel of its own */
   uint32_t rows, queries, scoreStride, base_index; /* base_index added to every output index */
 } KvipTopkArgs;
 uint32_t kvip_b200_topk(const KvipTopkArgs* args, void* stream);
@@ -315,8 +317,8 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
   uint32_t history, resident, options, max_events;      /* options word at byte 96 */
   uint64_t query_bitmaps, query_errors, update_bindings;
   uint64_t dense_shadow, packed_fetch;
-  uint64_t gather_out, topk_scores, li_status;
-  uint8_t reserved[88];
+  uint64_t gather_out, topk_scores, li_status, topk_histogram;
+  uint8_t reserved[80];
 } KvipWorkspace;
 
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,

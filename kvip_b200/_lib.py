@@ -43,7 +43,7 @@ LiArgs = _struct("LiArgs", (
         "batch", "queries", "heads", "pagesPerRequest", "keyRows", "scoreStride", "keyDtype", "weightDtype",
         "scoreMode", "ctas", "reserved0", "reserved1")])
 
-TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores"),
+TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")])
 
 MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"), [("rows", u32), ("shards", u32)])
@@ -102,7 +102,8 @@ class Workspace(ctypes.Structure):
         "context", "keys", "scales", "addresses", "logical_ids", "hot_valid", "flags", "events_src", "events_dst",
         "worker_status", "times")] + [(n, u32) for n in ("history", "resident", "options", "max_events")] + [
             (n, u64) for n in ("query_bitmaps", "query_errors", "update_bindings", "dense_shadow", "packed_fetch",
-                               "gather_out", "topk_scores", "li_status")] + [("reserved", ctypes.c_uint8 * 88)]
+                               "gather_out", "topk_scores", "li_status", "topk_histogram")] + [
+                                   ("reserved", ctypes.c_uint8 * 80)]
 
 
 _STAGES = {

@@ -133,19 +133,20 @@ __global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
     // 2. drop the touched slots from the list, keeping the order of the rest (in place: a chunk
     //    is fully in registers before anything is written, and writes never pass the reads)
     uint32_t kept_total = 0;
-    for (uint32_t start = 0; start < active; start += kLruThreads * 4u) {
-      int32_t v[4];
+    constexpr uint32_t kPer = 16;  // consecutive list entries per thread and chunk
+    for (uint32_t start = 0; start < active; start += kLruThreads * kPer) {
+      int32_t v[kPer];
       uint32_t keep = 0;
 #pragma unroll
-      for (uint32_t j = 0; j < 4; ++j) {
-        const uint32_t p = start + tid * 4u + j;
+      for (uint32_t j = 0; j < kPer; ++j) {
+        const uint32_t p = start + tid * kPer + j;
         v[j] = p < active ? order[p] : -1;
         if (v[j] >= 0 && !((bitmap[v[j] >> 5] >> (v[j] & 31)) & 1u)) keep |= 1u << j;
       }
       uint32_t total;
       uint32_t offset = kept_total + block_exclusive_scan(__popc(keep), scan, &total);
 #pragma unroll
-      for (uint32_t j = 0; j < 4; ++j)
+      for (uint32_t j = 0; j < kPer; ++j)
         if ((keep >> j) & 1u) order[offset++] = v[j];
       kept_total += total;
       __syncthreads();

@@ -245,31 +245,56 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
 
   if (warp == 0) {
     // ================= TMA producer =================
-    if (lane == 0) {
-      TileCursor cur(prefix, a.batch);
-      uint32_t stage = 0, phase = 0, loaded_q = 0;
-      int32_t bound = -1;
-      for (uint32_t t = tile_begin; t < tile_end; ++t) {
-        const uint32_t b = cur.seek(t);
-        if (static_cast<int32_t>(b) != bound) {
-          if (!mbar_wait(bar(2 * S + 5), (loaded_q & 1u) ^ 1u, abort_flag)) break;
-          const uint32_t rows = active_q[b] * H;
-          mbar_expect_tx(bar(2 * S + 4), rows * 128u * Cfg::kAtoms);
-          for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
-            for (uint32_t r = 0; r < rows; r += 32)
-              tma_load_2d(q_smem + atom * (kMaxN * 128u) + r * 128u, &query_map,
-                          static_cast<int32_t>(atom * 64u), static_cast<int32_t>(b * Q * H + r),
-                          bar(2 * S + 4));
-          ++loaded_q;
-          bound = static_cast<int32_t>(b);
+    // The whole warp stays in the loop: each lane looks up the page of one of the next 32 tiles (one
+    // coalesced read of the block table, issued a full group ahead), lane 0 issues the copies. A page
+    // lookup is a dependent global load; done per tile by the issuing thread it would serialise the
+    // pipeline on memory latency.
+    TileCursor lane_cursor(prefix, a.batch);
+    auto lookup = [&](uint32_t t, uint32_t* request) -> int32_t {
+      if (t >= tile_end) { *request = 0; return 0; }
+      const uint32_t b = lane_cursor.seek(t);
+      *request = b;
+      return a.block_table[static_cast<uint64_t>(b) * pages + (t - prefix[b])];
+    };
+    uint32_t stage = 0, phase = 0, loaded_q = 0, alive = 1;
+    int32_t bound = -1;
+    uint32_t next_request;
+    int32_t next_page = lookup(tile_begin + lane, &next_request);
+    for (uint32_t base = tile_begin; base < tile_end && alive; base += 32) {
+      const int32_t my_page = next_page;
+      const uint32_t my_request = next_request;
+      next_page = lookup(base + 32 + lane, &next_request);   // lands while this group is being issued
+      const uint32_t count = min(32u, tile_end - base);
+      for (uint32_t i = 0; i < count && alive; ++i) {
+        const int32_t page = __shfl_sync(0xffffffffu, my_page, i);
+        const uint32_t b = __shfl_sync(0xffffffffu, my_request, i);
+        if (lane == 0) {
+          if (static_cast<int32_t>(b) != bound) {
+            if (mbar_wait(bar(2 * S + 5), (loaded_q & 1u) ^ 1u, abort_flag)) {
+              const uint32_t rows = active_q[b] * H;
+              mbar_expect_tx(bar(2 * S + 4), rows * 128u * Cfg::kAtoms);
+              for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
+                for (uint32_t r = 0; r < rows; r += 32)
+                  tma_load_2d(q_smem + atom * (kMaxN * 128u) + r * 128u, &query_map,
+                              static_cast<int32_t>(atom * 64u), static_cast<int32_t>(b * Q * H + r),
+                              bar(2 * S + 4));
+              ++loaded_q;
+              bound = static_cast<int32_t>(b);
+            } else {
+              alive = 0;
+            }
+          }
+          if (alive && mbar_wait(bar(S + stage), phase ^ 1u, abort_flag)) {
+            mbar_expect_tx(bar(stage), Cfg::kTileBytes);
+            for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
+              tma_load_2d(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes, &key_map,
+                          static_cast<int32_t>(atom * 64u), page * static_cast<int32_t>(kBlockTokens), bar(stage));
+            if (++stage == S) { stage = 0; phase ^= 1u; }
+          } else {
+            alive = 0;
+          }
         }
-        if (!mbar_wait(bar(S + stage), phase ^ 1u, abort_flag)) break;
-        const int32_t page = a.block_table[static_cast<uint64_t>(b) * pages + (t - prefix[b])];
-        mbar_expect_tx(bar(stage), Cfg::kTileBytes);
-        for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
-          tma_load_2d(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes, &key_map,
-                      static_cast<int32_t>(atom * 64u), page * static_cast<int32_t>(kBlockTokens), bar(stage));
-        if (++stage == S) { stage = 0; phase ^= 1u; }
+        alive = __shfl_sync(0xffffffffu, alive, 0);
       }
     }
   } else if (warp == 1) {

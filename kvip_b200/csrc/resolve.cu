@@ -234,6 +234,7 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
 // routed to packed output rows (PrepareStagedQueryOutputs, staged_outputs.h:11-47).
 __global__ void __launch_bounds__(256) publish_outputs(const KvipResolveArgs a) {
   const uint32_t out_row = blockIdx.x, Q = a.queries;
+  const uint32_t k_begin = blockIdx.y * (kTop / 8u), k_end = k_begin + kTop / 8u;  // 8 CTAs per row
   int64_t src = out_row;
   bool live;
   if (a.unpack_indices && a.output_valid) {
@@ -248,14 +249,14 @@ __global__ void __launch_bounds__(256) publish_outputs(const KvipResolveArgs a) 
   const uint32_t b = static_cast<uint32_t>(src) / Q;
   if (live && a.row_status[b * 32u] != 0) live = false;
   if (!live) {
-    for (uint32_t k = threadIdx.x; k < kTop; k += 256) { logical[k] = -1; slots[k] = -1; }
+    for (uint32_t k = k_begin + threadIdx.x; k < k_end; k += 256) { logical[k] = -1; slots[k] = -1; }
     return;
   }
   const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
   const int64_t* ids = a.logical_ids + static_cast<uint64_t>(owner) * a.history;
   const int32_t* selected = a.topk + static_cast<uint64_t>(src) * kTop;
   const int32_t* loc = a.locations + static_cast<uint64_t>(src) * kTop;
-  for (uint32_t k = threadIdx.x; k < kTop; k += 256) {
+  for (uint32_t k = k_begin + threadIdx.x; k < k_end; k += 256) {
     const int32_t token = selected[k];
     logical[k] = token < 0 ? -1 : static_cast<int32_t>(ids[token]);
     slots[k] = loc[k];
@@ -277,7 +278,7 @@ uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream) {
   count_launch();
   if (uint32_t bad = check_launch("resolve_requests")) return bad;
   if (a.logical_output && a.slot_output) {
-    publish_outputs<<<a.batch * a.queries, 256, 0, stream>>>(a);
+    publish_outputs<<<dim3(a.batch * a.queries, 8), 256, 0, stream>>>(a);
     count_launch();
     return check_launch("publish_outputs");
   }

@@ -33,10 +33,46 @@ __device__ __forceinline__ void hist_add(uint32_t* hist, bool valid, uint32_t bi
   }
 }
 
+// First radix pass spread over the whole GPU: `segments` CTAs per row add their slice's 12-bit
+// histogram to the row's histogram in global memory (the selecting CTA clears it again after use).
+constexpr uint32_t kHistThreads = 256;
+
+__global__ void __launch_bounds__(kHistThreads) topk_histogram(const KvipTopkArgs a) {
+  __shared__ uint32_t hist[4096];
+  const uint32_t row = blockIdx.y, tid = threadIdx.x;
+  int32_t valid_len = min(a.key_lengths[row / a.queries], a.query_ends[row]);
+  valid_len = min(valid_len, static_cast<int32_t>(a.scoreStride));
+  if (valid_len <= static_cast<int32_t>(kTop)) return;
+  const uint32_t L = static_cast<uint32_t>(valid_len), vec_count = (L + 3u) >> 2;
+  const uint32_t per = ((vec_count + gridDim.x - 1u) / gridDim.x + kHistThreads - 1u) / kHistThreads * kHistThreads;
+  const uint32_t begin = blockIdx.x * per, end = min(begin + per, vec_count);
+  if (begin >= end) return;
+  for (uint32_t i = tid; i < 4096; i += kHistThreads) hist[i] = 0;
+  __syncthreads();
+  const float4* row4 = reinterpret_cast<const float4*>(a.scores + static_cast<uint64_t>(row) * a.scoreStride);
+  for (uint32_t v0 = begin; v0 < end; v0 += kHistThreads) {  // `per` is a multiple of the block: warps stay converged
+    const uint32_t v = v0 + tid;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (v < end) x = row4[v];
+    const float e[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+      hist_add(hist, v < end && (v * 4u + j) < L, sortable_key(e[j]) >> 20);
+  }
+  __syncthreads();
+  uint32_t* out = a.histogram + static_cast<uint64_t>(row) * 4096u;
+  for (uint32_t i = tid; i < 4096; i += kHistThreads)
+    if (hist[i]) atomicAdd(out + i, hist[i]);
+}
+
+constexpr uint32_t kCandidates = 8192;  // shared-memory candidates of the threshold bin
+
 __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
   __shared__ uint32_t hist[4096];
   __shared__ uint32_t scan_scratch[33];
   __shared__ uint32_t found[2];
+  __shared__ uint32_t cand_count;
+  extern __shared__ uint32_t cand_keys[];  // [kCandidates] when a histogram is supplied
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
   const uint32_t b = row / a.queries;
   int32_t valid_len = min(a.key_lengths[b], a.query_ends[row]);
@@ -57,15 +93,31 @@ __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
   const float4* row4 = reinterpret_cast<const float4*>(scores);
 
   uint32_t prefix = 0, prefix_mask = 0, remaining = kTop;
+  bool in_smem = false;  // passes 2 and 3 run over the shared-memory candidates instead of the row
 #pragma unroll 1
   for (uint32_t pass = 0; pass < 3; ++pass) {
     const uint32_t bits = pass == 2 ? 8u : 12u;
     const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
     const uint32_t bins = 1u << bits;
-    for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
+    if (pass == 0 && a.histogram) {
+      uint32_t* global_hist = a.histogram + static_cast<uint64_t>(row) * 4096u;
+      for (uint32_t i = tid; i < bins; i += kThreads) { hist[i] = global_hist[i]; global_hist[i] = 0; }
+      if (tid == 0) cand_count = 0;
+    } else {
+      for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
+    }
     __syncthreads();
     // every lane of a warp runs the same number of iterations (hist_add uses warp votes)
-    const uint32_t rounds = (vec_count + kThreads - 1) / kThreads;
+    const uint32_t rounds = (pass == 0 && a.histogram) ? 0u : (in_smem ? (cand_count + kThreads - 1) / kThreads
+                                                                       : (vec_count + kThreads - 1) / kThreads);
+    if (in_smem) {
+      const uint32_t n = cand_count;
+      for (uint32_t r = 0; r < rounds; ++r) {
+        const uint32_t i = r * kThreads + tid;
+        const uint32_t key = i < n ? cand_keys[i] : 0u;
+        hist_add(hist, i < n && (key & prefix_mask) == prefix, (key >> shift) & (bins - 1u));
+      }
+    } else
     for (uint32_t r = 0; r < rounds; ++r) {
       const uint32_t v = r * kThreads + tid;
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -104,6 +156,27 @@ __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
     prefix_mask |= (bins - 1u) << shift;
     remaining = found[1];
     __syncthreads();
+    if (pass == 0 && a.histogram) {
+      // One cheap pass collects the threshold bin's keys; if they fit, the remaining 20 bits are
+      // resolved in shared memory. (An overfull bin, e.g. a constant row, keeps the global passes.)
+      const uint32_t want = hist[prefix >> 20];
+      if (want <= kCandidates) {
+        const uint32_t rounds_f = (vec_count + kThreads - 1) / kThreads;
+        for (uint32_t r = 0; r < rounds_f; ++r) {
+          const uint32_t v = r * kThreads + tid;
+          if (v >= vec_count) continue;
+          const float4 x = row4[v];
+          const float e[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t key = sortable_key(e[j]);
+            if ((v * 4u + j) < L && (key & prefix_mask) == prefix) cand_keys[atomicAdd(&cand_count, 1u)] = key;
+          }
+        }
+        in_smem = true;
+      }
+      __syncthreads();
+    }
   }
   const uint32_t kth = prefix;             // exact key of the 2048th largest element
   const uint32_t need_eq = remaining;      // how many == kth positions are taken
@@ -205,7 +278,16 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a, ui
 }  // namespace
 
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream) {
-  topk_select<<<a.rows, kThreads, 0, stream>>>(a);
+  size_t smem = 0;
+  if (a.histogram) {
+    uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
+    segments = segments < 1u ? 1u : (segments > 32u ? 32u : segments);
+    topk_histogram<<<dim3(segments, a.rows), kHistThreads, 0, stream>>>(a);
+    count_launch();
+    if (uint32_t bad = check_launch("topk_histogram")) return bad;
+    smem = kCandidates * sizeof(uint32_t);
+  }
+  topk_select<<<a.rows, kThreads, smem, stream>>>(a);
   count_launch();
   return check_launch("topk_select");
 }

@@ -67,16 +67,18 @@ def oracle_step(p, before, scores):
     return state, topk, logical_out, slot_out, gathered, reads
 
 
-def li_tolerance_check(p, scores):
-    """Device LI scores against the NumPy golden formula, on the valid prefix of every row."""
-    inputs, s = p.workspace.inputs, p.storage
+def li_tolerance_check(p, scores, before):
+    """Device LI scores against the NumPy golden formula, on the valid prefix of every row. Keys and scales
+    come from the snapshot taken before the step: the step itself permutes the Index rows."""
+    inputs = p.workspace.inputs
     bf16 = p.key_dtype == "bf16"
     as_np = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else (  # noqa: E731
         t.cpu().view(torch.uint8).numpy() if t.element_size() == 1 else t.cpu().numpy())
     query_ends = inputs.query_ends.cpu().numpy().reshape(p.batch, p.queries)
     expected = oracle.li_scores(
-        as_np(inputs.query), as_np(s.keys).reshape(-1, 128), as_np(inputs.weights),
-        None if bf16 else inputs.scale.cpu().numpy(), None if bf16 else s.scales.cpu().numpy().reshape(-1),
+        as_np(inputs.query), before["keys"].view(np.uint16 if bf16 else np.uint8).reshape(-1, 128),
+        as_np(inputs.weights), None if bf16 else inputs.scale.cpu().numpy(),
+        None if bf16 else before["scales"].reshape(-1),
         p.workspace.key_lengths.cpu().numpy(), query_ends, inputs.block_table.cpu().numpy(), key_is_bf16=bf16,
         weight_is_bf16=inputs.weights.dtype == torch.bfloat16)
     rtol = 2e-3 if bf16 else 1e-2
@@ -119,7 +121,7 @@ def test_forward_matches_oracle_over_steps(config, device):
             assert int(p.forward.li_status.item()) == 0
             assert (p.update.status.cpu().numpy() == 0).all() and (p.rotating.row_status[:, 0].cpu().numpy() == 0).all()
             scores = p.workspace.scores.cpu().numpy()
-            li_tolerance_check(p, scores)
+            li_tolerance_check(p, scores, before)
             state, topk, logical_out, slot_out, gathered, reads = oracle_step(p, before, scores)
             total_reads.append(reads)
             assert np.array_equal(p.workspace.topk.cpu().numpy(), topk)

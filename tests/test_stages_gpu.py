@@ -103,9 +103,16 @@ def test_li_exact_binary_fraction_fixture(device):
 def _topk_check(scores_np, key_lengths, query_ends, device, base_index=0):
     scores = torch.from_numpy(scores_np).to(device)
     out_scores = torch.zeros((scores.shape[0], TOPK), dtype=torch.float32, device=device)
-    got = ops.topk(scores, torch.from_numpy(key_lengths).to(device), torch.from_numpy(query_ends).to(device),
-                   out_scores=out_scores, base_index=base_index)
-    torch.cuda.synchronize()
+    lengths_t, ends_t = torch.from_numpy(key_lengths).to(device), torch.from_numpy(query_ends).to(device)
+    got = ops.topk(scores, lengths_t, ends_t, out_scores=out_scores, base_index=base_index)
+    # second path: first radix pass in its own kernel + shared-memory candidates; run twice to prove the
+    # histogram scratch is handed back all-zero
+    histogram = torch.zeros((scores.shape[0], 4096), dtype=torch.int32, device=device)
+    for _ in range(2):
+        split = ops.topk(scores, lengths_t, ends_t, base_index=base_index, histogram=histogram)
+        torch.cuda.synchronize()
+        assert torch.equal(split, got)
+        assert int(histogram.abs().sum()) == 0
     expected = oracle_c.topk(scores_np, key_lengths, query_ends, base_index)
     got = got.cpu().numpy()
     assert np.array_equal(got, expected)
