@@ -14,8 +14,9 @@
 //   * persistent CTAs (one per SM) walk a flat list of (request, page) tiles, so a
 //     request's keys and scales are streamed from HBM exactly once for all of its
 //     query rows;
-//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-5 =
-//     epilogue; key stages and two accumulator buffers are handed over with mbarriers;
+//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-9 = two
+//     epilogue groups that take alternate tiles; key stages and a ring of up to eight
+//     accumulator buffers in tensor memory are handed over with mbarriers;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
 //     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
 //     is released and the kernel returns.
@@ -27,7 +28,8 @@
 namespace kvip {
 namespace {
 
-constexpr uint32_t kLiThreads = 192;
+constexpr uint32_t kLiThreads = 320;  // TMA warp, MMA warp, two epilogue groups of four warps
+constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (512 columns / stride)
 constexpr uint32_t kMaxBatch = 1024;
 constexpr uint32_t kMaxN = 256;            // query slots * heads
 constexpr uint32_t kAtomBytes = 128 * 128; // one 128-row x 128-byte swizzle atom
@@ -39,7 +41,7 @@ template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kStages = kBf16 ? 4 : 8;
   static constexpr uint32_t kQBytes = kMaxN * 128 * kAtoms;
   static constexpr uint32_t kSmemBytes =
-      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 4 * kMaxN * 4 /*W per epilogue warp*/ +
+      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 8 * kMaxN * 4 /*W per epilogue warp*/ +
       (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 1024 /*barriers*/;
 };
 
@@ -178,18 +180,22 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t key_smem = base + 1024u;
   const uint32_t q_smem = key_smem + Cfg::kStages * Cfg::kTileBytes;
   float* w_smem = reinterpret_cast<float*>(smem + 1024u + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
-  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kMaxN);
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 8 * kMaxN);
   uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
-  // barrier map: [0,S) full, [S,2S) empty, 2S..2S+1 tmem_full, 2S+2..2S+3 tmem_empty,
-  // 2S+4 q_full, 2S+5 q_empty; then the tmem base word and the abort flag.
+  // barrier map: [0,S) full, [S,2S) empty, 2S q_full, 2S+1 q_empty, then kMaxAcc tmem_full and kMaxAcc
+  // tmem_empty; then the tmem base word and the abort flag.
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
   constexpr uint32_t S = Cfg::kStages;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 6);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 + 2 * kMaxAcc);
+  constexpr uint32_t kQFull = 2 * S, kQEmpty = 2 * S + 1, kAccFull = 2 * S + 2, kAccEmpty = 2 * S + 2 + kMaxAcc;
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t H = a.heads, Q = a.queries, pages = a.pagesPerRequest;
+  // accumulator ring in tensor memory: stride = columns one tile can need, rounded to a power of two
+  const uint32_t acc_stride = Q * H <= 32u ? 32u : (Q * H <= 64u ? 64u : (Q * H <= 128u ? 128u : 256u));
+  const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);
 
   // ---- per-CTA schedule: tiles per request -> prefix sums (warp 0) -------------------
   if (warp == 0) {
@@ -221,9 +227,8 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   }
   if (threadIdx.x == 64) {
     for (uint32_t i = 0; i < S; ++i) { mbar_init(bar(i), 1); mbar_init(bar(S + i), 1); }
-    mbar_init(bar(2 * S + 0), 1); mbar_init(bar(2 * S + 1), 1);
-    mbar_init(bar(2 * S + 2), 128); mbar_init(bar(2 * S + 3), 128);
-    mbar_init(bar(2 * S + 4), 1); mbar_init(bar(2 * S + 5), 1);
+    mbar_init(bar(kQFull), 1); mbar_init(bar(kQEmpty), 1);
+    for (uint32_t i = 0; i < kMaxAcc; ++i) { mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -270,14 +275,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         const uint32_t b = __shfl_sync(0xffffffffu, my_request, i);
         if (lane == 0) {
           if (static_cast<int32_t>(b) != bound) {
-            if (mbar_wait(bar(2 * S + 5), (loaded_q & 1u) ^ 1u, abort_flag)) {
+            if (mbar_wait(bar(kQEmpty), (loaded_q & 1u) ^ 1u, abort_flag)) {
               const uint32_t rows = active_q[b] * H;
-              mbar_expect_tx(bar(2 * S + 4), rows * 128u * Cfg::kAtoms);
+              mbar_expect_tx(bar(kQFull), rows * 128u * Cfg::kAtoms);
               for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
                 for (uint32_t r = 0; r < rows; r += 32)
                   tma_load_2d(q_smem + atom * (kMaxN * 128u) + r * 128u, &query_map,
                               static_cast<int32_t>(atom * 64u), static_cast<int32_t>(b * Q * H + r),
-                              bar(2 * S + 4));
+                              bar(kQFull));
               ++loaded_q;
               bound = static_cast<int32_t>(b);
             } else {
@@ -301,12 +306,12 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     // ================= MMA issuer =================
     if (lane == 0) {
       TileCursor cur(prefix, a.batch);
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, seen_q = 0, idesc = 0;
+      uint32_t stage = 0, phase = 0, seen_q = 0, idesc = 0;
       int32_t bound = -1;
       for (uint32_t t = tile_begin; t < tile_end; ++t) {
         const uint32_t b = cur.seek(t);
         if (static_cast<int32_t>(b) != bound) {
-          if (!mbar_wait(bar(2 * S + 4), seen_q & 1u, abort_flag)) break;
+          if (!mbar_wait(bar(kQFull), seen_q & 1u, abort_flag)) break;
           ++seen_q;
           bound = static_cast<int32_t>(b);
           const uint32_t n = active_q[b] * H;
@@ -314,9 +319,10 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
           idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
         }
         if (!mbar_wait(bar(stage), phase, abort_flag)) break;
-        if (!mbar_wait(bar(2 * S + 2 + acc), acc_phase ^ 1u, abort_flag)) break;
+        const uint32_t local = t - tile_begin, acc = local % acc_count, acc_phase = (local / acc_count) & 1u;
+        if (!mbar_wait(bar(kAccEmpty + acc), acc_phase ^ 1u, abort_flag)) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kMaxN;
+        const uint32_t d_tmem = tmem_base + acc * acc_stride;
 #pragma unroll
         for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
           const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
@@ -326,23 +332,25 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
             tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
         }
         tcgen05_commit(bar(S + stage));        // key stage free once these MMAs retire
-        tcgen05_commit(bar(2 * S + acc));      // accumulator ready for the epilogue
+        tcgen05_commit(bar(kAccFull + acc));   // accumulator ready for the epilogue
         const bool last_of_request = (t + 1 == tile_end) || (t + 1 >= prefix[b + 1]);
-        if (last_of_request) tcgen05_commit(bar(2 * S + 5));  // query operand may be replaced
+        if (last_of_request) tcgen05_commit(bar(kQEmpty));  // query operand may be replaced
         if (++stage == S) { stage = 0; phase ^= 1u; }
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else {
-    // ================= epilogue: 4 warps, one token row per thread =================
+    // ================= epilogue: two groups of 4 warps, one token row per thread =================
+    // Group g reduces the tiles with (t - tile_begin) % 2 == g, so two tiles are in flight per SM and
+    // the tensor-memory load latency of one hides behind the arithmetic of the other.
+    const uint32_t group = (warp - 2u) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
     const uint32_t row = quad * 32u + lane;       // token row inside the page
     float* w_warp = w_smem + (warp - 2u) * kMaxN;  // private copy: no cross-warp barrier needed
     TileCursor cur(prefix, a.batch), ahead(prefix, a.batch);
-    uint32_t acc = 0, acc_phase = 0, live_mask = 0;
+    uint32_t live_mask = 0;
     int32_t bound = -1;
     // The page index and the key scale of a tile are two dependent global loads. They are issued two
-    // and one tile ahead, so their latency is hidden behind the tile being reduced.
+    // and one of this group's tiles ahead, so their latency is hidden behind the tile being reduced.
     auto page_of = [&](uint32_t t) -> int32_t {
       if (t >= tile_end) return 0;
       const uint32_t b = ahead.seek(t);
@@ -352,14 +360,15 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (t >= tile_end || !a.key_scale) return 1.0f;
       return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
     };
-    int32_t page_next = page_of(tile_begin);
-    float kscale = scale_of(tile_begin, page_next);
-    page_next = page_of(tile_begin + 1);
-    for (uint32_t t = tile_begin; t < tile_end; ++t) {
+    const uint32_t first = tile_begin + group;
+    int32_t page_next = page_of(first);
+    float kscale = scale_of(first, page_next);
+    page_next = page_of(first + 2);
+    for (uint32_t t = first; t < tile_end; t += 2) {
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
-      const float kscale_next = scale_of(t + 1, page_next);   // consumed next iteration
-      page_next = page_of(t + 2);
+      const float kscale_next = scale_of(t + 2, page_next);   // consumed next iteration
+      page_next = page_of(t + 4);
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
         for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
@@ -369,10 +378,11 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         bound = static_cast<int32_t>(b);
       }
       const uint32_t token = (t - prefix[b]) * kBlockTokens + row;
+      const uint32_t local = t - tile_begin, acc = local % acc_count, acc_phase = (local / acc_count) & 1u;
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(2 * S + acc), acc_phase, abort_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(kAccFull + acc), acc_phase, abort_flag))) break;
       tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * kMaxN;
+      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
       for (uint32_t q = 0; q < nq; ++q) {
         float even = 0.f, odd = 0.f;
         if (H == 64) {
@@ -418,8 +428,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         }
       }
       tcgen05_fence_before();
-      mbar_arrive(bar(2 * S + 2 + acc));
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      mbar_arrive(bar(kAccEmpty + acc));
       kscale = kscale_next;
     }
   }

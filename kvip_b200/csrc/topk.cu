@@ -286,6 +286,12 @@ uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream) {
     count_launch();
     if (uint32_t bad = check_launch("topk_histogram")) return bad;
     smem = kCandidates * sizeof(uint32_t);
+    static bool configured = false;  // static + dynamic shared memory exceeds the 48 KiB default
+    if (!configured) {
+      if (cudaFuncSetAttribute(topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+        return check_launch("topk_select attribute");
+      configured = true;
+    }
   }
   topk_select<<<a.rows, kThreads, smem, stream>>>(a);
   count_launch();
