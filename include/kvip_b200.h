@@ -115,6 +115,17 @@ typedef struct KvipTopkArgs {
 } KvipTopkArgs;
 uint32_t kvip_b200_topk(const KvipTopkArgs* args, void* stream);
 
+/* Same selection for callers that cannot allocate device memory (for instance a serving process whose
+ * KV-cache pool already owns all free HBM, or a decode-loop plugin that must not stall the device on an
+ * allocation). No counterpart in the reference. `histogram` of the argument struct is ignored: the
+ * [rows, 4096] scratch is a 4 MiB array inside the library image, held by every GPU that loads the
+ * library until the process exits. Limit: rows <= 256 (KVIP_BAD_ARGUMENT with a message beyond that).
+ * The call allocates nothing; it clears the rows of the scratch it is about to use on `stream` first.
+ * The first call on a device looks up the scratch address (a one-time set-up): make that first call
+ * before any stream capture. All calls share the one array: calls that overlap on the GPU (different
+ * streams, or different threads) race on it - keep them on one stream. */
+uint32_t kvip_b200_topk_static(const KvipTopkArgs* args, void* stream);
+
 /* Merge of sequence-sharded candidates: rows x shards x 2048 (score,index) pairs ->
  * global top-2048 under the same total order. New on B200 (no reference counterpart;
  * precedent: the on-chip sequence split, common/lifetch/sequence_schedule.h:9-37). */

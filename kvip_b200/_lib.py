@@ -108,6 +108,7 @@ class Workspace(ctypes.Structure):
 
 _STAGES = {
     "kvip_b200_li_score": LiArgs, "kvip_b200_li_score_simt": LiArgs, "kvip_b200_topk": TopkArgs,
+    "kvip_b200_topk_static": TopkArgs,
     "kvip_b200_topk_merge": MergeArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs,

@@ -308,6 +308,46 @@ extern "C" uint32_t kvip_b200_topk(const KvipTopkArgs* a, void* stream) {
   return kvip::launch_topk(*a, static_cast<cudaStream_t>(stream));
 }
 
+// ---- TopK for callers that cannot allocate --------------------------------------------------------
+// The split TopK needs a [rows, 4096] histogram scratch. Some hosts of this library have nowhere to get
+// it from: a serving process that handed every free byte of HBM to its KV-cache pool at start-up (a later
+// cudaMalloc fails or fragments the pool), or a decode-loop plugin that is forbidden to allocate because
+// an allocation would stall the device it is feeding. For them the scratch lives in the library's own
+// image: a fixed 4 MiB array that every GPU loading the library holds until the process exits.
+#define KVIP_TOPK_STATIC_ROWS 256u
+static __device__ __align__(256) uint32_t g_static_histogram[KVIP_TOPK_STATIC_ROWS * 4096u];
+
+extern "C" uint32_t kvip_b200_topk_static(const KvipTopkArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->scores && a->key_lengths && a->query_ends && a->topk, "topk_static: null pointer");
+  KVIP_REQUIRE(a->rows >= 1 && a->queries >= 1 && a->rows % a->queries == 0, "topk_static: rows must be batch*queries");
+  KVIP_REQUIRE(a->rows <= KVIP_TOPK_STATIC_ROWS,
+               "topk_static: more than 256 score rows do not fit the built-in scratch; split the call or use "
+               "kvip_b200_topk with a caller-provided histogram");
+  KVIP_REQUIRE(a->scoreStride % 4 == 0 && (reinterpret_cast<uintptr_t>(a->scores) & 15u) == 0,
+               "topk_static: score rows must be 16-byte aligned");
+  // In host code `g_static_histogram` is only a stand-in for the symbol; the address kernels can use is
+  // looked up once per device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static uint32_t* scratch_of_device[kMaxDevices] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return kvip::check_launch("topk_static: cudaGetDevice");
+  if (!scratch_of_device[device]) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_static_histogram) != cudaSuccess || !address)
+      return kvip::check_launch("topk_static: cudaGetSymbolAddress");
+    scratch_of_device[device] = static_cast<uint32_t*>(address);
+  }
+  uint32_t* scratch = scratch_of_device[device];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // every call shares the array and finds what the last call left: the rows used now must start at zero
+  if (cudaMemsetAsync(scratch, 0, static_cast<size_t>(a->rows) * 4096u * sizeof(uint32_t), s) != cudaSuccess)
+    return kvip::check_launch("topk_static: clearing the scratch");
+  KvipTopkArgs with_scratch = *a;
+  with_scratch.histogram = scratch;
+  return kvip::launch_topk(with_scratch, s);
+}
+
 extern "C" uint32_t kvip_b200_topk_merge(const KvipMergeArgs* a, void* stream) {
   KVIP_REQUIRE(a && a->cand_scores && a->cand_index && a->topk, "topk_merge: null pointer");
   KVIP_REQUIRE(a->rows >= 1 && a->shards >= 1 && a->shards <= 8, "topk_merge: 1..8 shards");
