@@ -189,14 +189,21 @@ def run_ours(args):
         ga = lambda: ops.gather(p.pool_hbm, p.update.slot_output.view(-1, 2048), p.gather_out,  # noqa: E731
                                 queries=p.queries, output_stride=p.output_stride, token_bytes=p.token_bytes,
                                 row_owners=inputs.row_owners)
-        for name, fn in (("li_score", li), ("topk", tk), ("gather", ga)):
+        split_scratch = torch.zeros((p.batch * p.queries, _lib.TOPK_SPLIT_WORDS), dtype=torch.int32, device=device)
+        tk_hist = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048),  # noqa: E731
+                                   histogram=p.forward.topk_histogram)
+        tk_split = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048),  # noqa: E731
+                                    split_scratch=split_scratch)
+        lru = lambda: p.lru.commit(p.update.slot_output.view(p.batch, -1))  # noqa: E731
+        for name, fn in (("li_score", li), ("topk_one_kernel", tk), ("topk", tk_hist), ("topk_all_passes_split", tk_split),
+                         ("gather", ga), ("lru_commit", lru)):
             for _ in range(2):
                 fn()
             stream.synchronize()
             stages[name] = time_region(torch, stream, fn, args.steps) / args.steps
         stages["step_graph"] = elapsed / args.steps
-        stages["resolve_exchange_fetch_lru"] = max(0.0, stages["step_graph"] - stages["li_score"] - stages["topk"]
-                                                   - stages["gather"])
+        stages["resolve_outputs_exchange_fetch"] = max(0.0, stages["step_graph"] - stages["li_score"] - stages["topk"]
+                                                       - stages["gather"] - stages["lru_commit"])
 
         # ---- end to end: host inputs in, host outputs out, through the public objects ----------------
         heads, T = p.heads, tokens
@@ -226,6 +233,10 @@ def run_ours(args):
         barrier()
         h2d = sum(x.numel() * x.element_size() for x in (host_q, host_w, host_s, host_pos))
         d2h = host_out.numel() * host_out.element_size()
+
+        miss_path = None
+        if world == 1 and not args.no_miss_path:
+            miss_path = measure_miss_path(torch, ops, p, stream, args)
 
     worst = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
     if world > 1:
@@ -260,6 +271,8 @@ def run_ours(args):
                   "cold_host_link_gbs": cold_reads * p.token_bytes / cold_s / 1e9, "steady_reads_per_step": steady_reads},
         "clocks": clocks.result,
     }
+    if miss_path:
+        line["miss_path"] = miss_path
     if rank == 0:
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, args.cpu_requests)
@@ -267,6 +280,55 @@ def run_ours(args):
     p.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_miss_path(torch, ops, p, stream, args):
+    """Steps whose selections drift (AR(1) queries), so that part of every selection misses the resident pool
+    and is fetched from the pinned host pool, with the Index update of one new bf16 row per token in the
+    step; plus the host link alone (the fetch kernel over synthetic descriptors)."""
+    steps, warm = 8, 4
+    p.make_query_bank(steps + warm, correlation=0.95)
+    for i in range(warm):
+        p.load_queries(i)
+        p.step(ingest=True)
+    stream.synchronize()
+    misses, start, stop = [], torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    counts = torch.zeros(steps, dtype=torch.int64, device=p.device)
+    start.record(stream)
+    for i in range(steps):
+        p.load_queries(warm + i)
+        p.step(ingest=True)
+        counts[i] = p.rotating.query_counts[:, 4].sum()
+    stop.record(stream)
+    stop.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3
+    misses = counts.tolist()
+    status = int(p.update.status.max().item()) | int(p.rotating.row_status[:, 2].max().item())
+    out = {"steps": steps, "ms_per_step": seconds / steps * 1e3, "tokens_per_s": p.query_tokens() * steps / seconds,
+           "misses_per_step": sum(misses) / steps, "miss_fraction": sum(misses) / steps / (p.query_tokens() * 2048),
+           "miss_bytes_per_step": sum(misses) / steps * p.token_bytes, "status": status,
+           "query_drift": "AR(1), rho = 0.95, new bf16 k_I row per token quantised to FP8"}
+    if p.host_pool is not None:
+        # host link alone: 16384 rows per request from distinct host rows into the resident slots
+        rows = min(8192, p.resident)
+        state = ops.ResolveState(p.batch, p.queries, p.device)
+        gen = torch.Generator(device=p.device)
+        gen.manual_seed(5)
+        tokens = torch.stack([torch.randperm(p.history, generator=gen, device=p.device)[:rows] for _ in range(p.batch)])
+        owners = p.workspace.inputs.row_owners.long()[:, None]
+        state.fetch_sources[:, :rows] = (owners * p.history + tokens) * p.token_bytes
+        state.fetch_destinations[:, :rows] = (owners * p.output_stride + torch.arange(rows, device=p.device)[None, :]).int()
+        state.query_counts[:, 4] = rows
+        valid = torch.zeros_like(p.storage.hot_valid)
+        fetch = lambda: ops.fetch(p.host_pool.device_pointer, p.host_pool.nbytes, p.pool_hbm, valid, state,  # noqa: E731
+                                  resident=p.resident, output_stride=p.output_stride, token_bytes=p.token_bytes,
+                                  row_owners=p.workspace.inputs.row_owners)
+        fetch()
+        stream.synchronize()
+        t = time_region(torch, stream, fetch, 3) / 3
+        out["host_link"] = {"rows": rows * p.batch, "bytes": rows * p.batch * p.token_bytes, "ms": t * 1e3,
+                            "gbs": rows * p.batch * p.token_bytes / t / 1e9}
+    return out
 
 
 def cpu_step(cfg, requests, seed=0, budget_s=1e9):
@@ -357,6 +419,7 @@ def main():
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")
     parser.add_argument("--device-source", action="store_true", help="serve misses from HBM instead of the host pool")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--no-miss-path", action="store_true", help="skip the drifting-query / host-link measurement")
     parser.add_argument("--cpu-requests", type=int, default=4096, help="upper bound; the leg stops after ~15 s")
     parser.add_argument("--cpu-requests-per-step", type=int, default=2)
     args = parser.parse_args()

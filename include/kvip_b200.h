@@ -32,6 +32,7 @@ extern "C" {
 #define KVIP_CHANGE_CAPACITY 10240u  /* common/lifetch/cache_metadata.h:3 */
 #define KVIP_BLOCK_TOKENS 128u       /* paged Index cache block */
 #define KVIP_INDEX_WIDTH 128u        /* d_I */
+#define KVIP_TOPK_SPLIT_WORDS 20544u /* u32 words of TopK scratch per score row for the multi-CTA path */
 #define KVIP_BAD_ARGUMENT 100000u
 #define KVIP_CUDA_ERROR_BASE 200000u
 
@@ -112,6 +113,9 @@ typedef struct KvipTopkArgs {
   uint32_t* histogram;        /* [rows, 4096] all-zero scratch (left all-zero) or NULL: with it the first
                                  radix pass runs on the whole GPU in a kernel of its own */
   uint32_t rows, queries, scoreStride, base_index; /* base_index added to every output index */
+  uint32_t* split_scratch;    /* [rows, KVIP_TOPK_SPLIT_WORDS] scratch or NULL: with it every pass runs on several
+                                 CTAs per row (takes precedence over `histogram`). The first 4160 words of each
+                                 row must be zero on entry and are zero again on return. */
 } KvipTopkArgs;
 uint32_t kvip_b200_topk(const KvipTopkArgs* args, void* stream);
 
@@ -328,8 +332,8 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
   uint32_t history, resident, options, max_events;      /* options word at byte 96 */
   uint64_t query_bitmaps, query_errors, update_bindings;
   uint64_t dense_shadow, packed_fetch;
-  uint64_t gather_out, topk_scores, li_status, topk_histogram;
-  uint8_t reserved[80];
+  uint64_t gather_out, topk_scores, li_status, topk_histogram, topk_split;
+  uint8_t reserved[72];
 } KvipWorkspace;
 
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,

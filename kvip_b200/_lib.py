@@ -10,6 +10,7 @@ u32, i32, u64, i64, vp, f32 = (ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64,
                                ctypes.c_void_p, ctypes.c_float)
 
 TOPK, SLOTS, LRU_SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS, MAX_QUERIES = 2048, 8192, 2048, 10240, 128, 4
+TOPK_SPLIT_WORDS = 20544
 BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
 WEIGHT_BF16, WEIGHT_FP32 = 0, 1
@@ -44,7 +45,7 @@ LiArgs = _struct("LiArgs", (
         "scoreMode", "ctas", "reserved0", "reserved1")])
 
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
-                   [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")])
+                   [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])
 
 MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"), [("rows", u32), ("shards", u32)])
 
@@ -102,8 +103,8 @@ class Workspace(ctypes.Structure):
         "context", "keys", "scales", "addresses", "logical_ids", "hot_valid", "flags", "events_src", "events_dst",
         "worker_status", "times")] + [(n, u32) for n in ("history", "resident", "options", "max_events")] + [
             (n, u64) for n in ("query_bitmaps", "query_errors", "update_bindings", "dense_shadow", "packed_fetch",
-                               "gather_out", "topk_scores", "li_status", "topk_histogram")] + [
-                                   ("reserved", ctypes.c_uint8 * 80)]
+                               "gather_out", "topk_scores", "li_status", "topk_histogram", "topk_split")] + [
+                                   ("reserved", ctypes.c_uint8 * 72)]
 
 
 _STAGES = {

@@ -129,6 +129,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   tk.scores = li.scores; tk.key_lengths = li.key_lengths; tk.query_ends = li.query_ends;
   tk.topk = ptr<int32_t>(bind[9]); tk.topk_scores = ptr<float>(ws->topk_scores);
   tk.histogram = ptr<uint32_t>(ws->topk_histogram);
+  tk.split_scratch = ptr<uint32_t>(ws->topk_split);
   tk.rows = s.batch * s.queries; tk.queries = s.queries; tk.scoreStride = s.scoreStride; tk.base_index = 0;
   KVIP_REQUIRE(tk.topk, "forward: the TopK output is unbound");
   if ((rc = launch_topk(tk, stream))) return rc;

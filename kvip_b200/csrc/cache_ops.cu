@@ -97,13 +97,21 @@ __global__ void __launch_bounds__(128) ingest_rows(const KvipIngestArgs a) {
 }
 
 // ---- SlotLRU commit ---------------------------------------------------------------------------
+// One CTA per row. The set of touched slots lives in shared memory (a 16 KiB bitmap covers the 131072
+// slots a resident pool can have); the list is compacted in place in chunks of 32768 entries, every
+// thread holding 32 consecutive entries in registers, so a 25 % pool of a 128k context is one chunk:
+// one round of loads, one block scan, one round of stores.
 constexpr uint32_t kLruThreads = 1024;
+constexpr uint32_t kLruPer = 32;
+constexpr uint32_t kLruMaxWords = 4096;
 
 __global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
+  __shared__ uint32_t touched_bits[kLruMaxWords];
   __shared__ uint32_t scan[33];
   __shared__ uint32_t unique_count;
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
   const uint32_t active = min(static_cast<uint32_t>(max(a.active[row], 0)), a.capacity);
+  const uint32_t active_words = (active + 31u) >> 5;
   int32_t* order = a.order + static_cast<uint64_t>(row) * a.capacity;
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(a.bitmap) + static_cast<uint64_t>(row) * a.words;
   int32_t* slots = a.slots + static_cast<uint64_t>(row) * kLruSlots;
@@ -111,6 +119,7 @@ __global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
   const int32_t* touched = a.touched + static_cast<uint64_t>(row) * a.touched_stride;
 
   if (tid == 0) unique_count = 0;
+  for (uint32_t w = tid; w < active_words; w += kLruThreads) touched_bits[w] = 0;
   for (uint32_t w = tid; w < a.words; w += kLruThreads) bitmap[w] = 0;
   if (reserved)
     for (uint32_t i = tid; i < kLruSlots; i += kLruThreads) {
@@ -124,41 +133,53 @@ __global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
     const int32_t s = touched[i];
     if (s < 0 || static_cast<uint32_t>(s) >= active) continue;
     const uint32_t bit = 1u << (s & 31);
-    if (!(atomicOr(bitmap + (s >> 5), bit) & bit)) ++mine;
+    if (!(atomicOr(touched_bits + (s >> 5), bit) & bit)) ++mine;
   }
   if (mine) atomicAdd(&unique_count, mine);
   __syncthreads();
   const uint32_t unique = unique_count;
   if (unique) {
-    // 2. drop the touched slots from the list, keeping the order of the rest (in place: a chunk
-    //    is fully in registers before anything is written, and writes never pass the reads)
+    // 2. drop the touched slots from the list, keeping the order of the rest. In place: a chunk is fully
+    //    in registers before anything is written, and writes never pass the reads. Every warp owns a
+    //    contiguous run of the chunk (32 groups of 32 entries), so loads and stores are coalesced and the
+    //    ranks inside a group come from a ballot; one block scan per chunk orders the warps.
     uint32_t kept_total = 0;
-    constexpr uint32_t kPer = 16;  // consecutive list entries per thread and chunk
-    for (uint32_t start = 0; start < active; start += kLruThreads * kPer) {
-      int32_t v[kPer];
-      uint32_t keep = 0;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t start = 0; start < active; start += kLruThreads * kLruPer) {
+      int32_t v[kLruPer];
+      uint32_t keep_mask[kLruPer];
+      const uint32_t warp_base = start + warp * (32u * kLruPer);
+      uint32_t warp_kept = 0;
 #pragma unroll
-      for (uint32_t j = 0; j < kPer; ++j) {
-        const uint32_t p = start + tid * kPer + j;
+      for (uint32_t j = 0; j < kLruPer; ++j) {
+        const uint32_t p = warp_base + j * 32u + lane;
         v[j] = p < active ? order[p] : -1;
-        if (v[j] >= 0 && !((bitmap[v[j] >> 5] >> (v[j] & 31)) & 1u)) keep |= 1u << j;
+      }
+#pragma unroll
+      for (uint32_t j = 0; j < kLruPer; ++j) {
+        const bool keep = v[j] >= 0 && !((touched_bits[v[j] >> 5] >> (v[j] & 31)) & 1u);
+        keep_mask[j] = __ballot_sync(0xffffffffu, keep);
+        warp_kept += __popc(keep_mask[j]);
       }
       uint32_t total;
-      uint32_t offset = kept_total + block_exclusive_scan(__popc(keep), scan, &total);
+      // one value per warp: lane 0 carries the warp's count into the block scan
+      uint32_t offset = kept_total + block_exclusive_scan(lane == 0 ? warp_kept : 0u, scan, &total);
+      offset = __shfl_sync(0xffffffffu, offset, 0);
 #pragma unroll
-      for (uint32_t j = 0; j < kPer; ++j)
-        if ((keep >> j) & 1u) order[offset++] = v[j];
+      for (uint32_t j = 0; j < kLruPer; ++j) {
+        if ((keep_mask[j] >> lane) & 1u) order[offset + __popc(keep_mask[j] & ((1u << lane) - 1u))] = v[j];
+        offset += __popc(keep_mask[j]);
+      }
       kept_total += total;
       __syncthreads();
     }
     // 3. append the touched slots in ascending slot number
-    const uint32_t active_words = (active + 31u) >> 5;
     const uint32_t per = (active_words + kLruThreads - 1u) / kLruThreads;
     uint32_t local = 0;
-    for (uint32_t w = tid * per; w < (tid + 1u) * per && w < active_words; ++w) local += __popc(bitmap[w]);
+    for (uint32_t w = tid * per; w < (tid + 1u) * per && w < active_words; ++w) local += __popc(touched_bits[w]);
     uint32_t out = kept_total + block_exclusive_scan(local, scan, nullptr);
     for (uint32_t w = tid * per; w < (tid + 1u) * per && w < active_words; ++w) {
-      uint32_t bits = bitmap[w];
+      uint32_t bits = touched_bits[w];
       while (bits) {
         order[out++] = static_cast<int32_t>(w * 32u + __ffs(bits) - 1u);
         bits &= bits - 1u;
@@ -167,8 +188,6 @@ __global__ void __launch_bounds__(kLruThreads) lru_commit(const KvipLruArgs a) {
     __syncthreads();
   }
   // 4. victims = the oldest min(2048, active) slots, their bitmap and inverse map
-  for (uint32_t w = tid; w < a.words; w += kLruThreads) bitmap[w] = 0;
-  __syncthreads();
   for (uint32_t i = tid; i < kLruSlots; i += kLruThreads) {
     const int32_t s = i < active ? order[i] : -1;
     slots[i] = s;
@@ -254,6 +273,7 @@ extern "C" uint32_t kvip_b200_ingest(const KvipIngestArgs* a, void* stream) {
 extern "C" uint32_t kvip_b200_lru_commit(const KvipLruArgs* a, void* stream) {
   KVIP_REQUIRE(a && a->order && a->slots && a->bitmap && a->unique && a->touched && a->active, "lru_commit: null pointer");
   KVIP_REQUIRE(a->rows >= 1 && a->capacity >= 1 && a->words * 32u >= a->capacity, "lru_commit: bitmap too small");
+  KVIP_REQUIRE(a->capacity <= kvip::kLruMaxWords * 32u, "lru_commit: at most 131072 slots per row");
   kvip::lru_commit<<<a->rows, kvip::kLruThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
   kvip::count_launch();
   return kvip::check_launch("lru_commit");

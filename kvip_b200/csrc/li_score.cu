@@ -14,8 +14,8 @@
 //   * persistent CTAs (one per SM) walk a flat list of (request, page) tiles, so a
 //     request's keys and scales are streamed from HBM exactly once for all of its
 //     query rows;
-//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-9 = two
-//     epilogue groups that take alternate tiles; key stages and a ring of up to eight
+//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-17 = four
+//     epilogue groups that take tiles round-robin; key stages and a ring of up to eight
 //     accumulator buffers in tensor memory are handed over with mbarriers;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
 //     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
@@ -28,7 +28,8 @@
 namespace kvip {
 namespace {
 
-constexpr uint32_t kLiThreads = 320;  // TMA warp, MMA warp, two epilogue groups of four warps
+constexpr uint32_t kEpilogueGroups = 4;
+constexpr uint32_t kLiThreads = 64 + 128 * kEpilogueGroups;  // TMA warp, MMA warp, epilogue groups of four warps
 constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (512 columns / stride)
 constexpr uint32_t kMaxBatch = 1024;
 constexpr uint32_t kMaxN = 256;            // query slots * heads
@@ -41,7 +42,7 @@ template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kStages = kBf16 ? 4 : 8;
   static constexpr uint32_t kQBytes = kMaxN * 128 * kAtoms;
   static constexpr uint32_t kSmemBytes =
-      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 8 * kMaxN * 4 /*W per epilogue warp*/ +
+      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 4 * kEpilogueGroups * kMaxN * 4 /*W per epilogue warp*/ +
       (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 1024 /*barriers*/;
 };
 
@@ -180,7 +181,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t key_smem = base + 1024u;
   const uint32_t q_smem = key_smem + Cfg::kStages * Cfg::kTileBytes;
   float* w_smem = reinterpret_cast<float*>(smem + 1024u + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
-  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 8 * kMaxN);
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kEpilogueGroups * kMaxN);
   uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
   // barrier map: [0,S) full, [S,2S) empty, 2S q_full, 2S+1 q_empty, then kMaxAcc tmem_full and kMaxAcc
   // tmem_empty; then the tmem base word and the abort flag.
@@ -339,9 +340,10 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       }
     }
   } else {
-    // ================= epilogue: two groups of 4 warps, one token row per thread =================
-    // Group g reduces the tiles with (t - tile_begin) % 2 == g, so two tiles are in flight per SM and
-    // the tensor-memory load latency of one hides behind the arithmetic of the other.
+    // ================= epilogue: groups of 4 warps, one token row per thread =================
+    // Group g reduces the tiles with (t - tile_begin) % kEpilogueGroups == g. One tile's reduction is a
+    // long dependent chain (tensor-memory load, 64 max+fma pairs, store), far longer than the time the
+    // next key page needs to arrive, so several tiles are reduced concurrently per SM.
     const uint32_t group = (warp - 2u) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
     const uint32_t row = quad * 32u + lane;       // token row inside the page
@@ -360,15 +362,16 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (t >= tile_end || !a.key_scale) return 1.0f;
       return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
     };
+    constexpr uint32_t G = kEpilogueGroups;
     const uint32_t first = tile_begin + group;
     int32_t page_next = page_of(first);
     float kscale = scale_of(first, page_next);
-    page_next = page_of(first + 2);
-    for (uint32_t t = first; t < tile_end; t += 2) {
+    page_next = page_of(first + G);
+    for (uint32_t t = first; t < tile_end; t += G) {
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
-      const float kscale_next = scale_of(t + 2, page_next);   // consumed next iteration
-      page_next = page_of(t + 4);
+      const float kscale_next = scale_of(t + G, page_next);   // consumed next iteration
+      page_next = page_of(t + 2 * G);
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
         for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
@@ -384,45 +387,25 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
       for (uint32_t q = 0; q < nq; ++q) {
-        float even = 0.f, odd = 0.f;
-        if (H == 64) {
-          uint32_t v0[32], v1[32];
-          tmem_ld_32x32(taddr + q * 64u, v0);
-          tmem_ld_32x32(taddr + q * 64u + 32u, v1);
-          tmem_ld_wait();
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * 64u);
-#pragma unroll
-          for (uint32_t j = 0; j < 8; ++j) {
-            const float4 w = w4[j];
-            even = fmaf(fmaxf(__uint_as_float(v0[4 * j + 0]), 0.f), w.x, even);
-            odd = fmaf(fmaxf(__uint_as_float(v0[4 * j + 1]), 0.f), w.y, odd);
-            even = fmaf(fmaxf(__uint_as_float(v0[4 * j + 2]), 0.f), w.z, even);
-            odd = fmaf(fmaxf(__uint_as_float(v0[4 * j + 3]), 0.f), w.w, odd);
-          }
-#pragma unroll
-          for (uint32_t j = 0; j < 8; ++j) {
-            const float4 w = w4[8 + j];
-            even = fmaf(fmaxf(__uint_as_float(v1[4 * j + 0]), 0.f), w.x, even);
-            odd = fmaf(fmaxf(__uint_as_float(v1[4 * j + 1]), 0.f), w.y, odd);
-            even = fmaf(fmaxf(__uint_as_float(v1[4 * j + 2]), 0.f), w.z, even);
-            odd = fmaf(fmaxf(__uint_as_float(v1[4 * j + 3]), 0.f), w.w, odd);
-          }
-        } else {
+        // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
+        // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        for (uint32_t c = 0; c < H; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + q * 32u, v);
+          tmem_ld_32x32(taddr + q * H + c, v);
           tmem_ld_wait();
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * 32u);
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j) {
             const float4 w = w4[j];
-            even = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, even);
-            odd = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, odd);
-            even = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, even);
-            odd = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, odd);
+            s0 = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, s0);
+            s1 = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, s1);
+            s2 = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, s2);
+            s3 = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, s3);
           }
         }
         if ((live_mask >> q) & 1u) {
-          float score = (even + odd) * kscale;
+          float score = ((s0 + s2) + (s1 + s3)) * kscale;   // (even heads) + (odd heads)
           if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
           a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
         }

@@ -15,23 +15,12 @@
 // block-wide prefix sums (no atomics, so the order is the position order). The row is read
 // from L2 (the LI kernel has just written it) with 16-byte loads.
 #include "common.cuh"
+#include "topk_core.cuh"
 
 namespace kvip {
 namespace {
 
-constexpr uint32_t kThreads = 1024;
-constexpr uint32_t kItems = 16;  // consecutive elements per thread in the ordered pass
-
-__device__ __forceinline__ void hist_add(uint32_t* hist, bool valid, uint32_t bin) {
-  // Degenerate rows (every lane in one bin, e.g. an all-zero score row) would serialise
-  // on one shared-memory word: one lane adds for the whole warp instead.
-  const uint32_t first = __shfl_sync(0xffffffffu, bin, 0);
-  if (__all_sync(0xffffffffu, valid && bin == first)) {
-    if ((threadIdx.x & 31u) == 0) atomicAdd(hist + first, 32u);
-  } else if (valid) {
-    atomicAdd(hist + bin, 1u);
-  }
-}
+using namespace topk_core;
 
 // First radix pass spread over the whole GPU: `segments` CTAs per row add their slice's 12-bit
 // histogram to the row's histogram in global memory (the selecting CTA clears it again after use).
@@ -65,165 +54,8 @@ __global__ void __launch_bounds__(kHistThreads) topk_histogram(const KvipTopkArg
     if (hist[i]) atomicAdd(out + i, hist[i]);
 }
 
-constexpr uint32_t kCandidates = 8192;  // shared-memory candidates of the threshold bin
-
 __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
-  __shared__ uint32_t hist[4096];
-  __shared__ uint32_t scan_scratch[33];
-  __shared__ uint32_t found[2];
-  __shared__ uint32_t cand_count;
-  extern __shared__ uint32_t cand_keys[];  // [kCandidates] when a histogram is supplied
-  const uint32_t row = blockIdx.x, tid = threadIdx.x;
-  const uint32_t b = row / a.queries;
-  int32_t valid_len = min(a.key_lengths[b], a.query_ends[row]);
-  valid_len = min(valid_len, static_cast<int32_t>(a.scoreStride));
-  int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
-  float* out_scores = a.topk_scores ? a.topk_scores + static_cast<uint64_t>(row) * kTop : nullptr;
-  const float* scores = a.scores + static_cast<uint64_t>(row) * a.scoreStride;
-  if (valid_len <= static_cast<int32_t>(kTop)) {
-    for (uint32_t i = tid; i < kTop; i += kThreads) {
-      const bool live = static_cast<int32_t>(i) < valid_len;
-      out[i] = live ? static_cast<int32_t>(i + a.base_index) : -1;
-      if (out_scores) out_scores[i] = live ? scores[i] : 0.f;
-    }
-    return;
-  }
-  const uint32_t L = static_cast<uint32_t>(valid_len);
-  const uint32_t vec_count = (L + 3u) >> 2;
-  const float4* row4 = reinterpret_cast<const float4*>(scores);
-
-  uint32_t prefix = 0, prefix_mask = 0, remaining = kTop;
-  bool in_smem = false;  // passes 2 and 3 run over the shared-memory candidates instead of the row
-#pragma unroll 1
-  for (uint32_t pass = 0; pass < 3; ++pass) {
-    const uint32_t bits = pass == 2 ? 8u : 12u;
-    const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
-    const uint32_t bins = 1u << bits;
-    if (pass == 0 && a.histogram) {
-      uint32_t* global_hist = a.histogram + static_cast<uint64_t>(row) * 4096u;
-      for (uint32_t i = tid; i < bins; i += kThreads) { hist[i] = global_hist[i]; global_hist[i] = 0; }
-      if (tid == 0) cand_count = 0;
-    } else {
-      for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
-    }
-    __syncthreads();
-    // every lane of a warp runs the same number of iterations (hist_add uses warp votes)
-    const uint32_t rounds = (pass == 0 && a.histogram) ? 0u : (in_smem ? (cand_count + kThreads - 1) / kThreads
-                                                                       : (vec_count + kThreads - 1) / kThreads);
-    if (in_smem) {
-      const uint32_t n = cand_count;
-      for (uint32_t r = 0; r < rounds; ++r) {
-        const uint32_t i = r * kThreads + tid;
-        const uint32_t key = i < n ? cand_keys[i] : 0u;
-        hist_add(hist, i < n && (key & prefix_mask) == prefix, (key >> shift) & (bins - 1u));
-      }
-    } else
-    for (uint32_t r = 0; r < rounds; ++r) {
-      const uint32_t v = r * kThreads + tid;
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (v < vec_count) x = row4[v];
-      const float e[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-      for (uint32_t j = 0; j < 4; ++j) {
-        const uint32_t key = sortable_key(e[j]);
-        const bool ok = v < vec_count && (v * 4u + j) < L && (key & prefix_mask) == prefix;
-        hist_add(hist, ok, (key >> shift) & (bins - 1u));
-      }
-    }
-    __syncthreads();
-    // thread i owns the 4 (or fewer) highest unclaimed bins: suffix counts via a scan over
-    // reversed bin groups
-    const uint32_t per = bins / kThreads ? bins / kThreads : 1u;  // 4, 4, then 1 (256 bins)
-    const uint32_t groups = bins / per;
-    uint32_t local = 0;
-    const uint32_t group = groups - 1u - tid;  // valid when tid < groups
-    if (tid < groups)
-      for (uint32_t j = 0; j < per; ++j) local += hist[group * per + j];
-    uint32_t above = block_exclusive_scan(local, scan_scratch, nullptr);
-    if (tid < groups) {
-      for (int32_t j = static_cast<int32_t>(per) - 1; j >= 0; --j) {
-        const uint32_t bin = group * per + static_cast<uint32_t>(j);
-        const uint32_t c = hist[bin];
-        if (above < remaining && above + c >= remaining) {
-          found[0] = bin;
-          found[1] = remaining - above;
-        }
-        above += c;
-      }
-    }
-    __syncthreads();
-    prefix |= found[0] << shift;
-    prefix_mask |= (bins - 1u) << shift;
-    remaining = found[1];
-    __syncthreads();
-    if (pass == 0 && a.histogram) {
-      // One cheap pass collects the threshold bin's keys; if they fit, the remaining 20 bits are
-      // resolved in shared memory. (An overfull bin, e.g. a constant row, keeps the global passes.)
-      const uint32_t want = hist[prefix >> 20];
-      if (want <= kCandidates) {
-        const uint32_t rounds_f = (vec_count + kThreads - 1) / kThreads;
-        for (uint32_t r = 0; r < rounds_f; ++r) {
-          const uint32_t v = r * kThreads + tid;
-          if (v >= vec_count) continue;
-          const float4 x = row4[v];
-          const float e[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            const uint32_t key = sortable_key(e[j]);
-            if ((v * 4u + j) < L && (key & prefix_mask) == prefix) cand_keys[atomicAdd(&cand_count, 1u)] = key;
-          }
-        }
-        in_smem = true;
-      }
-      __syncthreads();
-    }
-  }
-  const uint32_t kth = prefix;             // exact key of the 2048th largest element
-  const uint32_t need_eq = remaining;      // how many == kth positions are taken
-  const uint32_t count_gt = kTop - need_eq;
-
-  // ordered compaction
-  uint32_t gt_base = 0, eq_base = 0;
-  const uint32_t chunk = kThreads * kItems;
-  for (uint32_t start = 0; start < L; start += chunk) {
-    const uint32_t first = start + tid * kItems;
-    float e[kItems];
-    uint32_t flags_gt = 0, flags_eq = 0;
-#pragma unroll
-    for (uint32_t v = 0; v < kItems / 4; ++v) {
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (first + v * 4u < L) x = row4[(first >> 2) + v];
-      e[v * 4 + 0] = x.x; e[v * 4 + 1] = x.y; e[v * 4 + 2] = x.z; e[v * 4 + 3] = x.w;
-    }
-#pragma unroll
-    for (uint32_t j = 0; j < kItems; ++j) {
-      const uint32_t key = sortable_key(e[j]);
-      const bool live = first + j < L;
-      flags_gt |= (live && key > kth ? 1u : 0u) << j;
-      flags_eq |= (live && key == kth ? 1u : 0u) << j;
-    }
-    const uint32_t packed = __popc(flags_gt) | (__popc(flags_eq) << 16);
-    uint32_t total;
-    const uint32_t offset = block_exclusive_scan(packed, scan_scratch, &total);
-    uint32_t g = gt_base + (offset & 0xffffu), q = eq_base + (offset >> 16);
-#pragma unroll
-    for (uint32_t j = 0; j < kItems; ++j) {
-      if ((flags_gt >> j) & 1u) {
-        out[g] = static_cast<int32_t>(first + j + a.base_index);
-        if (out_scores) out_scores[g] = e[j];
-        ++g;
-      } else if ((flags_eq >> j) & 1u) {
-        if (q < need_eq) {
-          out[count_gt + q] = static_cast<int32_t>(first + j + a.base_index);
-          if (out_scores) out_scores[count_gt + q] = e[j];
-        }
-        ++q;
-      }
-    }
-    gt_base += total & 0xffffu;
-    eq_base += total >> 16;
-    if (gt_base == count_gt && eq_base >= need_eq) break;  // block-uniform
-  }
+  select_row(a, blockIdx.x, a.histogram ? a.histogram + static_cast<uint64_t>(blockIdx.x) * 4096u : nullptr);
 }
 
 // ---- merge of shard candidates -----------------------------------------------------------
@@ -277,7 +109,10 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a, ui
 
 }  // namespace
 
+uint32_t launch_topk_split(const KvipTopkArgs& a, cudaStream_t stream);
+
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream) {
+  if (a.split_scratch) return launch_topk_split(a, stream);
   size_t smem = 0;
   if (a.histogram) {
     uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
@@ -345,6 +180,7 @@ extern "C" uint32_t kvip_b200_topk_static(const KvipTopkArgs* a, void* stream) {
     return kvip::check_launch("topk_static: clearing the scratch");
   KvipTopkArgs with_scratch = *a;
   with_scratch.histogram = scratch;
+  with_scratch.split_scratch = nullptr;
   return kvip::launch_topk(with_scratch, s);
 }
 

@@ -70,9 +70,12 @@ def li_score(query, keys, weights, query_scale, key_scale, key_lengths, query_en
     return scores, status
 
 
-def topk(scores, key_lengths, query_ends, out=None, *, out_scores=None, base_index=0, histogram=None):
+def topk(scores, key_lengths, query_ends, out=None, *, out_scores=None, base_index=0, histogram=None,
+         split_scratch=None):
     """Canonical TopK-2048 per score row. query_ends [B, Q] or flat [B*Q]. `histogram` is an all-zero int32
-    [rows, 4096] scratch (returned all-zero): with it the first radix pass is spread over the whole GPU."""
+    [rows, 4096] scratch (returned all-zero): with it the first radix pass is spread over the whole GPU;
+    `split_scratch` is an int32 [rows, 20544] scratch whose first 4160 words per row are zero (and are
+    zero again afterwards): with it every pass is."""
     device = scores.device
     rows = scores.shape[0]
     queries = rows // key_lengths.numel()
@@ -83,8 +86,8 @@ def topk(scores, key_lengths, query_ends, out=None, *, out_scores=None, base_ind
         out = torch.empty((rows, TOPK), dtype=torch.int32, device=device)
     args = _lib.TopkArgs(scores=_ptr(scores), key_lengths=_ptr(key_lengths), query_ends=_ptr(query_ends),
                          topk=_ptr(out), topk_scores=_ptr(out_scores), histogram=_ptr(histogram), rows=rows,
-                         queries=queries,
-                         scoreStride=scores.shape[1], base_index=base_index)
+                         queries=queries, scoreStride=scores.shape[1], base_index=base_index,
+                         split_scratch=_ptr(split_scratch))
     _lib.check(_lib.load_library().kvip_b200_topk(ctypes.byref(args), _stream(device)), "topk")
     return out
 

@@ -131,10 +131,53 @@ class DecodePipeline:
             scale = _log_uniform((tokens, heads), 1e-3, 1e-1, g, device)
         inputs.pack(query, weights, scale)
 
-    def step(self):
-        """One decode step of the path: the fused forward, then the LRU feedback of the slots it used."""
+    def step(self, ingest=False):
+        """One decode step of the path: (the paged Index update of the new tokens,) the fused forward, then
+        the LRU feedback of the slots it used."""
+        if ingest:
+            self.ingest_new_tokens()
         self.forward()
         self.lru.commit(self.update.slot_output.view(self.batch, -1))
+
+    def ingest_new_tokens(self):
+        """Write one new bf16 k_I row per query token into the Index cache (quantised to FP8 + scale)."""
+        if self.key_dtype != "fp8":
+            raise ValueError("the Index update quantises into FP8 storage")
+        if not hasattr(self, "new_keys"):
+            from types import SimpleNamespace
+            tokens = self.batch * self.queries
+            g = torch.Generator(device=self.device)
+            g.manual_seed(777)
+            self.new_keys = torch.randn((tokens, 128), generator=g, device=self.device).to(torch.bfloat16)
+            self.new_meta = SimpleNamespace(slot_mapping=torch.arange(tokens, dtype=torch.int64, device=self.device))
+        inputs = self.workspace.inputs
+        self.storage.ingest_decode((self.new_keys, None), self.new_meta, inputs, inputs.row_owners)
+
+    def make_query_bank(self, count, correlation=0.9, seed=0):
+        """`count` query sets whose selections overlap from one step to the next: an AR(1) drift
+        q[k] = rho * q[k-1] + sqrt(1 - rho^2) * noise on the unquantised queries, fixed head weights."""
+        device, heads = self.device, self.heads
+        tokens = self.batch * self.queries
+        g = torch.Generator(device=device)
+        g.manual_seed(2000003 + seed)
+        weights = (torch.randn((tokens, heads), generator=g, device=device) / 8).to(self.workspace.inputs.weights.dtype)
+        scale = _log_uniform((tokens, heads), 1e-3, 1e-1, g, device)
+        state = torch.randn((tokens, heads, 128), generator=g, device=device)
+        bank = []
+        for _ in range(count):
+            noise = torch.randn((tokens, heads, 128), generator=g, device=device)
+            state = correlation * state + (1 - correlation ** 2) ** 0.5 * noise
+            if self.key_dtype == "bf16":
+                bank.append((state.to(torch.bfloat16), weights, None))
+            else:
+                bank.append(((state * 8).clamp(-448, 448).to(torch.float8_e4m3fn), weights, scale))
+        self.query_bank = bank
+        return bank
+
+    def load_queries(self, index):
+        """Pack query set `index` of the bank into the bound input buffers (device copies, in stream order)."""
+        query, weights, scale = self.query_bank[index % len(self.query_bank)]
+        self.workspace.inputs.pack(query, weights, scale)
 
     def query_tokens(self):
         return self.batch * self.queries

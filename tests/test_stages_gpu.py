@@ -113,6 +113,14 @@ def _topk_check(scores_np, key_lengths, query_ends, device, base_index=0):
         torch.cuda.synchronize()
         assert torch.equal(split, got)
         assert int(histogram.abs().sum()) == 0
+    # third path: every pass on several CTAs per row
+    scratch = torch.zeros((scores.shape[0], 20544), dtype=torch.int32, device=device)
+    split_scores = torch.zeros_like(out_scores)
+    for _ in range(2):
+        split = ops.topk(scores, lengths_t, ends_t, base_index=base_index, split_scratch=scratch, out_scores=split_scores)
+        torch.cuda.synchronize()
+        assert torch.equal(split, got) and torch.equal(split_scores, out_scores)
+        assert int(scratch[:, :4160].abs().sum()) == 0   # histogram + header are handed back all-zero
     expected = oracle_c.topk(scores_np, key_lengths, query_ends, base_index)
     got = got.cpu().numpy()
     assert np.array_equal(got, expected)
