@@ -91,7 +91,9 @@ typedef struct KvipLiArgs {
   int32_t* status;            /* [1] OR-ed KVIP_ERR_* */
   uint32_t batch, queries, heads, pagesPerRequest;
   uint32_t keyRows, scoreStride, keyDtype, weightDtype;
-  uint32_t scoreMode, ctas, reserved0, reserved1;
+  uint32_t scoreMode, ctas;
+  uint32_t stages;            /* key pages in flight per CTA; 0 = as many as shared memory holds */
+  uint32_t reserved1;
 } KvipLiArgs;
 uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
 /* CUDA-core restatement of the same formula with the oracle's accumulation order;

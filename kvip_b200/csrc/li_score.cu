@@ -14,9 +14,13 @@
 //   * persistent CTAs (one per SM) walk a flat list of (request, page) tiles, so a
 //     request's keys and scales are streamed from HBM exactly once for all of its
 //     query rows;
-//   * warp 0 = TMA producer, warp 1 = MMA issuer (owns tensor memory), warps 2-17 = four
-//     epilogue groups that take tiles round-robin; key stages and a ring of up to eight
-//     accumulator buffers in tensor memory are handed over with mbarriers;
+//   * warp 0 = TMA producer, warps 1-4 = MMA issuers that take tiles round-robin (warp 1 owns
+//     tensor memory), warps 5-20 = four epilogue groups that take tiles round-robin; key
+//     stages and a ring of up to eight accumulator buffers in tensor memory are handed over
+//     with mbarriers. The number of issuers divides the number of key stages and of
+//     accumulators, and the number of epilogue groups divides the number of accumulators, so
+//     every use of one stage or accumulator is waited for by the same thread, in order: a
+//     parity wait by a thread that runs a whole phase ahead of the barrier would pass at once;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
 //     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
 //     is released and the kernel returns.
@@ -29,7 +33,9 @@ namespace kvip {
 namespace {
 
 constexpr uint32_t kEpilogueGroups = 4;
-constexpr uint32_t kLiThreads = 64 + 128 * kEpilogueGroups;  // TMA warp, MMA warp, epilogue groups of four warps
+constexpr uint32_t kMmaWarps = 4;          // MMA issuers: warps 1..4 (one thread each)
+constexpr uint32_t kFirstEpilogueWarp = 5; // any four consecutive warps cover the four tensor-memory lane quadrants
+constexpr uint32_t kLiThreads = 32 * kFirstEpilogueWarp + 128 * kEpilogueGroups;
 constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (512 columns / stride)
 constexpr uint32_t kMaxBatch = 1024;
 constexpr uint32_t kMaxN = 256;            // query slots * heads
@@ -39,11 +45,19 @@ constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
 template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kAtoms = kBf16 ? 2 : 1;           // 128-byte K slices per row
   static constexpr uint32_t kTileBytes = kAtomBytes * kAtoms; // one key page in smem
-  static constexpr uint32_t kStages = kBf16 ? 4 : 8;
-  static constexpr uint32_t kQBytes = kMaxN * 128 * kAtoms;
-  static constexpr uint32_t kSmemBytes =
-      1024 /*alignment slack*/ + kStages * kTileBytes + kQBytes + 4 * kEpilogueGroups * kMaxN * 4 /*W per epilogue warp*/ +
-      (kMaxBatch + 1) * 4 /*tile prefix*/ + kMaxBatch /*active queries*/ + 1024 /*barriers*/;
+  static constexpr uint32_t kMaxStages = 8;   // more than eight 16 KB stages in flight per SM measured slower
+  static constexpr uint32_t kSmemLimit = 227 * 1024;
+  // everything but the key stages, for `n` = query slots x heads accumulator columns
+  static constexpr uint32_t fixed_bytes(uint32_t n) {
+    return 1024 /*alignment slack*/ + 1024 /*barriers*/ + n * 128 * kAtoms /*query tile*/ +
+           4 * kEpilogueGroups * n * 4 /*W per epilogue warp*/ + (kMaxBatch + 1) * 4 /*tile prefix*/ +
+           kMaxBatch /*active queries*/ + 64;
+  }
+  // as many key stages as shared memory holds: bytes in flight are what saturates HBM
+  static constexpr uint32_t stages_for(uint32_t n) {
+    const uint32_t s = (kSmemLimit - fixed_bytes(n)) / kTileBytes;
+    return s > kMaxStages ? kMaxStages : s;
+  }
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------
@@ -61,18 +75,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one gave up).
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0u;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try(bar, parity)) return true;  // the common case costs one instruction
   const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
+    if (mbar_try(bar, parity)) return true;
     if ((spin & 255u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - start > kWaitCycles) break;
@@ -168,7 +186,7 @@ __device__ __forceinline__ float load_weight(const KvipLiArgs& a, uint32_t index
 template <bool kBf16>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap query_map,
-                 const __grid_constant__ KvipLiArgs a) {
+                 const __grid_constant__ KvipLiArgs a, const uint32_t S) {
   using Cfg = LiCfg<kBf16>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -179,24 +197,27 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   // [W per epilogue warp][tile prefix][active queries]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   const uint32_t key_smem = base + 1024u;
-  const uint32_t q_smem = key_smem + Cfg::kStages * Cfg::kTileBytes;
-  float* w_smem = reinterpret_cast<float*>(smem + 1024u + Cfg::kStages * Cfg::kTileBytes + Cfg::kQBytes);
-  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kEpilogueGroups * kMaxN);
+  const uint32_t n_max = a.queries * a.heads;  // accumulator columns / query-tile rows of this launch
+  const uint32_t q_atom_bytes = n_max * 128u;  // one 128-byte K slice of the query tile
+  const uint32_t q_smem = key_smem + S * Cfg::kTileBytes;
+  float* w_smem = reinterpret_cast<float*>(smem + 1024u + S * Cfg::kTileBytes + q_atom_bytes * Cfg::kAtoms);
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kEpilogueGroups * n_max);
   uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
   // barrier map: [0,S) full, [S,2S) empty, 2S q_full, 2S+1 q_empty, then kMaxAcc tmem_full and kMaxAcc
   // tmem_empty; then the tmem base word and the abort flag.
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
-  constexpr uint32_t S = Cfg::kStages;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 + 2 * kMaxAcc);
-  constexpr uint32_t kQFull = 2 * S, kQEmpty = 2 * S + 1, kAccFull = 2 * S + 2, kAccEmpty = 2 * S + 2 + kMaxAcc;
+  const uint32_t kQFull = 2 * S, kQEmpty = 2 * S + 1, kAccFull = 2 * S + 2, kAccEmpty = 2 * S + 2 + kMaxAcc;
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t H = a.heads, Q = a.queries, pages = a.pagesPerRequest;
   // accumulator ring in tensor memory: stride = columns one tile can need, rounded to a power of two
   const uint32_t acc_stride = Q * H <= 32u ? 32u : (Q * H <= 64u ? 64u : (Q * H <= 128u ? 128u : 256u));
-  const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);
+  const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);   // 2, 4 or 8
+  const uint32_t issuers = ((S | acc_count) & 3u) == 0u ? 4u : (((S | acc_count) & 1u) == 0u ? 2u : 1u);
+  const uint32_t groups = min(kEpilogueGroups, acc_count);
 
   // ---- per-CTA schedule: tiles per request -> prefix sums (warp 0) -------------------
   if (warp == 0) {
@@ -228,7 +249,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   }
   if (threadIdx.x == 64) {
     for (uint32_t i = 0; i < S; ++i) { mbar_init(bar(i), 1); mbar_init(bar(S + i), 1); }
-    mbar_init(bar(kQFull), 1); mbar_init(bar(kQEmpty), 1);
+    mbar_init(bar(kQFull), 1); mbar_init(bar(kQEmpty), issuers);
     for (uint32_t i = 0; i < kMaxAcc; ++i) { mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -281,7 +302,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
               mbar_expect_tx(bar(kQFull), rows * 128u * Cfg::kAtoms);
               for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
                 for (uint32_t r = 0; r < rows; r += 32)
-                  tma_load_2d(q_smem + atom * (kMaxN * 128u) + r * 128u, &query_map,
+                  tma_load_2d(q_smem + atom * q_atom_bytes + r * 128u, &query_map,
                               static_cast<int32_t>(atom * 64u), static_cast<int32_t>(b * Q * H + r),
                               bar(kQFull));
               ++loaded_q;
@@ -303,40 +324,55 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         alive = __shfl_sync(0xffffffffu, alive, 0);
       }
     }
-  } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
+  } else if (warp <= kMmaWarps) {
+    // ================= MMA issuers =================
+    // Issuer w (one thread of warp 1 + w) takes the tiles with (t - tile_begin) % issuers == w. Issuing
+    // a tcgen05 instruction occupies the issuing thread for tens of nanoseconds, and a page needs four MMAs
+    // and two commits: one thread alone caps the SM below the rate at which key pages arrive from HBM.
+    // Tiles are independent (each has its own accumulator), so the issuers need no order among themselves.
+    // The query operand is shared: every issuer waits for each request's query tile and arrives on the
+    // q_empty barrier once per request, by tcgen05.commit if it issued MMAs that read the tile.
+    const uint32_t w = warp - 1u;
+    if (lane == 0 && w < issuers && tile_begin < tile_end) {
       TileCursor cur(prefix, a.batch);
-      uint32_t stage = 0, phase = 0, seen_q = 0, idesc = 0;
-      int32_t bound = -1;
-      for (uint32_t t = tile_begin; t < tile_end; ++t) {
-        const uint32_t b = cur.seek(t);
-        if (static_cast<int32_t>(b) != bound) {
-          if (!mbar_wait(bar(kQFull), seen_q & 1u, abort_flag)) break;
-          ++seen_q;
-          bound = static_cast<int32_t>(b);
-          const uint32_t n = active_q[b] * H;
-          const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
-          idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-        }
-        if (!mbar_wait(bar(stage), phase, abort_flag)) break;
-        const uint32_t local = t - tile_begin, acc = local % acc_count, acc_phase = (local / acc_count) & 1u;
-        if (!mbar_wait(bar(kAccEmpty + acc), acc_phase ^ 1u, abort_flag)) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * acc_stride;
+      uint32_t request = cur.seek(tile_begin), seq = 0;
+      uint32_t t = tile_begin + w;
+      uint32_t stage = w, phase = 0, acc = w, acc_phase = 0;   // w < issuers <= min(S, acc_count)
+      bool alive = true;
+      while (alive) {
+        const uint32_t request_end = min(prefix[request + 1], tile_end);
+        if (!mbar_wait(bar(kQFull), seq & 1u, abort_flag)) break;
+        const uint32_t n = active_q[request] * H;
+        const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+        bool issued = false;
+        for (; t < request_end; t += issuers) {
+          if (!mbar_wait(bar(stage), phase, abort_flag) ||
+              !mbar_wait(bar(kAccEmpty + acc), acc_phase ^ 1u, abort_flag)) { alive = false; break; }
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * acc_stride;
 #pragma unroll
-        for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
-          const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
-          const uint64_t db = umma_desc(q_smem + atom * (kMaxN * 128u));
+          for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
+            const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
+            const uint64_t db = umma_desc(q_smem + atom * q_atom_bytes);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k)  // 32 bytes of K per instruction
-            tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
+            for (uint32_t k = 0; k < 4; ++k)  // 32 bytes of K per instruction
+              tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
+          }
+          tcgen05_commit(bar(S + stage));        // key stage free once these MMAs retire
+          tcgen05_commit(bar(kAccFull + acc));   // accumulator ready for the epilogue
+          issued = true;
+          stage += issuers;
+          if (stage >= S) { stage -= S; phase ^= 1u; }
+          acc += issuers;
+          if (acc >= acc_count) { acc -= acc_count; acc_phase ^= 1u; }
         }
-        tcgen05_commit(bar(S + stage));        // key stage free once these MMAs retire
-        tcgen05_commit(bar(kAccFull + acc));   // accumulator ready for the epilogue
-        const bool last_of_request = (t + 1 == tile_end) || (t + 1 >= prefix[b + 1]);
-        if (last_of_request) tcgen05_commit(bar(kQEmpty));  // query operand may be replaced
-        if (++stage == S) { stage = 0; phase ^= 1u; }
+        if (!alive) break;
+        if (issued) tcgen05_commit(bar(kQEmpty));  // query operand may be replaced once my MMAs retire
+        else mbar_arrive(bar(kQEmpty));
+        if (request_end >= tile_end) break;
+        do { ++request; } while (prefix[request + 1] == prefix[request]);  // next request that has tiles
+        ++seq;
       }
     }
   } else {
@@ -344,10 +380,10 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     // Group g reduces the tiles with (t - tile_begin) % kEpilogueGroups == g. One tile's reduction is a
     // long dependent chain (tensor-memory load, 64 max+fma pairs, store), far longer than the time the
     // next key page needs to arrive, so several tiles are reduced concurrently per SM.
-    const uint32_t group = (warp - 2u) >> 2;
+    const uint32_t group = (warp - kFirstEpilogueWarp) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
     const uint32_t row = quad * 32u + lane;       // token row inside the page
-    float* w_warp = w_smem + (warp - 2u) * kMaxN;  // private copy: no cross-warp barrier needed
+    float* w_warp = w_smem + (warp - kFirstEpilogueWarp) * n_max;  // private copy: no cross-warp barrier needed
     TileCursor cur(prefix, a.batch), ahead(prefix, a.batch);
     uint32_t live_mask = 0;
     int32_t bound = -1;
@@ -362,11 +398,12 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (t >= tile_end || !a.key_scale) return 1.0f;
       return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
     };
-    constexpr uint32_t G = kEpilogueGroups;
-    const uint32_t first = tile_begin + group;
+    const uint32_t G = groups;
+    const uint32_t first = group < G ? tile_begin + group : tile_end;   // surplus groups stay idle
     int32_t page_next = page_of(first);
     float kscale = scale_of(first, page_next);
     page_next = page_of(first + G);
+    uint32_t acc = group, acc_phase = 0;   // group < G <= acc_count
     for (uint32_t t = first; t < tile_end; t += G) {
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
@@ -381,7 +418,6 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         bound = static_cast<int32_t>(b);
       }
       const uint32_t token = (t - prefix[b]) * kBlockTokens + row;
-      const uint32_t local = t - tile_begin, acc = local % acc_count, acc_phase = (local / acc_count) & 1u;
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(bar(kAccFull + acc), acc_phase, abort_flag))) break;
       tcgen05_fence_after();
@@ -412,6 +448,8 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       }
       tcgen05_fence_before();
       mbar_arrive(bar(kAccEmpty + acc));
+      acc += G;
+      if (acc >= acc_count) { acc -= acc_count; acc_phase ^= 1u; }
       kscale = kscale_next;
     }
   }
@@ -537,10 +575,14 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(li_score_tcgen05<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(Cfg::kSmemBytes));
+                                         static_cast<int>(Cfg::kSmemLimit));
     if (e != cudaSuccess) return check_launch("li_score attribute");
     configured = true;
   }
+  const uint32_t n_max = a.queries * a.heads;
+  uint32_t stages = Cfg::stages_for(n_max);
+  if (a.stages && a.stages >= 2 && a.stages < stages) stages = a.stages;  // tuning knob: fewer key stages
+  const uint32_t smem_bytes = Cfg::fixed_bytes(n_max) + stages * Cfg::kTileBytes;
   uint32_t ctas = a.ctas;
   if (!ctas) {
     int dev = 0, sms = 0;
@@ -548,7 +590,7 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     ctas = static_cast<uint32_t>(sms);
   }
-  li_score_tcgen05<kBf16><<<ctas, kLiThreads, Cfg::kSmemBytes, stream>>>(key_map, query_map, a);
+  li_score_tcgen05<kBf16><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
   count_launch();
   return check_launch("li_score_tcgen05");
 }

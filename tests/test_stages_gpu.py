@@ -74,6 +74,31 @@ def test_li_tcgen05_within_tolerance(spec, score_mode, device):
         assert (err <= rtol * np.abs(ref) + rtol * 1e-2 * scale).all(), (t, err.max(), scale)
 
 
+RING_CASES = [(1, 64, "fp8"), (2, 64, "fp8"), (4, 64, "fp8"), (4, 32, "fp8"), (1, 64, "bf16"), (4, 64, "bf16")]
+
+
+@pytest.mark.parametrize("stages", [0, 2, 3, 5, 8])
+@pytest.mark.parametrize("queries,heads,key_dtype", RING_CASES)
+def test_li_tcgen05_rings_wrap(queries, heads, key_dtype, stages, device):
+    """Two CTAs for ~170 key pages: every CTA walks its key-stage ring and its accumulator ring many
+    times and crosses request boundaries, for each accumulator count (8, 4, 2) and for stage counts that
+    allow four, two and one MMA issuers. Checked against the CUDA-core kernel, which matches the C
+    oracle bit for bit."""
+    case = workloads.li_case(seed=40 + queries, batch=3, queries=queries, heads=heads, len_lo=5000, len_hi=9000,
+                             key_dtype=key_dtype, weight_dtype="bf16")
+    expected, _ = _li(case, device, simt=True)
+    scores, _ = _li(case, device, ctas=2, stages=stages)
+    expected, got = expected.cpu().numpy(), scores.cpu().numpy()
+    mask = _valid_mask(case, expected.shape[1])
+    rtol = 2e-3 if key_dtype == "bf16" else 1e-2
+    for t in range(got.shape[0]):
+        if not mask[t].any():
+            continue
+        ref, out = expected[t][mask[t]], got[t][mask[t]]
+        scale = np.abs(ref).max()
+        assert (np.abs(out - ref) <= rtol * np.abs(ref) + rtol * 1e-2 * scale).all(), (t, scale)
+
+
 def test_li_exact_binary_fraction_fixture(device):
     """Exact-arithmetic inputs in the style of the reference fixture (workloads.py:196-283: FP8 codes
     {0, 0x38, 0x40, 0x44}, power-of-two scales): every partial sum is exact in fp32, so the tensor-core
