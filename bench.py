@@ -190,12 +190,13 @@ def run_ours(args):
                                 queries=p.queries, output_stride=p.output_stride, token_bytes=p.token_bytes,
                                 row_owners=inputs.row_owners)
         split_scratch = torch.zeros((p.batch * p.queries, _lib.TOPK_SPLIT_WORDS), dtype=torch.int32, device=device)
+        histogram = torch.zeros((p.batch * p.queries, 4096), dtype=torch.int32, device=device)
         tk_hist = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048),  # noqa: E731
-                                   histogram=p.forward.topk_histogram)
+                                   histogram=histogram)
         tk_split = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048),  # noqa: E731
                                     split_scratch=split_scratch)
         lru = lambda: p.lru.commit(p.update.slot_output.view(p.batch, -1))  # noqa: E731
-        for name, fn in (("li_score", li), ("topk_one_kernel", tk), ("topk", tk_hist), ("topk_all_passes_split", tk_split),
+        for name, fn in (("li_score", li), ("topk", tk), ("topk_histogram_select", tk_hist), ("topk_all_passes_split", tk_split),
                          ("gather", ga), ("lru_commit", lru)):
             for _ in range(2):
                 fn()

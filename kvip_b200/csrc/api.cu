@@ -9,6 +9,7 @@ namespace kvip {
 uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream);
 uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream);
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream);
+
 uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream);
 uint32_t launch_exchange(const KvipExchangeArgs& a, cudaStream_t stream);
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream);

@@ -10,7 +10,7 @@
 // Ties therefore go to the lower token index, and the output is a deterministic function
 // of the score row.
 //
-// One CTA per query row. Three histogram passes (12 + 12 + 8 bits of the order-preserving
+// topk_select: one CTA per query row. Three histogram passes (12 + 12 + 8 bits of the order-preserving
 // u32 image of the float) find v exactly; a fourth, ordered pass compacts the winners with
 // block-wide prefix sums (no atomics, so the order is the position order). The row is read
 // from L2 (the LI kernel has just written it) with 16-byte loads.
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(kHistThreads) topk_histogram(const KvipTopkArg
 }
 
 __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
-  select_row(a, blockIdx.x, a.histogram ? a.histogram + static_cast<uint64_t>(blockIdx.x) * 4096u : nullptr);
+  select_row(a, blockIdx.x, a.histogram + static_cast<uint64_t>(blockIdx.x) * 4096u);
 }
 
 // ---- merge of shard candidates -----------------------------------------------------------
@@ -110,25 +110,26 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a, ui
 }  // namespace
 
 uint32_t launch_topk_split(const KvipTopkArgs& a, cudaStream_t stream);
+uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream);
 
+// Path by what the caller supplies: no scratch -> one CTA per row, sampled pivot + one filtering pass over
+// the row (topk_pivot.cu); `histogram` -> first radix pass spread over the GPU, then one CTA per row;
+// `split_scratch` -> every pass spread over the GPU.
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream) {
   if (a.split_scratch) return launch_topk_split(a, stream);
-  size_t smem = 0;
-  if (a.histogram) {
-    uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
-    segments = segments < 1u ? 1u : (segments > 32u ? 32u : segments);
-    topk_histogram<<<dim3(segments, a.rows), kHistThreads, 0, stream>>>(a);
-    count_launch();
-    if (uint32_t bad = check_launch("topk_histogram")) return bad;
-    smem = kCandidates * sizeof(uint32_t);
-    static bool configured = false;  // static + dynamic shared memory exceeds the 48 KiB default
-    if (!configured) {
-      if (cudaFuncSetAttribute(topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
-        return check_launch("topk_select attribute");
-      configured = true;
-    }
+  if (!a.histogram) return launch_topk_pivot(a, stream);
+  uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
+  segments = segments < 1u ? 1u : (segments > 32u ? 32u : segments);
+  topk_histogram<<<dim3(segments, a.rows), kHistThreads, 0, stream>>>(a);
+  count_launch();
+  if (uint32_t bad = check_launch("topk_histogram")) return bad;
+  static bool configured = false;  // static + dynamic shared memory exceeds the 48 KiB default
+  if (!configured) {
+    if (cudaFuncSetAttribute(topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+      return check_launch("topk_select attribute");
+    configured = true;
   }
-  topk_select<<<a.rows, kThreads, smem, stream>>>(a);
+  topk_select<<<a.rows, kThreads, kCandidates * sizeof(uint32_t), stream>>>(a);
   count_launch();
   return check_launch("topk_select");
 }

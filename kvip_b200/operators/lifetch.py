@@ -354,7 +354,8 @@ class LIFetch:
         self.worker_status = allocate("worker_status", (b, 32), torch.int32)
         self.times = allocate("times", (b * 256,), torch.int64)
         self.li_status = allocate("li_status", (1,), torch.int32)
-        self.topk_histogram = allocate("topk_histogram", (b * shape.queries, 4096), torch.int32)
+        # TopK scratch is optional: without it the forward selects with the sampled-pivot kernel
+        self.topk_histogram = None
         self.dense_shadow = allocate("dense_shadow", (b, 2 * self.history), torch.int32,
                                      lambda: ops.make_shadow(b, self.history, device))
         workspace = _lib.Workspace(
@@ -365,7 +366,7 @@ class LIFetch:
             resident=self.resident, options=q_workers << 16, max_events=CHANGE_CAPACITY, query_bitmaps=0,
             query_errors=0, update_bindings=update.bindings.data_ptr(), dense_shadow=self.dense_shadow.data_ptr(),
             packed_fetch=0, gather_out=0 if rotating.gather_output is None else rotating.gather_output.data_ptr(),
-            topk_scores=0, li_status=self.li_status.data_ptr(), topk_histogram=self.topk_histogram.data_ptr(), topk_split=0)
+            topk_scores=0, li_status=self.li_status.data_ptr(), topk_histogram=0, topk_split=0)
         self.workspace = _host_blob(torch, bytes(workspace))
         words = [x.data_ptr() for x in rotating.arguments] + [self.workspace.data_ptr()]
         rotating.bindings = torch.from_numpy(np.asarray(words, dtype="<u8").view("<i8").copy())

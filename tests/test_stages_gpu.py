@@ -192,6 +192,21 @@ def test_topk_long_row_and_base_index(device):
     _topk_check(scores, key_lengths, key_lengths.reshape(-1, 1).copy(), device, base_index=131072 * 3)
 
 
+@pytest.mark.parametrize("stride", [200704, 300032])
+def test_topk_wide_rows(stride, device):
+    """Rows beyond 131072 scores: 32 scores per thread in the cluster kernel, and (beyond 262144) the
+    one-CTA-per-row kernel. A constant row overflows every candidate list; a two-valued row puts the cut
+    inside a run of ties that spans all eight slices."""
+    rng = np.random.default_rng(stride)
+    rows = [rng.standard_normal(stride).astype(np.float32),
+            np.full(stride, 0.25, np.float32),
+            rng.integers(0, 2, stride).astype(np.float32),
+            (rng.standard_normal(stride) * np.exp(rng.uniform(-3, 3, stride))).astype(np.float32)]
+    scores = np.stack(rows)
+    key_lengths = np.array([stride, stride, stride - 5, stride // 2 + 1], np.int32)
+    _topk_check(scores, key_lengths, key_lengths.reshape(-1, 1).copy(), device, base_index=7)
+
+
 def test_topk_merge_equals_unsharded(device):
     """Sequence sharding: per-shard top-2048 + merge == top-2048 of the whole row (canonical order)."""
     rng = np.random.default_rng(3)
