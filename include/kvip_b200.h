@@ -33,6 +33,11 @@ extern "C" {
 #define KVIP_BLOCK_TOKENS 128u       /* paged Index cache block */
 #define KVIP_INDEX_WIDTH 128u        /* d_I */
 #define KVIP_TOPK_SPLIT_WORDS 20544u /* u32 words of TopK scratch per score row for the multi-CTA path */
+/* bits of KvipWorkspace.options (bits 0-15: prefetch limit, 16-23: resolver workers) */
+#define KVIP_OPTION_DIAGNOSTICS 0x80000000u
+#define KVIP_OPTION_DEFERRED_FETCH 0x40000000u /* descriptors only: no fetch, no gather */
+#define KVIP_OPTION_SELECT_ONLY 0x20000000u    /* LI score -> TopK -> resolver, then return */
+#define KVIP_OPTION_COMMIT_ONLY 0x10000000u    /* the rest of a SELECT_ONLY call: outputs -> exchange -> fetch (-> gather) */
 #define KVIP_BAD_ARGUMENT 100000u
 #define KVIP_CUDA_ERROR_BASE 200000u
 
@@ -335,7 +340,8 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
   uint64_t query_bitmaps, query_errors, update_bindings;
   uint64_t dense_shadow, packed_fetch;
   uint64_t gather_out, topk_scores, li_status, topk_histogram, topk_split;
-  uint8_t reserved[72];
+  uint64_t slots_ready_event;   /* optional cudaEvent_t recorded on the stream once the output rows are written */
+  uint8_t reserved[64];
 } KvipWorkspace;
 
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,

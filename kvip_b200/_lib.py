@@ -10,6 +10,8 @@ u32, i32, u64, i64, vp, f32 = (ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64,
                                ctypes.c_void_p, ctypes.c_float)
 
 TOPK, SLOTS, LRU_SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS, MAX_QUERIES = 2048, 8192, 2048, 10240, 128, 4
+OPTION_DIAGNOSTICS, OPTION_DEFERRED_FETCH = 0x80000000, 0x40000000
+OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY = 0x20000000, 0x10000000
 TOPK_SPLIT_WORDS = 20544
 BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
@@ -103,8 +105,8 @@ class Workspace(ctypes.Structure):
         "context", "keys", "scales", "addresses", "logical_ids", "hot_valid", "flags", "events_src", "events_dst",
         "worker_status", "times")] + [(n, u32) for n in ("history", "resident", "options", "max_events")] + [
             (n, u64) for n in ("query_bitmaps", "query_errors", "update_bindings", "dense_shadow", "packed_fetch",
-                               "gather_out", "topk_scores", "li_status", "topk_histogram", "topk_split")] + [
-                                   ("reserved", ctypes.c_uint8 * 72)]
+                               "gather_out", "topk_scores", "li_status", "topk_histogram", "topk_split",
+                               "slots_ready_event")] + [("reserved", ctypes.c_uint8 * 64)]
 
 
 _STAGES = {

@@ -10,7 +10,8 @@ uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream);
 uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream);
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream);
 
-uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream);
+uint32_t launch_resolve_requests(const KvipResolveArgs& a, cudaStream_t stream);
+uint32_t launch_publish_outputs(const KvipResolveArgs& a, cudaStream_t stream);
 uint32_t launch_exchange(const KvipExchangeArgs& a, cudaStream_t stream);
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream);
 uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream);
@@ -112,6 +113,9 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const KvipRuntimeShape& s = *shape;
   uint32_t rc;
+  const bool select_phase = !(ws->options & KVIP_OPTION_COMMIT_ONLY);
+  const bool commit_phase = !(ws->options & KVIP_OPTION_SELECT_ONLY);
+  KVIP_REQUIRE(select_phase || commit_phase, "forward: SELECT_ONLY and COMMIT_ONLY exclude each other");
 
   KvipLiArgs li{};
   li.query = ptr<const void>(bind[0]); li.keys = ptr<const void>(bind[1]); li.weights = ptr<const void>(bind[2]);
@@ -123,8 +127,10 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   li.scoreMode = s.scoreMode; li.ctas = s.smCount;
   KVIP_REQUIRE(li.query && li.keys && li.weights && li.key_lengths && li.query_ends && li.block_table && li.scores && li.status,
                "forward: an LI operand is unbound");
-  rc = s.liVariant ? launch_li_score_simt(li, stream) : launch_li_score(li, stream);
-  if (rc) return rc;
+  if (select_phase) {
+    rc = s.liVariant ? launch_li_score_simt(li, stream) : launch_li_score(li, stream);
+    if (rc) return rc;
+  }
 
   KvipTopkArgs tk{};
   tk.scores = li.scores; tk.key_lengths = li.key_lengths; tk.query_ends = li.query_ends;
@@ -133,7 +139,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   tk.split_scratch = ptr<uint32_t>(ws->topk_split);
   tk.rows = s.batch * s.queries; tk.queries = s.queries; tk.scoreStride = s.scoreStride; tk.base_index = 0;
   KVIP_REQUIRE(tk.topk, "forward: the TopK output is unbound");
-  if ((rc = launch_topk(tk, stream))) return rc;
+  if (select_phase && (rc = launch_topk(tk, stream))) return rc;
 
   KvipResolveArgs rs{};
   rs.topk = tk.topk; rs.row_owners = ptr<const int32_t>(ctx->row_owners); rs.hot_valid = ptr<const int32_t>(ctx->hot_valid);
@@ -155,7 +161,12 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
                    rs.changes && rs.change_slots && rs.change_count && rs.events_src && rs.events_dst && rs.query_counts &&
                    rs.fetch_sources && rs.fetch_destinations && rs.row_status, "forward: a resolver operand is unbound");
   KVIP_REQUIRE(rs.tail_bounds == nullptr, "forward: ABC tail bounds are not supported by this build");
-  if ((rc = launch_resolve(rs, stream))) return rc;
+  if (select_phase && (rc = launch_resolve_requests(rs, stream))) return rc;
+  if (!commit_phase) return 0;
+  if ((rc = launch_publish_outputs(rs, stream))) return rc;
+  if (ws->slots_ready_event &&
+      cudaEventRecord(reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->slots_ready_event)), stream) != cudaSuccess)
+    return check_launch("forward: recording the slots-ready event");
 
   KvipExchangeArgs ex{};
   ex.keys = ptr<uint8_t>(upd[0]); ex.scales = ptr<float>(upd[1]); ex.addresses = ptr<int64_t>(upd[2]);
@@ -168,7 +179,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   KVIP_REQUIRE(ex.keys && ex.scales && ex.addresses && ex.hot_valid && ex.shadow && ex.status, "forward: an update operand is unbound");
   if ((rc = launch_exchange(ex, stream))) return rc;
 
-  if (!(ws->options & 0x40000000u)) {  // deferred fetch: descriptors only
+  if (!(ws->options & KVIP_OPTION_DEFERRED_FETCH)) {  // deferred fetch: descriptors only
     KvipFetchArgs ft{};
     ft.source_base = ptr<const uint8_t>(ctx->source_base); ft.fetch_sources = rs.fetch_sources;
     ft.fetch_destinations = rs.fetch_destinations; ft.query_counts = rs.query_counts; ft.row_owners = rs.row_owners;

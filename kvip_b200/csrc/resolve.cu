@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(256) publish_outputs(const KvipResolveArgs a) 
 
 }  // namespace
 
-uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream) {
+uint32_t launch_resolve_requests(const KvipResolveArgs& a, cudaStream_t stream) {
   const uint32_t words = (a.resident + 31u) >> 5;
   const size_t smem = (words + 2u * kBuckets + 33u + 8u) * sizeof(uint32_t);
   static bool configured = false;
@@ -276,13 +276,19 @@ uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream) {
   }
   resolve_requests<<<a.batch, kThreads, smem, stream>>>(a);
   count_launch();
-  if (uint32_t bad = check_launch("resolve_requests")) return bad;
-  if (a.logical_output && a.slot_output) {
-    publish_outputs<<<dim3(a.batch * a.queries, 8), 256, 0, stream>>>(a);
-    count_launch();
-    return check_launch("publish_outputs");
-  }
-  return 0;
+  return check_launch("resolve_requests");
+}
+
+uint32_t launch_publish_outputs(const KvipResolveArgs& a, cudaStream_t stream) {
+  if (!a.logical_output || !a.slot_output) return 0;
+  publish_outputs<<<dim3(a.batch * a.queries, 8), 256, 0, stream>>>(a);
+  count_launch();
+  return check_launch("publish_outputs");
+}
+
+uint32_t launch_resolve(const KvipResolveArgs& a, cudaStream_t stream) {
+  if (uint32_t bad = launch_resolve_requests(a, stream)) return bad;
+  return launch_publish_outputs(a, stream);
 }
 
 }  // namespace kvip

@@ -319,9 +319,15 @@ class IndexUpdate:
 class LIFetch:
     """`kvip.LIFetch(rotating, update)`: allocate once, then `__call__()` enqueues the whole
     LI -> TopK -> resolve -> Index exchange -> fetch (-> gather) chain with one C call
-    (reference operators/lifetch/streaming.py:9-146, forward.py:7-17)."""
+    (reference operators/lifetch/streaming.py:9-146, forward.py:7-17).
 
-    def __init__(self, rotating, update, *, q_workers=2):
+    With `lru=SlotLRU` the LRU feedback of the slots the step used is part of the call: it is enqueued on a
+    side stream as soon as the output rows are written and runs beside the fetch and the gather (the reference
+    feeds its numba LRU from the host after the step, cache/lru.py:87-96). `select()` and `commit()` are the
+    two halves of `__call__()` for callers that overlap host copies with the step: `select()` reads the query
+    inputs and writes no output row, `commit()` reads no query input."""
+
+    def __init__(self, rotating, update, *, q_workers=2, lru=None):
         if rotating.device != update.device:
             raise ValueError("Fetch and Index update must use the same device")
         if update.bindings.numel() != 28:
@@ -334,6 +340,16 @@ class LIFetch:
         self.batch, self.history, self.resident = shape.batch, shape.history, shape.resident
         self.shape_pointer = ctypes.byref(shape)
         self.q_workers, self.prefetch_limit = q_workers, 0
+        self.lru = lru
+        self._slots_ready = self._lru_done = self._side = None
+        if lru is not None:
+            if lru.device != rotating.device or lru.rows_count != self.batch:
+                raise ValueError("the SlotLRU must have one row per request on the cache device")
+            current = torch.cuda.current_stream(rotating.device)
+            self._side = torch.cuda.Stream(rotating.device)
+            self._slots_ready, self._lru_done = torch.cuda.Event(), torch.cuda.Event()
+            self._slots_ready.record(current)   # an event has no handle before its first record
+            self._lru_done.record(current)
         library = rotating.library
         self.resolver_cores, flag_count = int(library.kvip_streaming_resolver_cores()), int(library.kvip_streaming_flag_count())
         if self.resolver_cores != 3 or flag_count != 16:
@@ -366,7 +382,8 @@ class LIFetch:
             resident=self.resident, options=q_workers << 16, max_events=CHANGE_CAPACITY, query_bitmaps=0,
             query_errors=0, update_bindings=update.bindings.data_ptr(), dense_shadow=self.dense_shadow.data_ptr(),
             packed_fetch=0, gather_out=0 if rotating.gather_output is None else rotating.gather_output.data_ptr(),
-            topk_scores=0, li_status=self.li_status.data_ptr(), topk_histogram=0, topk_split=0)
+            topk_scores=0, li_status=self.li_status.data_ptr(), topk_histogram=0, topk_split=0,
+            slots_ready_event=0 if self._slots_ready is None else int(self._slots_ready.cuda_event))
         self.workspace = _host_blob(torch, bytes(workspace))
         words = [x.data_ptr() for x in rotating.arguments] + [self.workspace.data_ptr()]
         rotating.bindings = torch.from_numpy(np.asarray(words, dtype="<u8").view("<i8").copy())
@@ -374,19 +391,39 @@ class LIFetch:
             rotating.bindings = rotating.bindings.pin_memory()
         self.set_options()
 
-    def __call__(self):
+    def _enqueue(self, phase):
         lease = self.rotating.lease
         stream = lease.check_stream() if lease is not None else self.torch.cuda.current_stream(self.rotating.device)
+        self._options_word[0] = self._options | phase   # host memory, read by the call below
         result = self.function(self.rotating.bindings.data_ptr(), self.update.bindings.data_ptr(),
                                self.workspace.data_ptr(), ctypes.c_void_p(stream.cuda_stream), self.shape_pointer,
                                self.q_workers)
+        self._options_word[0] = self._options
         if result:
             raise RuntimeError(f"streaming LIFetch launch failed: {result} ({_lib.last_error(self.rotating.library)})")
+        if self.lru is not None and phase != _lib.OPTION_SELECT_ONLY:
+            # fork: LRU feedback beside fetch + gather; join before the caller's next work on this stream
+            self._side.wait_event(self._slots_ready)
+            with self.torch.cuda.stream(self._side):
+                self.lru.commit(self.update.slot_output.view(self.batch, -1))
+                self._lru_done.record(self._side)
+            stream.wait_event(self._lru_done)
+
+    def __call__(self):
+        self._enqueue(0)
+
+    def select(self):
+        """First half: LI score -> TopK -> resolver. Reads the query inputs; writes no output row."""
+        self._enqueue(_lib.OPTION_SELECT_ONLY)
+
+    def commit(self):
+        """Second half: output rows -> Index exchange -> fetch (-> gather) and the LRU feedback."""
+        self._enqueue(_lib.OPTION_COMMIT_ONLY)
 
     def set_options(self, *, diagnostics=False, deferred_fetch=False):
         """Startup/profile-only update of the options word (byte 96 of the workspace record). The record
         is read when the call is enqueued: a graph captured earlier keeps the options it was captured with."""
-        value = (self.prefetch_limit | (self.q_workers << 16) | (0x80000000 if diagnostics else 0)
-                 | (0x40000000 if deferred_fetch else 0))
-        encoded = np.asarray([value], dtype="<u4").view("u1")
-        self.workspace[96:100].copy_(self.torch.from_numpy(encoded.copy()))
+        self._options = (self.prefetch_limit | (self.q_workers << 16) | (_lib.OPTION_DIAGNOSTICS if diagnostics else 0)
+                         | (_lib.OPTION_DEFERRED_FETCH if deferred_fetch else 0))
+        self._options_word = self.workspace.numpy()[96:100].view("<u4")   # same host memory as the record
+        self._options_word[0] = self._options

@@ -35,7 +35,8 @@ def _log_uniform(shape, lo, hi, generator, device):
 class DecodePipeline:
     def __init__(self, device, *, batch, queries=1, heads=64, history, resident, len_lo, len_hi, key_dtype="fp8",
                  weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
-                 score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0):
+                 score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0,
+                 overlap_lru=True):
         self.device = device = torch.device(device)
         self.batch, self.queries, self.heads, self.history, self.resident = batch, queries, heads, history, resident
         self.token_bytes, self.key_dtype = token_bytes, key_dtype
@@ -112,7 +113,9 @@ class DecodePipeline:
             query_inputs=inputs)
         self.lru = SlotLRU(device, rows=batch, slots=self.rotating.lru_slots, reserved_hot=self.rotating.reserved_hot)
         self.lru.resize(resident, resident)
-        self.forward = LIFetch(self.rotating, self.update)
+        # LRU feedback inside the call (beside fetch + gather) or, as in the reference, after it
+        self.overlap_lru = overlap_lru
+        self.forward = LIFetch(self.rotating, self.update, lru=self.lru if overlap_lru else None)
 
     def new_queries(self, seed):
         """Fresh projected queries / head weights for all rows, packed through QueryInputs.pack."""
@@ -137,7 +140,8 @@ class DecodePipeline:
         if ingest:
             self.ingest_new_tokens()
         self.forward()
-        self.lru.commit(self.update.slot_output.view(self.batch, -1))
+        if not self.overlap_lru:
+            self.lru.commit(self.update.slot_output.view(self.batch, -1))
 
     def ingest_new_tokens(self):
         """Write one new bf16 k_I row per query token into the Index cache (quantised to FP8 + scale)."""

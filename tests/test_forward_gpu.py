@@ -182,6 +182,31 @@ def test_forward_is_graph_capturable_and_allocation_free(device):
         assert after - before < (64 << 20)
 
 
+def test_two_phase_call_and_serial_lru_equal_the_fused_call(device):
+    """`select()` + `commit()` with the LRU feedback after the step (the reference's order) leave the same
+    outputs, Index rows, pool bytes and LRU order as `__call__()` with the feedback enqueued beside fetch and
+    gather."""
+    config = dict(batch=3, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=656, seed=11, host_pool=False, fill_payload=True)
+    fused = DecodePipeline(device, **config)
+    split = DecodePipeline(device, overlap_lru=False, **config)
+    for step in range(4):
+        for p in (fused, split):
+            p.new_queries(100 + step)
+        fused.step()
+        split.forward.select()
+        split.forward.commit()
+        split.lru.commit(split.update.slot_output.view(split.batch, -1))
+        torch.cuda.synchronize()
+        assert torch.equal(fused.update.outputs, split.update.outputs)
+        assert torch.equal(fused.gather_out, split.gather_out)
+        assert torch.equal(fused.pool_hbm, split.pool_hbm)
+        assert torch.equal(fused.storage.logical_ids, split.storage.logical_ids)
+        assert torch.equal(fused.lru.order, split.lru.order)
+        assert torch.equal(fused.rotating.lru_slots, split.rotating.lru_slots)
+        assert int(fused.update.status.abs().sum()) == 0
+
+
 def test_forward_rejects_mismatched_shape(device):
     config = dict(batch=2, queries=1, heads=64, history=4096, resident=2048, len_lo=3000, len_hi=4096, key_dtype="fp8",
                   weight_dtype="bf16", token_bytes=1152, seed=3, host_pool=False, gather=False)
