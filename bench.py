@@ -217,7 +217,7 @@ def run_ours(args):
         dev_w, dev_s, dev_pos = (torch.empty_like(x, device=device) for x in (host_w, host_s, host_pos))
         host_out = torch.empty((2, T, 1, 2048), dtype=torch.int32).pin_memory()
 
-        def e2e_step():
+        def serial_step():  # everything on one stream, one after the other
             dev_q.view(torch.uint8).copy_(host_q, non_blocking=True)
             dev_w.copy_(host_w, non_blocking=True)
             dev_s.copy_(host_s, non_blocking=True)
@@ -228,9 +228,27 @@ def run_ours(args):
             host_out.copy_(p.update.outputs, non_blocking=True)
 
         for _ in range(3):
-            e2e_step()
+            serial_step()
         barrier()
-        e2e_elapsed = time_region(torch, stream, e2e_step, args.steps)
+        serial_elapsed = time_region(torch, stream, serial_step, args.steps)
+        barrier()
+
+        # the same work per step through HostDecodeLoop: copies overlap the neighbouring steps' kernels
+        from kvip_b200 import HostDecodeLoop
+        loop = HostDecodeLoop(torch, p.forward, inputs, p.update.outputs, host_query=host_q.view(torch.float8_e4m3fn),
+                              host_weights=host_w, host_scale=host_s, host_positions=host_pos, host_outputs=host_out)
+
+        def looped_steps():
+            loop.step()
+            if loop.steps % args.steps == 0:
+                loop.drain()  # the timed region ends when the last read-back has landed
+
+        for _ in range(3):
+            loop.step()
+        loop.drain()
+        loop.steps = 0
+        barrier()
+        e2e_elapsed = time_region(torch, stream, looped_steps, args.steps)
         barrier()
         h2d = sum(x.numel() * x.element_size() for x in (host_q, host_w, host_s, host_pos))
         d2h = host_out.numel() * host_out.element_size()
@@ -239,10 +257,10 @@ def run_ours(args):
         if world == 1 and not args.no_miss_path:
             miss_path = measure_miss_path(torch, ops, p, stream, args)
 
-    worst = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
+    worst = torch.tensor([elapsed, e2e_elapsed, serial_elapsed], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed = (float(x) for x in worst.tolist())
+    elapsed, e2e_elapsed, serial_elapsed = (float(x) for x in worst.tolist())
     hbm_peak, peak_kind = peaks()
     key_bytes = 1 if p.key_dtype == "fp8" else 2
     li_bytes = li_algorithmic_bytes(p.lengths, p.queries, p.heads, key_bytes)
@@ -260,7 +278,10 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (keys %.0f MB per step)" % (li_bytes / 1e6),
                    "miss_source": "device tensor" if args.device_source else "pinned mapped host pool"},
         "e2e": {"value": world * tokens * args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3,
+                "api": "HostDecodeLoop.step: copies of steps i-1 / i+1 overlap the kernels of step i",
+                "one_stream": {"value": world * tokens * args.steps / serial_elapsed,
+                               "ms_per_step": serial_elapsed / args.steps * 1e3}},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",

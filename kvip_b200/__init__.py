@@ -19,6 +19,7 @@ _EXPORTS = {
     "CudaBinding": ("operators.lifetch", "CudaBinding"),
     "IndexUpdate": ("operators.lifetch", "IndexUpdate"),
     "HostKVPool": ("operators.lifetch", "HostKVPool"),
+    "HostDecodeLoop": ("host_loop", "HostDecodeLoop"),
     "FusedQueryInputs": ("inputs", "QueryInputs"),
     "FusedWorkspace": ("operators.lifetch", "LIFetchWorkspace"),
 }

@@ -207,6 +207,48 @@ def test_two_phase_call_and_serial_lru_equal_the_fused_call(device):
         assert int(fused.update.status.abs().sum()) == 0
 
 
+def _host_inputs(p):
+    inputs = p.workspace.inputs
+    pin = lambda t: t.cpu().pin_memory()  # noqa: E731
+    return dict(host_query=pin(inputs.query.view(torch.uint8)).view(torch.float8_e4m3fn), host_weights=pin(inputs.weights),
+                host_scale=pin(inputs.scale), host_positions=pin(p.positions))
+
+
+@pytest.mark.parametrize("prefetch", [False, True])
+def test_host_decode_loop_equals_serial_steps(prefetch, device):
+    """Copies overlapped with neighbouring steps (and both halves replayed from graphs) change nothing: the
+    rows read back on the host, the pool and the LRU order equal those of steps issued on one stream. Without
+    prefetch the queries change every step; with it they are the same every step, as the caller must have
+    the next step's inputs in host memory one step early."""
+    from kvip_b200 import HostDecodeLoop
+    config = dict(batch=4, queries=1, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=656, seed=21, host_pool=False, fill_payload=True, permute_owners=False)
+    serial, looped = DecodePipeline(device, **config), DecodePipeline(device, **config)
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        host = _host_inputs(serial)
+        host_out = torch.empty(tuple(looped.update.outputs.shape), dtype=torch.int32).pin_memory()
+        loop = HostDecodeLoop(torch, looped.forward, looped.workspace.inputs, looped.update.outputs,
+                              host_outputs=host_out, **host)
+        serial.step()   # the step the loop ran while it was built
+        for step in range(4):
+            if not prefetch:
+                serial.new_queries(300 + step)
+                stream.synchronize()
+                for name, tensor in _host_inputs(serial).items():
+                    host[name].view(torch.uint8).copy_(tensor.view(torch.uint8))
+            serial.step()
+            loop.step(prefetch_next=prefetch)
+            loop.drain()
+            stream.synchronize()
+            assert torch.equal(host_out, serial.update.outputs.cpu())
+            assert torch.equal(looped.update.outputs, serial.update.outputs)
+            assert torch.equal(looped.pool_hbm, serial.pool_hbm)
+            assert torch.equal(looped.lru.order, serial.lru.order)
+            assert torch.equal(looped.gather_out, serial.gather_out)
+    assert loop.steps == 4 and loop.h2d_bytes > 0 and loop.d2h_bytes == host_out.numel() * 4
+
+
 def test_forward_rejects_mismatched_shape(device):
     config = dict(batch=2, queries=1, heads=64, history=4096, resident=2048, len_lo=3000, len_hi=4096, key_dtype="fp8",
                   weight_dtype="bf16", token_bytes=1152, seed=3, host_pool=False, gather=False)
