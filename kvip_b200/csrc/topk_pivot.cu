@@ -31,12 +31,6 @@ __device__ __forceinline__ uint32_t isqrt_ceil(uint32_t v) {
   return r;
 }
 
-#ifdef KVIP_TOPK_DEBUG
-__device__ unsigned long long g_debug[16];
-#define DBG_T(i) do { __syncthreads(); if (blockIdx.x == 0 && threadIdx.x == 0) g_debug[i] = clock64(); } while (0)
-#else
-#define DBG_T(i)
-#endif
 __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) {
   extern __shared__ uint32_t list[];  // [kPivotCandidates] keys, then [kPivotCandidates] positions
   __shared__ uint32_t hist[4096];
@@ -64,7 +58,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   }
   const uint32_t L = static_cast<uint32_t>(valid_len);
 
-  DBG_T(0);
   // ---- 1. pivot from a sample ------------------------------------------------------------------------
   for (uint32_t i = tid; i < 4096; i += kThreads) hist[i] = 0;
   __syncthreads();
@@ -109,7 +102,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     pivot_key = found[0] << 20;
   }
 
-  DBG_T(1);
   // ---- 2. one pass over the row: keep key >= pivot, in position order ----------------------------------
   // The filter is instruction-bound (one SM works through the whole row), so the test is one float compare
   // per score: key(x) >= pivot_key  <=>  !(x < pivot_value), except that -0.0 also passes a pivot of +0.0 and
@@ -196,10 +188,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     }
   }
   __syncthreads();
-  DBG_T(2);
-#ifdef KVIP_TOPK_DEBUG
-  if (threadIdx.x == 0) { atomicAdd(&g_debug[8], 1ull); atomicAdd(&g_debug[9], (unsigned long long)kept); if (kept < kTop || kept > kPivotCandidates) atomicAdd(&g_debug[10], 1ull); }
-#endif
   if (kept < kTop || kept > kPivotCandidates) {  // block-uniform: the sample misled, or the row is (nearly) constant
     select_row(a, row, nullptr);
     return;
@@ -250,7 +238,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   const uint32_t need_eq = remaining;  // how many == kth positions are taken
   const uint32_t count_gt = kTop - need_eq;
 
-  DBG_T(3);
   // ---- 4. emission: the list is in position order ---------------------------------------------------------
   const uint32_t groups = (kept + kThreads - 1u) / kThreads;  // groups of 32 list entries per warp
   const uint32_t run = warp * (32u * groups);
@@ -284,18 +271,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     g += __popc(mask_gt);
     q += __popc(mask_eq);
   }
-  DBG_T(4);
 }
 
 }  // namespace
-#ifdef KVIP_TOPK_DEBUG
-extern "C" void kvip_b200_debug_read(unsigned long long* host) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host, g_debug, sizeof(g_debug));
-  unsigned long long zero[16] = {};
-  cudaMemcpyToSymbol(g_debug, zero, sizeof(zero));
-}
-#endif
 
 uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
   constexpr int kSmem = static_cast<int>(2u * kPivotCandidates * sizeof(uint32_t));
