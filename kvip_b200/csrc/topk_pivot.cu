@@ -1,4 +1,4 @@
-// TopK-2048 of one score row by one CTA that reads the row once: pivot, filter, exact select.
+// TopK-2048 of one score row by one CTA (or a pair) that reads the row once: pivot, filter, exact select.
 //
 // A full radix pass costs one shared-memory atomic per score, and those atomics (not the memory
 // traffic) are what a histogram-per-pass selection spends its time on. Here only a SAMPLE of the row
@@ -13,8 +13,15 @@
 // would hold fewer than 2048 keys (an unlucky sample) or more than fit (a constant row) is handed to
 // the three-passes-over-the-row selection (topk_core::select_row). The result is therefore always the
 // exact, deterministic TopK; the sample only decides how fast.
+//
+// The kernel is instruction-bound (one SM works through a whole row), so while two CTAs per row still fit
+// the GPU in one wave it runs as clusters of two: each CTA samples and filters half of the row, rank 0
+// appends its partner's list through distributed shared memory and finishes alone.
+#include <cooperative_groups.h>
 #include "common.cuh"
 #include "topk_core.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace kvip {
 namespace {
@@ -33,14 +40,20 @@ __device__ __forceinline__ uint32_t isqrt_ceil(uint32_t v) {
 
 __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) {
   extern __shared__ uint32_t list[];  // [kPivotCandidates] keys, then [kPivotCandidates] positions
-  __shared__ uint32_t hist[4096];
+  __shared__ __align__(16) uint32_t hist[4096];
   __shared__ uint32_t scan_scratch[33];
   __shared__ uint32_t found[2];
   __shared__ uint32_t table[kRoundChunks * 32u];  // scores that passed the filter per (chunk, warp) of a round
+  __shared__ uint32_t kept_here;                  // what this CTA's filter kept (read by the partner)
   uint32_t* list_key = list;
   uint32_t* list_pos = list + kPivotCandidates;
 
-  const uint32_t row = blockIdx.x;
+  // One CTA per row, or a cluster of two when the GPU has SMs to spare: each samples and filters half of the
+  // row, rank 0 appends its partner's list to its own (distributed shared memory) and finishes alone. Every
+  // cluster barrier below is reached by both CTAs unconditionally.
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t ranks = cluster.num_blocks(), rank = cluster.block_rank();
+  const uint32_t row = blockIdx.x / ranks;
   const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, below = (1u << lane) - 1u;
   const uint32_t b = row / a.queries;
   int32_t valid_len = min(a.key_lengths[b], a.query_ends[row]);
@@ -48,7 +61,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
   float* out_scores = a.topk_scores ? a.topk_scores + static_cast<uint64_t>(row) * kTop : nullptr;
   const float* scores = a.scores + static_cast<uint64_t>(row) * a.scoreStride;
-  if (valid_len <= static_cast<int32_t>(kTop)) {
+  if (valid_len <= static_cast<int32_t>(kTop)) {  // the same for both CTAs of a pair
+    if (rank == 0)
     for (uint32_t i = tid; i < kTop; i += kThreads) {
       const bool live = static_cast<int32_t>(i) < valid_len;
       out[i] = live ? static_cast<int32_t>(i + a.base_index) : -1;
@@ -69,7 +83,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     bool ok[kPerWarp];
 #pragma unroll
     for (uint32_t i = 0; i < kPerWarp; ++i) {  // all loads first: one memory latency, not kPerWarp
-      const uint32_t s = warp + i * (kThreads / 32u);
+      const uint32_t mine = warp + i * (kThreads / 32u);       // a pair shares the sample lines: rank r takes
+      const uint32_t s = (mine % ranks == rank) ? mine : ~0u;  // those with s % 2 == r
       const uint32_t line = s < sample_lines ? (s * lines) / sample_lines : 0u;
       const uint32_t position = line * 32u + lane;
       ok[i] = s < sample_lines && position < L;
@@ -78,12 +93,15 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
 #pragma unroll
     for (uint32_t i = 0; i < kPerWarp; ++i) hist_add(hist, ok[i], sortable_key(x[i]) >> 20);
   }
-  __syncthreads();
+  cluster.sync();  // both sample histograms are complete (a block barrier when there is no partner)
   uint32_t pivot_key;
   {
     const uint32_t group = 1023u - tid;  // thread i owns the 4 highest unclaimed bins
-    const uint32_t c0 = hist[group * 4u], c1 = hist[group * 4u + 1u], c2 = hist[group * 4u + 2u],
-                   c3 = hist[group * 4u + 3u];
+    uint32_t c0 = hist[group * 4u], c1 = hist[group * 4u + 1u], c2 = hist[group * 4u + 2u], c3 = hist[group * 4u + 3u];
+    if (ranks == 2u) {
+      const uint4 other = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(hist, rank ^ 1u) + group * 4u);
+      c0 += other.x; c1 += other.y; c2 += other.z; c3 += other.w;
+    }
     uint32_t sampled;
     uint32_t above = block_exclusive_scan(c0 + c1 + c2 + c3, scan_scratch, &sampled);
     // expected rank of the 2048th key inside the sample, plus four standard deviations
@@ -117,7 +135,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     const float4* row4 = reinterpret_cast<const float4*>(scores);
     const uint32_t vectors = (L + 3u) >> 2;
     constexpr uint32_t kChunk = kThreads * 16u;
-    for (uint32_t round = 0; round < L; round += kRoundChunks * kChunk) {
+    const uint32_t chunks_each = ((L + kChunk - 1u) / kChunk + ranks - 1u) / ranks;   // rank 0: the first half
+    const uint32_t begin = min(L, rank * chunks_each * kChunk), end = min(L, (rank + 1u) * chunks_each * kChunk);
+    for (uint32_t round = begin; round < end; round += kRoundChunks * kChunk) {
       uint32_t masks[kRoundChunks / 2];
 #pragma unroll
       for (uint32_t c = 0; c < kRoundChunks / 2; ++c) masks[c] = 0;
@@ -125,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
       for (uint32_t c = 0; c < kRoundChunks; ++c) {
         const uint32_t start = round + c * kChunk;
         uint32_t mask = 0;
-        if (start < L) {  // block-uniform
+        if (start < end) {  // block-uniform
           const uint32_t run = start + warp * 512u;  // first position of this warp's run
           float4 x[4];
 #pragma unroll
@@ -188,6 +208,19 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     }
   }
   __syncthreads();
+  if (ranks == 2u) {
+    // hand the second half's list to rank 0: positions are already in order, rank 0's come first
+    if (tid == 0) kept_here = kept;
+    cluster.sync();  // both lists and counts are complete
+    const uint32_t theirs = *cluster.map_shared_rank(&kept_here, rank ^ 1u);
+    if (rank == 0 && kept <= kPivotCandidates && theirs <= kPivotCandidates - kept) {
+      const uint32_t* remote = cluster.map_shared_rank(list_pos, 1u);
+      for (uint32_t i = tid; i < theirs; i += kThreads) list_pos[kept + i] = remote[i];
+    }
+    kept = (kept > kPivotCandidates || theirs > kPivotCandidates) ? kPivotCandidates + 1u : kept + theirs;
+    cluster.sync();  // rank 0 has read its partner's shared memory
+    if (rank != 0) return;
+  }
   if (kept < kTop || kept > kPivotCandidates) {  // block-uniform: the sample misled, or the row is (nearly) constant
     select_row(a, row, nullptr);
     return;
@@ -283,7 +316,28 @@ uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
       return check_launch("topk_pivot attribute");
     configured = true;
   }
-  topk_pivot<<<a.rows, kThreads, kSmem, stream>>>(a);
+  // two CTAs per row while that still fits the GPU in one wave
+  static int sm_count = 0;
+  if (!sm_count) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+      sm_count = 148;
+  }
+  const unsigned ranks = 2u * a.rows <= static_cast<unsigned>(sm_count) ? 2u : 1u;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a.rows * ranks, 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = kSmem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = ranks;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, topk_pivot, a) != cudaSuccess) return check_launch("topk_pivot");
   count_launch();
   return check_launch("topk_pivot");
 }

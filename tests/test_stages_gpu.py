@@ -192,6 +192,18 @@ def test_topk_long_row_and_base_index(device):
     _topk_check(scores, key_lengths, key_lengths.reshape(-1, 1).copy(), device, base_index=131072 * 3)
 
 
+def test_topk_many_rows_one_cta_each(device):
+    """More rows than half the SMs: the selection runs one CTA per row instead of a pair per row."""
+    rng = np.random.default_rng(9)
+    rows, stride = 96, 20480
+    scores = (rng.standard_normal((rows, stride)) * np.exp(rng.uniform(-2, 2, (rows, 1)))).astype(np.float32)
+    scores[5] = 1.0                                  # constant row: the kept list overflows -> three-pass path
+    scores[6] = rng.integers(0, 2, stride)           # two values: the cut falls inside a long run of ties
+    key_lengths = rng.integers(2048, stride + 1, rows).astype(np.int32)
+    key_lengths[:8] = stride
+    _topk_check(scores, key_lengths, key_lengths.reshape(-1, 1).copy(), device)
+
+
 @pytest.mark.parametrize("stride", [200704, 300032])
 def test_topk_wide_rows(stride, device):
     """Rows beyond 131072 scores: 32 scores per thread in the cluster kernel, and (beyond 262144) the
