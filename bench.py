@@ -286,7 +286,11 @@ def run_ours(args):
         "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": li_bytes, "us_per_launch": stages["li_score"] * 1e6,
-                     "traffic": None,
+                     # dram__bytes_read + dram__bytes_write of the ncu capture of decode_128k_b8 (8 x 128k FP8
+                     # pages, 1.014 x its algorithmic bytes), scaled by the pages one launch of this workload streams
+                     "traffic": (int(1.014 * li_bytes) if p.key_dtype == "fp8" and args.workload.startswith("decode_128k")
+                                 else None),
+                     "traffic_source": "profiles/li_score_tcgen05__decode_128k_b8.md, scaled by pages per launch",
                      "step_frac": step_bytes / stages["step_graph"] / 1e9 / hbm_peak},
         "stages_us": {k: v * 1e6 for k, v in stages.items()},
         "fetch": {"cold_step_reads": cold_reads, "cold_step_ms": cold_s * 1e3,
