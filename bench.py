@@ -435,13 +435,103 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_prefill(args):
+    """`--workload prefill_16k_128k`: LI score + TopK of one request's 16384-token query chunk against its causal
+    131072-token context (FP8), the dense-contraction stress of the benchmark configs. The reference packs at
+    most four query slots per row, so the chunk runs as 4 launches of 1024 rows x 4 queries that all read the
+    same key pages; the score rows of one launch (2.1 GB) are reused by the next."""
+    import torch
+
+    from kvip_b200 import ops
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    chunk, context, heads, rows = 16384, 131072, 64, 4096
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+    log_uniform = lambda shape: torch.exp(torch.rand(shape, generator=g, device=device) * 4.6052 - 6.9078)  # noqa: E731
+    keys = (torch.randn((context, 128), generator=g, device=device) * 8).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    key_scale = log_uniform((context,))
+    query = (torch.randn((chunk, heads, 128), generator=g, device=device) * 8).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    query_scale = log_uniform((chunk, heads))
+    weights = (torch.randn((chunk, heads), generator=g, device=device) / 8).to(torch.bfloat16)
+    batch = rows // 4
+    key_lengths = torch.full((batch,), context, dtype=torch.int32, device=device)
+    ends = (context - chunk + 1 + torch.arange(chunk, device=device)).to(torch.int32).view(chunk // 4, 4)
+    table = torch.arange(context // 128, dtype=torch.int32, device=device).repeat(batch, 1)
+    scores = torch.zeros((rows, context), dtype=torch.float32, device=device)
+    picked = torch.empty((chunk, 2048), dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    host_query = query.view(torch.uint8).cpu().pin_memory()
+    host_picked = torch.empty((chunk, 2048), dtype=torch.int32).pin_memory()
+    stream = torch.cuda.Stream(device)
+    lib = _load_counter()
+
+    def li(part):
+        lo, hi = part * rows, (part + 1) * rows
+        ops.li_score(query[lo:hi], keys, weights[lo:hi], query_scale[lo:hi], key_scale, key_lengths,
+                     ends[lo // 4:hi // 4], table, scores, status=status)
+
+    def step(li_only=False):
+        for part in range(chunk // rows):
+            li(part)
+            if not li_only:
+                lo, hi = part * rows, (part + 1) * rows
+                ops.topk(scores, key_lengths, ends[lo // 4:hi // 4], picked[lo:hi])
+
+    def e2e_step():
+        query.view(torch.uint8).copy_(host_query, non_blocking=True)
+        step()
+        host_picked.copy_(picked, non_blocking=True)
+
+    steps = max(1, min(args.steps, 5))
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+        stream.synchronize()
+        if int(status.item()):
+            raise RuntimeError(f"device status {int(status.item())}")
+        with ClockSampler(device.index or 0) as sampler:
+            before = lib.kvip_b200_launch_count()
+            elapsed = time_region(torch, stream, step, steps)
+            launches = lib.kvip_b200_launch_count() - before
+            li_elapsed = time_region(torch, stream, lambda: step(li_only=True), steps)
+            e2e_elapsed = time_region(torch, stream, e2e_step, steps)
+        clocks = sampler.result
+    flops = 2.0 * heads * 128 * float(ends.to(torch.float64).sum().item())
+    peak_path = ROOT / "MEASURED_PEAKS.json"
+    bf16_peak = float(json.loads(peak_path.read_text())["bf16_tflops"]) if peak_path.exists() else 1590.0
+    achieved = flops / (li_elapsed / steps) / 1e12
+    print(json.dumps({
+        "metric": "LI+TopK query tokens/s, chunked prefill 16384 x 131072 causal", "value": chunk * steps / elapsed,
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": elapsed / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "chunk": chunk, "context": context, "index_heads": heads, "topk": 2048,
+                   "launches_per_chunk": chunk // rows, "l2": "score rows of one launch (2.1 GB) exceed L2"},
+        "e2e": {"value": chunk * steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": host_query.numel(),
+                "d2h_bytes_per_step": host_picked.numel() * 4, "ms_per_step": e2e_elapsed / steps * 1e3},
+        "gpu_launches": launches,
+        "roofline": {"kernel": "li_score_tcgen05", "bound": "tensor", "achieved": achieved, "peak": 2 * bf16_peak,
+                     "unit": "TFLOP/s", "frac": achieved / (2 * bf16_peak),
+                     "peak_kind": "2 x the measured bf16 burst figure (no FP8 figure was measured on this pool)",
+                     "flops_per_chunk": flops, "ms_li_per_chunk": li_elapsed / steps * 1e3, "traffic": None},
+        "clocks": clocks,
+    }), flush=True)
+
+
+def _load_counter():
+    from kvip_b200 import _lib
+    return _lib.load_library()
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="decode_128k_b64")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k"], default="decode_128k_b64")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")
     parser.add_argument("--device-source", action="store_true", help="serve misses from HBM instead of the host pool")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -452,6 +542,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill_16k_128k":
+        run_prefill(args)
     else:
         run_ours(args)
 

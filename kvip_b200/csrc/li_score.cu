@@ -18,7 +18,7 @@
 //     tensor memory), warps 5-20 = four epilogue groups that take tiles round-robin; key
 //     stages and a ring of up to eight accumulator buffers in tensor memory are handed over
 //     with mbarriers. The number of issuers divides the number of key stages and of
-//     accumulators, and the number of epilogue groups divides the number of accumulators, so
+//     accumulators, and the number of units reduced at once divides the number of accumulators, so
 //     every use of one stage or accumulator is waited for by the same thread, in order: a
 //     parity wait by a thread that runs a whole phase ahead of the barrier would pass at once;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
@@ -213,11 +213,18 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t H = a.heads, Q = a.queries, pages = a.pagesPerRequest;
-  // accumulator ring in tensor memory: stride = columns one tile can need, rounded to a power of two
-  const uint32_t acc_stride = Q * H <= 32u ? 32u : (Q * H <= 64u ? 64u : (Q * H <= 128u ? 128u : 256u));
-  const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);   // 2, 4 or 8
-  const uint32_t issuers = ((S | acc_count) & 3u) == 0u ? 4u : (((S | acc_count) & 1u) == 0u ? 2u : 1u);
-  const uint32_t groups = min(kEpilogueGroups, acc_count);
+  // A tile (key page x query rows of the request) is handed over in UNITS of at most 128 accumulator columns:
+  // one unit per tile up to 128 (query, head) columns, two beyond (queries 0-1 and 2-3 at 64 heads). Four units
+  // fit tensor memory at 128 columns each, so MMA and reduction overlap even for the widest query tile.
+  const uint32_t halves = Q * H > 128u ? 2u : 1u;
+  const uint32_t unit_queries = halves == 2u ? 128u / H : Q;    // query slots per unit
+  const uint32_t acc_stride = Q * H <= 32u ? 32u : (Q * H <= 64u ? 64u : 128u);
+  const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);   // 4 or 8
+  // issuer w owns the units of the tiles with local index = w (mod issuers): the accumulators of those units
+  // must be the same every time round the ring, i.e. issuers * halves divides acc_count (and issuers divides S)
+  const uint32_t acc_tiles = acc_count / halves;
+  const uint32_t issuers = ((S | acc_tiles) & 3u) == 0u ? 4u : (((S | acc_tiles) & 1u) == 0u ? 2u : 1u);
+  const uint32_t groups = kEpilogueGroups;   // units reduced concurrently; divides acc_count (4 or 8)
 
   // ---- per-CTA schedule: tiles per request -> prefix sums (warp 0) -------------------
   if (warp == 0) {
@@ -250,7 +257,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   if (threadIdx.x == 64) {
     for (uint32_t i = 0; i < S; ++i) { mbar_init(bar(i), 1); mbar_init(bar(S + i), 1); }
     mbar_init(bar(kQFull), 1); mbar_init(bar(kQEmpty), issuers);
-    for (uint32_t i = 0; i < kMaxAcc; ++i) { mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128); }
+    for (uint32_t i = 0; i < kMaxAcc; ++i) { mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128u); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -337,34 +344,44 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       TileCursor cur(prefix, a.batch);
       uint32_t request = cur.seek(tile_begin), seq = 0;
       uint32_t t = tile_begin + w;
-      uint32_t stage = w, phase = 0, acc = w, acc_phase = 0;   // w < issuers <= min(S, acc_count)
+      uint32_t stage = w, phase = 0;                           // w < issuers <= S
+      uint32_t acc = w * halves, acc_phase = 0;                // first unit of tile w; w * halves < acc_count
       bool alive = true;
       while (alive) {
         const uint32_t request_end = min(prefix[request + 1], tile_end);
         if (!mbar_wait(bar(kQFull), seq & 1u, abort_flag)) break;
-        const uint32_t n = active_q[request] * H;
+        const uint32_t n = active_q[request] * H;              // live accumulator columns of this request
         const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
         bool issued = false;
         for (; t < request_end; t += issuers) {
-          if (!mbar_wait(bar(stage), phase, abort_flag) ||
-              !mbar_wait(bar(kAccEmpty + acc), acc_phase ^ 1u, abort_flag)) { alive = false; break; }
-          tcgen05_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * acc_stride;
+          if (!mbar_wait(bar(stage), phase, abort_flag)) { alive = false; break; }
+          for (uint32_t h = 0; h < halves; ++h) {
+            if (!mbar_wait(bar(kAccEmpty + acc + h), acc_phase ^ 1u, abort_flag)) { alive = false; break; }
+            const uint32_t first_column = h * 128u;
+            if (n <= first_column) {                 // no live query slot in this unit: nothing to compute
+              mbar_arrive(bar(kAccFull + acc + h));
+              continue;
+            }
+            const uint32_t columns = min(n - first_column, halves == 2u ? 128u : n);
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((columns >> 3) << 17) | ((128u >> 4) << 24);
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem_base + (acc + h) * acc_stride;
 #pragma unroll
-          for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
-            const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
-            const uint64_t db = umma_desc(q_smem + atom * q_atom_bytes);
+            for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom) {
+              const uint64_t da = umma_desc(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes);
+              const uint64_t db = umma_desc(q_smem + atom * q_atom_bytes + first_column * 128u);
 #pragma unroll
-            for (uint32_t k = 0; k < 4; ++k)  // 32 bytes of K per instruction
-              tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
+              for (uint32_t k = 0; k < 4; ++k)  // 32 bytes of K per instruction
+                tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
+            }
+            tcgen05_commit(bar(kAccFull + acc + h));   // accumulator ready for the epilogue
           }
-          tcgen05_commit(bar(S + stage));        // key stage free once these MMAs retire
-          tcgen05_commit(bar(kAccFull + acc));   // accumulator ready for the epilogue
+          if (!alive) break;
+          tcgen05_commit(bar(S + stage));              // key stage free once these MMAs retire
           issued = true;
           stage += issuers;
           if (stage >= S) { stage -= S; phase ^= 1u; }
-          acc += issuers;
+          acc += issuers * halves;
           if (acc >= acc_count) { acc -= acc_count; acc_phase ^= 1u; }
         }
         if (!alive) break;
@@ -377,9 +394,8 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     }
   } else {
     // ================= epilogue: groups of 4 warps, one token row per thread =================
-    // Group g reduces the tiles with (t - tile_begin) % kEpilogueGroups == g. One tile's reduction is a
-    // long dependent chain (tensor-memory load, 64 max+fma pairs, store), far longer than the time the
-    // next key page needs to arrive, so several tiles are reduced concurrently per SM.
+    // One unit's reduction is a long dependent chain (tensor-memory load, 64 max+fma pairs per query, store),
+    // far longer than the time the next key page needs to arrive, so several units are reduced concurrently.
     const uint32_t group = (warp - kFirstEpilogueWarp) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
     const uint32_t row = quad * 32u + lane;       // token row inside the page
@@ -398,17 +414,21 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (t >= tile_end || !a.key_scale) return 1.0f;
       return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
     };
+    // Group g reduces the units u = g (mod groups); unit u is half (u % halves) of tile u / halves.
     const uint32_t G = groups;
-    const uint32_t first = group < G ? tile_begin + group : tile_end;   // surplus groups stay idle
-    int32_t page_next = page_of(first);
-    float kscale = scale_of(first, page_next);
-    page_next = page_of(first + G);
-    uint32_t acc = group, acc_phase = 0;   // group < G <= acc_count
-    for (uint32_t t = first; t < tile_end; t += G) {
+    const uint32_t tiles_here = tile_end - tile_begin, units_here = tiles_here * halves;
+    auto tile_of = [&](uint32_t u) { return u < units_here ? tile_begin + u / halves : tile_end; };
+    const uint32_t first = group;
+    int32_t page_next = page_of(tile_of(first));
+    float kscale = scale_of(tile_of(first), page_next);
+    page_next = page_of(tile_of(first + G));
+    uint32_t acc = group % acc_count, acc_phase = 0;   // G divides acc_count: a group meets the same accumulators
+    for (uint32_t u = first; u < units_here; u += G) {
+      const uint32_t t = tile_begin + u / halves, h = u % halves;
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
-      const float kscale_next = scale_of(t + G, page_next);   // consumed next iteration
-      page_next = page_of(t + 2 * G);
+      const float kscale_next = scale_of(tile_of(u + G), page_next);   // consumed next iteration
+      page_next = page_of(tile_of(u + 2 * G));
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
         for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
@@ -422,13 +442,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(bar(kAccFull + acc), acc_phase, abort_flag))) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
-      for (uint32_t q = 0; q < nq; ++q) {
+      const uint32_t q_first = h * unit_queries, q_last = min(nq, q_first + unit_queries);
+      for (uint32_t q = q_first; q < q_last; ++q) {
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
         // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         for (uint32_t c = 0; c < H; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + q * H + c, v);
+          tmem_ld_32x32(taddr + (q - q_first) * H + c, v);
           tmem_ld_wait();
           const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
 #pragma unroll

@@ -99,6 +99,47 @@ def test_li_tcgen05_rings_wrap(queries, heads, key_dtype, stages, device):
         assert (np.abs(out - ref) <= rtol * np.abs(ref) + rtol * 1e-2 * scale).all(), (t, scale)
 
 
+@pytest.mark.parametrize("key_dtype", ["fp8", "bf16"])
+def test_li_tcgen05_ragged_query_slots_two_units(key_dtype, device):
+    """Four query slots of 64 heads are reduced as two 128-column units per key page; requests with one, two or
+    three live slots leave the second unit partly or wholly empty, and a request without live slots has no
+    tiles at all."""
+    case = workloads.li_case(seed=77, batch=5, queries=4, heads=64, len_lo=3000, len_hi=6000, key_dtype=key_dtype,
+                             weight_dtype="bf16", active=[3, 1, 4, 0, 2])
+    expected, _ = _li(case, device, simt=True)
+    expected = expected.cpu().numpy()
+    mask = _valid_mask(case, expected.shape[1])
+    rtol = 2e-3 if key_dtype == "bf16" else 1e-2
+    for kw in (dict(), dict(ctas=2), dict(ctas=3, stages=3)):
+        scores, _ = _li(case, device, **kw)
+        got = scores.cpu().numpy()
+        for t in range(got.shape[0]):
+            if not mask[t].any():
+                continue
+            ref, out = expected[t][mask[t]], got[t][mask[t]]
+            scale = np.abs(ref).max()
+            assert (np.abs(out - ref) <= rtol * np.abs(ref) + rtol * 1e-2 * scale).all(), (kw, t)
+
+
+def test_chunked_prefill_li_and_topk(device):
+    """The chunked-prefill configuration at test size: 128 query tokens of one request against a causal
+    8192-token context, four query slots per row, all rows reading the same key pages. Scores within the FP8
+    tolerance of the golden formula; TopK of the kernel's own scores bit-exact with the oracle's TopK of them."""
+    case = workloads.prefill_case(seed=3, chunk=128, context=8192)
+    expected = workloads.oracle_scores(case)
+    scores, t = _li(case, device)
+    got = scores.cpu().numpy()
+    mask = _valid_mask(case, expected.shape[1])
+    for row in range(got.shape[0]):
+        ref, out = expected[row][mask[row]], got[row][mask[row]]
+        scale = np.abs(ref).max()
+        assert (np.abs(out - ref) <= 1e-2 * np.abs(ref) + 1e-4 * scale).all(), row
+    ends = case["query_ends"].reshape(-1, 1)
+    picked = ops.topk(scores, t["key_lengths"], t["query_ends"])
+    torch.cuda.synchronize()
+    assert np.array_equal(picked.cpu().numpy(), oracle_c.topk(got, case["key_lengths"], ends))
+
+
 def test_li_exact_binary_fraction_fixture(device):
     """Exact-arithmetic inputs in the style of the reference fixture (workloads.py:196-283: FP8 codes
     {0, 0x38, 0x40, 0x44}, power-of-two scales): every partial sum is exact in fp32, so the tensor-core

@@ -48,6 +48,25 @@ def li_case(seed=0, batch=4, queries=1, heads=64, len_lo=2048, len_hi=4096, key_
                 batch=batch, history=history, key_dtype=key_dtype, weight_dtype=weight_dtype)
 
 
+def prefill_case(seed=0, chunk=64, context=8192, heads=64, scale_lo=1e-3, scale_hi=1e-1):
+    """A chunked-prefill LI problem in the layout of `li_case`: one owner's `context` FP8 keys, the last `chunk`
+    tokens as queries (query i sees context - chunk + i + 1 keys), packed four query slots per row; every row
+    reads the same pages through its own copy of one permuted block table."""
+    assert chunk % 4 == 0 and context % BLOCK == 0
+    rng = np.random.default_rng(seed)
+    batch, queries, pages = chunk // 4, 4, context // BLOCK
+    ends = (context - chunk + 1 + np.arange(chunk)).astype(np.int32).reshape(batch, queries)
+    key_scale = np.exp(rng.uniform(np.log(scale_lo), np.log(scale_hi), context)).astype(np.float32)
+    query_scale = np.exp(rng.uniform(np.log(scale_lo), np.log(scale_hi), (chunk, heads))).astype(np.float32)
+    keys = oracle.encode_e4m3(np.clip(rng.standard_normal((context, 128), dtype=np.float32) * 8, -448, 448))
+    query = oracle.encode_e4m3(np.clip(rng.standard_normal((chunk, heads, 128), dtype=np.float32) * 8, -448, 448))
+    weights = oracle.f32_to_bf16_rne((rng.standard_normal((chunk, heads)) / 8).astype(np.float32))
+    table = np.tile(rng.permutation(pages).astype(np.int32), (batch, 1))
+    return dict(query=query, keys=keys, weights=weights, query_scale=query_scale, key_scale=key_scale,
+                key_lengths=np.full(batch, context, np.int32), query_ends=ends, block_table=table, heads=heads,
+                queries=queries, batch=batch, history=context, key_dtype="fp8", weight_dtype="bf16")
+
+
 def to_torch(case, device):
     """Device tensors for the keys of a case (FP8 codes viewed as float8_e4m3fn, bf16 bits as bfloat16)."""
     import torch
