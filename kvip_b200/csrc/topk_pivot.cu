@@ -14,9 +14,9 @@
 // the three-passes-over-the-row selection (topk_core::select_row). The result is therefore always the
 // exact, deterministic TopK; the sample only decides how fast.
 //
-// The kernel is instruction-bound (one SM works through a whole row), so while two CTAs per row still fit
-// the GPU in one wave it runs as clusters of two: each CTA samples and filters half of the row, rank 0
-// appends its partner's list through distributed shared memory and finishes alone.
+// The kernel is instruction-bound (one SM works through a whole row), so while several CTAs per row still fit
+// the GPU in one wave it runs as clusters of two, four or eight: each CTA samples and filters its slice of the
+// row, rank 0 appends the others' lists through distributed shared memory and finishes alone.
 #include <cooperative_groups.h>
 #include "common.cuh"
 #include "topk_core.cuh"
@@ -48,9 +48,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   uint32_t* list_key = list;
   uint32_t* list_pos = list + kPivotCandidates;
 
-  // One CTA per row, or a cluster of two when the GPU has SMs to spare: each samples and filters half of the
-  // row, rank 0 appends its partner's list to its own (distributed shared memory) and finishes alone. Every
-  // cluster barrier below is reached by both CTAs unconditionally.
+  // One CTA per row, or a cluster of two, four or eight when the GPU has SMs to spare: each samples and filters
+  // its slice of the row, rank 0 appends the others' lists to its own (distributed shared memory) and finishes
+  // alone. Every cluster barrier below is reached by all CTAs of the cluster unconditionally.
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t ranks = cluster.num_blocks(), rank = cluster.block_rank();
   const uint32_t row = blockIdx.x / ranks;
@@ -76,15 +76,14 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   for (uint32_t i = tid; i < 4096; i += kThreads) hist[i] = 0;
   __syncthreads();
   const uint32_t lines = (L + 31u) >> 5;                       // <= 65536
-  const uint32_t sample_lines = min(lines, kSampleLines);
+  const uint32_t sample_lines = min(lines, kSampleLines * ranks);   // every CTA of the cluster samples up to 256 lines
   {
     constexpr uint32_t kPerWarp = kSampleLines / (kThreads / 32u);  // every warp: the same trip count
     float x[kPerWarp];
     bool ok[kPerWarp];
 #pragma unroll
     for (uint32_t i = 0; i < kPerWarp; ++i) {  // all loads first: one memory latency, not kPerWarp
-      const uint32_t mine = warp + i * (kThreads / 32u);       // a pair shares the sample lines: rank r takes
-      const uint32_t s = (mine % ranks == rank) ? mine : ~0u;  // those with s % 2 == r
+      const uint32_t s = (warp + i * (kThreads / 32u)) * ranks + rank;   // sample lines are dealt round-robin
       const uint32_t line = s < sample_lines ? (s * lines) / sample_lines : 0u;
       const uint32_t position = line * 32u + lane;
       ok[i] = s < sample_lines && position < L;
@@ -93,13 +92,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
 #pragma unroll
     for (uint32_t i = 0; i < kPerWarp; ++i) hist_add(hist, ok[i], sortable_key(x[i]) >> 20);
   }
-  cluster.sync();  // both sample histograms are complete (a block barrier when there is no partner)
+  cluster.sync();  // every sample histogram is complete (a block barrier when the cluster is one CTA)
   uint32_t pivot_key;
   {
     const uint32_t group = 1023u - tid;  // thread i owns the 4 highest unclaimed bins
     uint32_t c0 = hist[group * 4u], c1 = hist[group * 4u + 1u], c2 = hist[group * 4u + 2u], c3 = hist[group * 4u + 3u];
-    if (ranks == 2u) {
-      const uint4 other = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(hist, rank ^ 1u) + group * 4u);
+    for (uint32_t r = 1; r < ranks; ++r) {
+      const uint4 other = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(hist, (rank + r) % ranks) + group * 4u);
       c0 += other.x; c1 += other.y; c2 += other.z; c3 += other.w;
     }
     uint32_t sampled;
@@ -135,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     const float4* row4 = reinterpret_cast<const float4*>(scores);
     const uint32_t vectors = (L + 3u) >> 2;
     constexpr uint32_t kChunk = kThreads * 16u;
-    const uint32_t chunks_each = ((L + kChunk - 1u) / kChunk + ranks - 1u) / ranks;   // rank 0: the first half
+    const uint32_t chunks_each = ((L + kChunk - 1u) / kChunk + ranks - 1u) / ranks;   // rank r: the r-th slice
     const uint32_t begin = min(L, rank * chunks_each * kChunk), end = min(L, (rank + 1u) * chunks_each * kChunk);
     for (uint32_t round = begin; round < end; round += kRoundChunks * kChunk) {
       uint32_t masks[kRoundChunks / 2];
@@ -208,18 +207,25 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     }
   }
   __syncthreads();
-  if (ranks == 2u) {
-    // hand the second half's list to rank 0: positions are already in order, rank 0's come first
+  if (ranks > 1u) {
+    // hand the other slices' lists to rank 0 in rank order: positions stay in order
     if (tid == 0) kept_here = kept;
-    cluster.sync();  // both lists and counts are complete
-    const uint32_t theirs = *cluster.map_shared_rank(&kept_here, rank ^ 1u);
-    if (rank == 0 && kept <= kPivotCandidates && theirs <= kPivotCandidates - kept) {
-      const uint32_t* remote = cluster.map_shared_rank(list_pos, 1u);
-      for (uint32_t i = tid; i < theirs; i += kThreads) list_pos[kept + i] = remote[i];
+    cluster.sync();  // all lists and counts are complete
+    if (rank == 0) {
+      for (uint32_t r = 1; r < ranks; ++r) {
+        const uint32_t theirs = *cluster.map_shared_rank(&kept_here, r);
+        if (kept <= kPivotCandidates && theirs <= kPivotCandidates - kept) {
+          const uint32_t* remote = cluster.map_shared_rank(list_pos, r);
+          for (uint32_t i = tid; i < theirs; i += kThreads) list_pos[kept + i] = remote[i];
+          kept += theirs;
+        } else {
+          kept = kPivotCandidates + 1u;  // does not fit: three passes over the row instead
+        }
+      }
     }
-    kept = (kept > kPivotCandidates || theirs > kPivotCandidates) ? kPivotCandidates + 1u : kept + theirs;
-    cluster.sync();  // rank 0 has read its partner's shared memory
+    cluster.sync();  // rank 0 has read the other CTAs' shared memory
     if (rank != 0) return;
+    __syncthreads();
   }
   if (kept < kTop || kept > kPivotCandidates) {  // block-uniform: the sample misled, or the row is (nearly) constant
     select_row(a, row, nullptr);
@@ -316,7 +322,8 @@ uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
       return check_launch("topk_pivot attribute");
     configured = true;
   }
-  // two CTAs per row while that still fits the GPU in one wave
+  // two, four or eight CTAs per row while the clusters still fit the GPU in one wave (a cluster of eight
+  // 1024-thread CTAs needs eight free SMs of one GPC: about two of them fit per GPC)
   static int sm_count = 0;
   if (!sm_count) {
     int device = 0;
@@ -324,7 +331,8 @@ uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
       sm_count = 148;
   }
-  const unsigned ranks = 2u * a.rows <= static_cast<unsigned>(sm_count) ? 2u : 1u;
+  const unsigned sms = static_cast<unsigned>(sm_count);
+  const unsigned ranks = 8u * a.rows <= (sms * 3u) / 4u ? 8u : (4u * a.rows <= (sms * 7u) / 8u ? 4u : (2u * a.rows <= sms ? 2u : 1u));
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(a.rows * ranks, 1, 1);
   config.blockDim = dim3(kThreads, 1, 1);

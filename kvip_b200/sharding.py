@@ -36,15 +36,17 @@ def shard_bounds(total_tokens, world, rank, block=128):
 
 
 def gather_candidates(local_scores, local_index, group=None):
-    """All-gather of the per-rank candidates: [rows, 2048] each -> [rows, world*2048] in rank order."""
+    """ONE all-gather of the per-rank candidates: [rows, 2048] scores and indices each, exchanged as one packed
+    int32 tensor [2, rows, 2048] per rank -> ([rows, world*2048] scores, same shape indices) in rank order."""
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
-    scores = [torch.empty_like(local_scores) for _ in range(world)]
-    index = [torch.empty_like(local_index) for _ in range(world)]
-    dist.all_gather(scores, local_scores.contiguous(), group=group)
-    dist.all_gather(index, local_index.contiguous(), group=group)
-    return torch.cat(scores, dim=1).contiguous(), torch.cat(index, dim=1).contiguous()
+    packed = torch.stack((local_scores.contiguous().view(torch.int32), local_index.contiguous()))
+    parts = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(parts, packed, group=group)
+    scores = torch.cat([p[0] for p in parts], dim=1).contiguous().view(torch.float32)
+    index = torch.cat([p[1] for p in parts], dim=1).contiguous()
+    return scores, index
 
 
 def sequence_sharded_topk(local_scores, local_length, base_index, *, queries=1, group=None, local_topk=None,
