@@ -32,6 +32,40 @@ def _log_uniform(shape, lo, hi, generator, device):
     return torch.exp(u * (np.log(hi) - np.log(lo)) + np.log(lo))
 
 
+def lidu_state(batch, queries_per_request, source, hot, *, resident_fraction=0.5, hit_fraction=0.9, seed=0):
+    """Seeded inputs of one `lidu` call (NumPy): `batch` requests with `queries_per_request` query rows each,
+    `source` logical tokens, `hot` resident slots of which `resident_fraction` are mapped; every query selects
+    2048 distinct tokens, `hit_fraction` of them resident. Keys are the argument names of `kvip_b200.lidu`."""
+    rng = np.random.default_rng(seed)
+    t2s = np.full((batch, source), -1, np.int32)
+    s2t = np.full((batch, hot), -1, np.int32)
+    rows = []
+    for r in range(batch):
+        resident = rng.choice(source, int(hot * resident_fraction), replace=False)
+        slots = rng.permutation(hot)[: len(resident)]
+        t2s[r, resident], s2t[r, slots] = slots, resident
+        cold = np.setdiff1d(np.arange(source), resident, assume_unique=False)
+        hits = int(TOPK * hit_fraction)
+        for _ in range(queries_per_request):
+            picked = np.concatenate((rng.choice(resident, hits, replace=False),
+                                     rng.choice(cold, TOPK - hits, replace=False)))
+            rows.append(rng.permutation(picked))
+    miss_slots = np.stack([rng.permutation(hot)[:TOPK] for _ in range(batch)]).astype(np.int32)
+    bitmap = np.zeros((batch, 4176), np.int32)
+    for r in range(batch):  # the victim candidates are also marked in the bitmap: their tokens count as misses
+        bits = np.zeros(4176 * 32, np.uint8)
+        bits[miss_slots[r]] = 1
+        bitmap[r] = np.packbits(bits, bitorder="little").view("<i4")
+    return dict(
+        topk_indices=np.stack(rows).astype(np.int32).reshape(-1, 1, TOPK),
+        actual_seq_lengths_query=np.cumsum([queries_per_request] * batch).astype(np.int32),
+        req_pool_entries=np.arange(batch, dtype=np.int32), token_to_slot_pool=t2s, slot_to_token_pool=s2t,
+        eviction_cursors=rng.integers(0, hot, batch).astype(np.int32), cache_tokens=np.full(batch, hot, np.int32),
+        candidate_lens=np.full(batch, source, np.int32), miss_slots=miss_slots, miss_slot_bitmap=bitmap,
+        resident_block_table=rng.permutation(batch * hot // 128).astype(np.int32).reshape(batch, -1),
+        logical_seq_lengths=np.full(batch, source, np.int32))
+
+
 class DecodePipeline:
     def __init__(self, device, *, batch, queries=1, heads=64, history, resident, len_lo, len_hi, key_dtype="fp8",
                  weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
