@@ -423,6 +423,13 @@ __global__ void __launch_bounds__(kThreads, 1) lidu_requests(const KvipLiduArgs 
   lidu_request(a, smem, cluster, ranks, rank);
   if (rank != 0) return;   // helpers took part in the gather only
   if (stamps && threadIdx.x == 0) stamps[1] = device_time_ns();
+  if (a.batch == 1u) {  // nobody else to wait for: the block barrier orders this CTA's own scratch writes
+    __syncthreads();
+    lidu_compact(a);
+    __syncthreads();
+    if (stamps && threadIdx.x == 0) stamps[2] = device_time_ns();
+    return;
+  }
   __threadfence();   // this request's scratch and control words are visible before the ticket is taken
   __syncthreads();
   if (threadIdx.x == 0) {
