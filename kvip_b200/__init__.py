@@ -20,6 +20,9 @@ _EXPORTS = {
     "IndexUpdate": ("operators.lifetch", "IndexUpdate"),
     "HostKVPool": ("operators.lifetch", "HostKVPool"),
     "HostDecodeLoop": ("host_loop", "HostDecodeLoop"),
+    "IndexSelector": ("adapters", "IndexSelector"),
+    "PagedIndexer": ("adapters", "PagedIndexer"),
+    "RequestPlan": ("adapters", "RequestPlan"),
     "FusedQueryInputs": ("inputs", "QueryInputs"),
     "FusedWorkspace": ("operators.lifetch", "LIFetchWorkspace"),
 }

@@ -249,6 +249,63 @@ def test_host_decode_loop_equals_serial_steps(prefetch, device):
     assert loop.steps == 4 and loop.h2d_bytes > 0 and loop.d2h_bytes == host_out.numel() * 4
 
 
+def test_index_selector_mixed_batch(device):
+    """The serving-side caller: a forward batch of three decode tokens and one 64-token prefill chunk. Decode
+    rows go through QueryInputs.pack + LIFetch and must equal a plain pipeline step on the same queries; the
+    prefill rows are selected by the paged indexer over the model's own cache and must satisfy the reference's
+    TopK validity oracle against the golden scores; `slots()` returns the resident slots of the decode tokens."""
+    import workloads
+    from kvip_b200 import IndexSelector, PagedIndexer, RequestPlan
+    config = dict(batch=3, queries=1, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=656, seed=31, host_pool=False, fill_payload=True)
+    plain, served = DecodePipeline(device, **config), DecodePipeline(device, **config)
+    plain.step()
+    inputs = served.workspace.inputs
+    owners = served.row_owner_list
+    chunk, context = 64, 4096
+    case = workloads.prefill_case(seed=8, chunk=chunk, context=context)
+    t = workloads.to_torch(case, device)
+    # flattened forward batch: [decode 0 | prefill chunk | decode 1 | decode 2]
+    where = [0, chunk + 1, chunk + 2]
+    total = chunk + 3
+    query = torch.zeros((total, 64, 128), dtype=torch.uint8, device=device)
+    weights = torch.zeros((total, 64), dtype=torch.bfloat16, device=device)
+    scale = torch.ones((total, 64), dtype=torch.float32, device=device)
+    positions = torch.zeros(total, dtype=torch.int64, device=device)
+    query[where] = inputs.query.view(torch.uint8)[:3]
+    weights[where] = inputs.weights[:3]
+    scale[where] = inputs.scale[:3]
+    positions[where] = served.positions[:3]
+    query[1:chunk + 1] = t["query"].view(torch.uint8)
+    weights[1:chunk + 1] = t["weights"]
+    scale[1:chunk + 1] = t["query_scale"]
+    plans = [RequestPlan("d0", owners[0], 0, 1, decode=True),
+             RequestPlan("p", 0, 1, chunk + 1, decode=False, start=context - chunk, key_end=context),
+             RequestPlan("d1", owners[1], chunk + 1, chunk + 2, decode=True),
+             RequestPlan("d2", owners[2], chunk + 2, chunk + 3, decode=True)]
+    selector = IndexSelector(torch, inputs=inputs, rotating=served.rotating, update=served.update,
+                             logical_ids=served.storage.logical_ids, row_owners=inputs.row_owners,
+                             forward=served.forward)
+    indexer = PagedIndexer(torch, t["keys"].view(torch.uint8).view(-1, 128, 128), t["key_scale"].view(-1, 128))
+    metadata = type("Metadata", (), {})()
+    metadata.block_table = torch.zeros((4, context // 128), dtype=torch.int32, device=device)
+    metadata.block_table[1] = t["block_table"][0]
+    selector.prepare(plans)
+    inputs.bind_positions(positions)
+    result = selector(query.view(torch.float8_e4m3fn), weights, indexer, metadata, scale)
+    torch.cuda.synchronize()
+    assert tuple(result.shape) == (total, 1, 2048)
+    assert torch.equal(result[where], plain.update.logical_output[:3])
+    assert torch.equal(selector.slots(3), plain.update.slot_output[:3])
+    assert torch.equal(served.pool_hbm, plain.pool_hbm)
+    expected = workloads.oracle_scores(case)
+    picked = result[1:chunk + 1, 0].cpu().numpy()
+    ends = case["query_ends"].reshape(-1)
+    for i in range(chunk):
+        assert picked[i].max() < ends[i]
+        oracle.validate_topk(picked[i], expected[i:i + 1, :ends[i]])
+
+
 def test_forward_rejects_mismatched_shape(device):
     config = dict(batch=2, queries=1, heads=64, history=4096, resident=2048, len_lo=3000, len_hi=4096, key_dtype="fp8",
                   weight_dtype="bf16", token_bytes=1152, seed=3, host_pool=False, gather=False)

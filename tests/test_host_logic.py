@@ -181,3 +181,19 @@ def test_reference_arm_prints_one_json_line():
     line = json.loads(out[0])
     assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+def test_serving_caller_objects_validate_their_inputs():
+    """RequestPlan / PagedIndexer of the serving-side caller: host-side checks only."""
+    import torch
+
+    from kvip_b200 import PagedIndexer, RequestPlan
+    plan = RequestPlan("r", 3, 10, 14, decode=False, start=100, key_end=104)
+    assert (plan.owner, plan.begin, plan.stop, plan.query_end, plan.decode, plan.key_end) == (3, 10, 14, 4, False, 104)
+    keys = torch.zeros((2, 128, 128), dtype=torch.uint8)
+    indexer = PagedIndexer(torch, keys, torch.ones((2, 128), dtype=torch.float32))
+    assert indexer.k_cache.kv_cache[0] is keys and tuple(indexer.keys.shape) == (256, 128)
+    with pytest.raises(ValueError):
+        PagedIndexer(torch, torch.zeros((2, 128, 128), dtype=torch.bfloat16), torch.ones((2, 128)))
+    with pytest.raises(ValueError):
+        PagedIndexer(torch, keys, torch.ones((2, 128), dtype=torch.float16))
