@@ -306,6 +306,60 @@ def test_index_selector_mixed_batch(device):
         oracle.validate_topk(picked[i], expected[i:i + 1, :ends[i]])
 
 
+def test_full_size_step_properties(device):
+    """The benchmark's context length (131072 keys per request, FP8, 2048 x 1152-byte rows gathered per query) at
+    batch 8, checked through properties that need no oracle pass over 128k keys: the selection is the TopK of the
+    step's own scores (values against torch.topk, canonical order by definition), the Index rows stay a
+    permutation that carries keys and scales along, every selected token sits in a valid resident slot holding
+    its payload, the dense gather returns those payloads, and repeating the step fetches nothing."""
+    p = DecodePipeline(device, batch=8, queries=1, heads=64, history=131072, resident=32768, len_lo=100000,
+                       len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152, seed=4, host_pool=False,
+                       fill_payload=True)
+    keys_before, scales_before = p.storage.keys.clone(), p.storage.scales.clone()
+    p.step()
+    torch.cuda.synchronize()
+    assert int(p.forward.li_status.item()) == 0 and int(p.update.status.abs().sum()) == 0
+    scores, topk = p.workspace.scores, p.workspace.topk.view(-1, 2048)
+    lengths = torch.from_numpy(p.lengths).to(device)
+    for row in range(8):
+        n = int(lengths[row])
+        picked = topk[row].long()
+        assert int(picked.min()) >= 0 and int(picked.max()) < n and picked.unique().numel() == 2048
+        values = scores[row, :n]
+        best = torch.topk(values, 2048).values
+        assert torch.equal(torch.sort(values[picked], descending=True).values, best)
+        cut = best[-1]
+        above = picked[values[picked] > cut]
+        ties = picked[values[picked] == cut]
+        assert torch.equal(torch.cat((above, ties)), picked)                      # all > cut first, then the ties
+        assert bool((above[1:] > above[:-1]).all()) and bool((ties[1:] > ties[:-1]).all())   # each in position order
+        lower_ties = torch.nonzero(values == cut).view(-1)[: ties.numel()]
+        assert torch.equal(ties, lower_ties)                                        # ties go to the lower positions
+    owners = torch.tensor(p.row_owner_list, device=device)
+    logical_ids = p.storage.logical_ids
+    identity = torch.arange(131072, device=device)
+    for row in range(8):
+        owner = int(owners[row])
+        ids = logical_ids[owner]
+        assert torch.equal(torch.sort(ids).values, identity)
+        assert torch.equal(p.storage.keys[owner], keys_before[owner][ids])
+        assert torch.equal(p.storage.scales[owner], scales_before[owner][ids])
+        logical = p.update.logical_output[row, 0].long()
+        slots = p.update.slot_output[row, 0].long()
+        assert torch.equal(torch.sort(logical).values, torch.sort(topk[row].long()).values)  # first step: ids = positions
+        assert int(slots.min()) >= 0 and int(slots.max()) < 32768 and slots.unique().numel() == 2048
+        assert bool((p.storage.hot_valid[owner][slots] == 1).all())
+        assert torch.equal(ids[slots], logical)                                  # slot p holds Index row p
+        expected_rows = p.source[owner * 131072 + logical]
+        assert torch.equal(p.pool_hbm[owner * p.output_stride + slots], expected_rows)
+        assert torch.equal(p.gather_out[row], expected_rows)
+    first_logical = p.update.logical_output.clone()
+    p.step()
+    torch.cuda.synchronize()
+    assert int(p.rotating.query_counts[:, 4].sum()) == 0, "a repeated query must find every row resident"
+    assert torch.equal(torch.sort(p.update.logical_output, dim=-1).values, torch.sort(first_logical, dim=-1).values)
+
+
 def test_forward_rejects_mismatched_shape(device):
     config = dict(batch=2, queries=1, heads=64, history=4096, resident=2048, len_lo=3000, len_hi=4096, key_dtype="fp8",
                   weight_dtype="bf16", token_bytes=1152, seed=3, host_pool=False, gather=False)
