@@ -98,7 +98,9 @@ typedef struct KvipLiArgs {
   uint32_t keyRows, scoreStride, keyDtype, weightDtype;
   uint32_t scoreMode, ctas;
   uint32_t stages;            /* key pages in flight per CTA; 0 = as many as shared memory holds */
-  uint32_t reserved1;
+  uint32_t withhold_tile;     /* test hook for the bounded waits: when n > 0, CTA 0 never loads its n-th key page,
+                                 so the wait for that page runs out (about a second) and the kernel returns with
+                                 KVIP_ERR_PIPELINE in *status; 0 in production */
 } KvipLiArgs;
 uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
 /* CUDA-core restatement of the same formula with the oracle's accumulation order;

@@ -44,7 +44,7 @@ LiArgs = _struct("LiArgs", (
     "query", "keys", "weights", "query_scale", "key_scale", "key_lengths", "query_ends", "block_table",
     "scores", "status"), [(n, u32) for n in (
         "batch", "queries", "heads", "pagesPerRequest", "keyRows", "scoreStride", "keyDtype", "weightDtype",
-        "scoreMode", "ctas", "stages", "reserved1")])
+        "scoreMode", "ctas", "stages", "withhold_tile")])
 
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])

@@ -319,10 +319,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
             }
           }
           if (alive && mbar_wait(bar(S + stage), phase ^ 1u, abort_flag)) {
-            mbar_expect_tx(bar(stage), Cfg::kTileBytes);
-            for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
-              tma_load_2d(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes, &key_map,
-                          static_cast<int32_t>(atom * 64u), page * static_cast<int32_t>(kBlockTokens), bar(stage));
+            // test hook: the withheld page never arrives, its consumer's bounded wait gives up
+            const bool withheld = a.withhold_tile && blockIdx.x == 0 && base + i - tile_begin + 1u == a.withhold_tile;
+            if (!withheld) {
+              mbar_expect_tx(bar(stage), Cfg::kTileBytes);
+              for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
+                tma_load_2d(key_smem + stage * Cfg::kTileBytes + atom * kAtomBytes, &key_map,
+                            static_cast<int32_t>(atom * 64u), page * static_cast<int32_t>(kBlockTokens), bar(stage));
+            }
             if (++stage == S) { stage = 0; phase ^= 1u; }
           } else {
             alive = 0;

@@ -121,6 +121,30 @@ def test_li_tcgen05_ragged_query_slots_two_units(key_dtype, device):
             assert (np.abs(out - ref) <= rtol * np.abs(ref) + rtol * 1e-2 * scale).all(), (kw, t)
 
 
+def test_li_bounded_wait_gives_up_and_reports(device):
+    """Every wait inside the tensor-core kernel is bounded. With the test hook one key page of CTA 0 is never
+    loaded: the wait for it runs out (about a second of SM clock), the CTA leaves its pipeline in order, the
+    kernel returns with KVIP_ERR_PIPELINE in the status word, and the next ordinary call on the same context
+    is correct again."""
+    case = workloads.li_case(seed=12, batch=2, queries=1, heads=64, len_lo=4000, len_hi=5000, key_dtype="fp8",
+                             weight_dtype="bf16")
+    t = workloads.to_torch(case, device)
+    args = (t["query"], t["keys"], t["weights"], t["query_scale"], t["key_scale"], t["key_lengths"], t["query_ends"],
+            t["block_table"])
+    _, status = ops.li_score(*args, ctas=2, withhold_tile=3)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 32, "the kernel must report the abandoned wait"
+    expected, _ = _li(case, device, simt=True)
+    scores, status = ops.li_score(*args, ctas=2)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    mask = _valid_mask(case, expected.shape[1])
+    ref, out = expected.cpu().numpy(), scores.cpu().numpy()
+    for row in range(out.shape[0]):
+        scale = np.abs(ref[row][mask[row]]).max()
+        assert (np.abs(out[row][mask[row]] - ref[row][mask[row]]) <= 1e-2 * np.abs(ref[row][mask[row]]) + 1e-4 * scale).all()
+
+
 def test_chunked_prefill_li_and_topk(device):
     """The chunked-prefill configuration at test size: 128 query tokens of one request against a causal
     8192-token context, four query slots per row, all rows reading the same key pages. Scores within the FP8
