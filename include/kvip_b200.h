@@ -150,6 +150,28 @@ typedef struct KvipMergeArgs {
 } KvipMergeArgs;
 uint32_t kvip_b200_topk_merge(const KvipMergeArgs* args, void* stream);
 
+/* ---- resident threshold and cold predicate ---------------------------------------------
+ * Input: the TopK of the RESIDENT prefix of every score row (kvip_b200_topk run with the row's query end
+ * clipped to `resident`) with its scores. Output per row: the threshold key (order-preserving u32 image of the
+ * smallest selected score; 0 while the prefix holds fewer than 2048 valid positions), one bit per cold
+ * position (position resident + 32 w + i is bit i of word w) set when its score beats the threshold, and the
+ * number of set bits. The marked positions contain the cold part of the row's final TopK: they are the
+ * candidates of a speculative prefetch. Replaces ProcessResidentTopK / SaveResident / ClassifyScore /
+ * BatchClassifyScore (op_kernel/indexer/indexer_vector.h:100-105, 162-234; indexer_score.h:784-792, 976-1017);
+ * the forward of this build does not consume it. */
+typedef struct KvipColdArgs {
+  const float* scores;          /* [rows, scoreStride] */
+  const int32_t* key_lengths;   /* [rows / queries] */
+  const int32_t* query_ends;    /* [rows] */
+  const int32_t* prefix_topk;   /* [rows, 2048] TopK of positions < resident, -1 padded */
+  const float* prefix_scores;   /* [rows, 2048] their scores */
+  uint32_t* threshold_keys;     /* [rows] out */
+  uint32_t* bitmap;             /* [rows, bitmap_words] out */
+  int32_t* counts;              /* [rows] out */
+  uint32_t rows, queries, scoreStride, resident, bitmap_words, reserved0;
+} KvipColdArgs;
+uint32_t kvip_b200_cold_predicate(const KvipColdArgs* args, void* stream);
+
 /* ---- stage 3: classification + resolver + service outputs + fetch descriptors ---
  * Replaces ClassifyTopkHalf / StagedInitializeReady / StagedQuery / PackStagedUrmaQuery /
  * PublishQueryOutputs (op_kernel/staged_topk_classify.h:9-46,

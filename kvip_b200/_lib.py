@@ -49,6 +49,10 @@ LiArgs = _struct("LiArgs", (
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])
 
+ColdArgs = _struct("ColdArgs", ("scores", "key_lengths", "query_ends", "prefix_topk", "prefix_scores", "threshold_keys",
+                                "bitmap", "counts"),
+                   [(n, u32) for n in ("rows", "queries", "scoreStride", "resident", "bitmap_words", "reserved0")])
+
 MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"), [("rows", u32), ("shards", u32)])
 
 ResolveArgs = _struct("ResolveArgs", (
@@ -112,7 +116,7 @@ class Workspace(ctypes.Structure):
 _STAGES = {
     "kvip_b200_li_score": LiArgs, "kvip_b200_li_score_simt": LiArgs, "kvip_b200_topk": TopkArgs,
     "kvip_b200_topk_static": TopkArgs,
-    "kvip_b200_topk_merge": MergeArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
+    "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs,
 }

@@ -92,6 +92,33 @@ def topk(scores, key_lengths, query_ends, out=None, *, out_scores=None, base_ind
     return out
 
 
+def cold_predicate(scores, key_lengths, query_ends, resident):
+    """Resident threshold and cold predicate of every score row: the TopK of the resident prefix (positions
+    below `resident`), the threshold key (smallest selected key; 0 while the prefix holds fewer than 2048 valid
+    positions), one bit per cold position whose score beats it, and the number of such positions.
+    Returns (prefix_topk [rows, 2048], threshold_keys [rows] int32 holding u32 bits, bitmap [rows, words] int32,
+    counts [rows])."""
+    device = scores.device
+    rows, stride = scores.shape
+    queries = rows // key_lengths.numel()
+    if resident % 32 or resident > stride:
+        raise ValueError("resident must be a multiple of 32 inside the score row")
+    clipped = torch.clamp(query_ends.reshape(-1), max=resident).to(torch.int32)
+    prefix_scores = torch.zeros((rows, TOPK), dtype=torch.float32, device=device)
+    prefix_topk = topk(scores, key_lengths, clipped, out_scores=prefix_scores)
+    words = max(1, (stride - resident + 31) // 32)
+    thresholds = torch.zeros(rows, dtype=torch.int32, device=device)
+    bitmap = torch.zeros((rows, words), dtype=torch.int32, device=device)
+    counts = torch.zeros(rows, dtype=torch.int32, device=device)
+    ends = query_ends.reshape(-1).contiguous()
+    args = _lib.ColdArgs(scores=_ptr(scores), key_lengths=_ptr(key_lengths), query_ends=_ptr(ends),
+                         prefix_topk=_ptr(prefix_topk), prefix_scores=_ptr(prefix_scores), threshold_keys=_ptr(thresholds),
+                         bitmap=_ptr(bitmap), counts=_ptr(counts), rows=rows, queries=queries, scoreStride=stride,
+                         resident=resident, bitmap_words=words)
+    _lib.check(_lib.load_library().kvip_b200_cold_predicate(ctypes.byref(args), _stream(device)), "cold_predicate")
+    return prefix_topk, thresholds, bitmap, counts
+
+
 def topk_merge(cand_scores, cand_index, out=None):
     """Global top-2048 of [rows, shards*2048] (score, index) candidates."""
     device = cand_scores.device

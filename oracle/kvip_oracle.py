@@ -169,6 +169,32 @@ def topk(scores, key_lengths, query_ends, base_index=0):
     return out
 
 
+def cold_predicate(scores, key_lengths, query_ends, resident):
+    """Resident threshold + cold predicate (ProcessResidentTopK / SaveResident, indexer_vector.h:100-105, 162-177;
+    ClassifyScore / BatchClassifyScore, indexer_score.h:784-792, 976-1017): TopK of the positions below
+    `resident`, threshold = smallest selected key (0 while that prefix holds fewer than 2048 valid positions),
+    one bit per cold position whose key beats it (bit i of word w = position resident + 32 w + i), their count."""
+    query_ends = np.asarray(query_ends).reshape(len(key_lengths), -1)
+    queries = query_ends.shape[1]
+    rows, stride = scores.shape
+    words = max(1, (stride - resident + 31) // 32)
+    prefix = np.empty((rows, TOPK), dtype=np.int32)
+    thresholds = np.zeros(rows, dtype=np.uint32)
+    bitmap = np.zeros((rows, words), dtype=np.uint32)
+    counts = np.zeros(rows, dtype=np.int32)
+    for t in range(rows):
+        b = t // queries
+        length = max(0, min(int(key_lengths[b]), int(query_ends[b, t % queries]), stride))
+        prefix[t] = topk_row(scores[t], min(length, resident), 0)
+        if (prefix[t] >= 0).all():
+            thresholds[t] = sortable_key(scores[t, prefix[t]]).min()
+        cold = np.arange(resident, length)
+        marked = cold[sortable_key(scores[t, cold]) > thresholds[t]] - resident
+        np.bitwise_or.at(bitmap[t], marked // 32, np.uint32(1) << (marked % 32).astype(np.uint32))
+        counts[t] = len(marked)
+    return prefix, thresholds, bitmap, counts
+
+
 def topk_merge(cand_scores, cand_index):
     """Global top-2048 of sharded candidates under (score desc, index asc), canonical order."""
     rows = cand_scores.shape[0]

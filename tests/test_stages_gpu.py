@@ -284,6 +284,33 @@ def test_topk_wide_rows(stride, device):
     _topk_check(scores, key_lengths, key_lengths.reshape(-1, 1).copy(), device, base_index=7)
 
 
+def test_cold_predicate_matches_oracle_and_covers_the_final_topk(device):
+    """Resident threshold + cold predicate: prefix TopK, threshold key, bitmap and count bit-exact with the
+    oracle; and the property that makes the stage useful - every cold position of the row's final TopK is marked."""
+    rng = np.random.default_rng(21)
+    stride, resident = 24576, 8192
+    scores = (rng.standard_normal((6, stride)) * np.exp(rng.uniform(-2, 2, (6, 1)))).astype(np.float32)
+    scores[1, :resident] -= 3.0                       # cold tokens dominate this row
+    scores[2] = rng.integers(0, 4, stride)            # heavy ties around the threshold
+    key_lengths = np.array([stride, stride, stride - 77, 9000, 4096, 1500], np.int32)   # the last two: no cold part
+    ends = key_lengths.reshape(-1, 1).copy()
+    prefix, thresholds, bitmap, counts = ops.cold_predicate(
+        torch.from_numpy(scores).to(device), torch.from_numpy(key_lengths).to(device), torch.from_numpy(ends).to(device),
+        resident)
+    torch.cuda.synchronize()
+    want_prefix, want_thresholds, want_bitmap, want_counts = oracle.cold_predicate(scores, key_lengths, ends, resident)
+    assert np.array_equal(prefix.cpu().numpy(), want_prefix)
+    assert np.array_equal(thresholds.cpu().numpy().view(np.uint32), want_thresholds)
+    assert np.array_equal(bitmap.cpu().numpy().view(np.uint32), want_bitmap)
+    assert np.array_equal(counts.cpu().numpy(), want_counts)
+    final = oracle.topk(scores, key_lengths, ends)
+    marked = np.unpackbits(want_bitmap.view(np.uint8), axis=1, bitorder="little").astype(bool)
+    for row in range(6):
+        cold = final[row][final[row] >= resident] - resident
+        assert marked[row][cold].all()
+    assert want_counts[4] == 0 and want_counts[5] == 0 and want_thresholds[5] == 0
+
+
 def test_topk_merge_equals_unsharded(device):
     """Sequence sharding: per-shard top-2048 + merge == top-2048 of the whole row (canonical order)."""
     rng = np.random.default_rng(3)
