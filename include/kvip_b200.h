@@ -150,6 +150,26 @@ typedef struct KvipMergeArgs {
 } KvipMergeArgs;
 uint32_t kvip_b200_topk_merge(const KvipMergeArgs* args, void* stream);
 
+/* ---- QueryInputs.pack / bind_positions ---------------------------------------------------
+ * Row r of the bound input buffers takes token gather_indices[r] of the caller's tensors; query_ends[r] =
+ * (positions[token] + 1) * query_valid[r]. Any of the three source groups may be NULL (skipped). One launch
+ * instead of the index_select / add / mul / copy calls of the reference (adapters/vllm/inputs.py:121-152). */
+typedef struct KvipPackArgs {
+  const uint8_t* query_src;     /* [tokens, query_row_bytes] or NULL */
+  const uint8_t* weights_src;   /* [tokens, weights_row_bytes] or NULL */
+  const float* scale_src;       /* [tokens, heads] or NULL */
+  const int64_t* positions_src; /* [tokens] or NULL */
+  const int64_t* gather_indices;/* [rows] */
+  const int64_t* query_valid;   /* [rows] 0/1 */
+  uint8_t* query_dst;           /* [rows, query_row_bytes] */
+  uint8_t* weights_dst;         /* [rows, weights_row_bytes] */
+  float* scale_dst;             /* [rows, heads] */
+  int64_t* position_scratch;    /* [rows] */
+  int32_t* query_ends;          /* [rows] */
+  uint32_t rows, tokens, heads, query_row_bytes, weights_row_bytes, reserved0;
+} KvipPackArgs;
+uint32_t kvip_b200_pack_inputs(const KvipPackArgs* args, void* stream);
+
 /* ---- resident threshold and cold predicate ---------------------------------------------
  * Input: the TopK of the RESIDENT prefix of every score row (kvip_b200_topk run with the row's query end
  * clipped to `resident`) with its scores. Output per row: the threshold key (order-preserving u32 image of the

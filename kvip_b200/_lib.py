@@ -49,6 +49,10 @@ LiArgs = _struct("LiArgs", (
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])
 
+PackArgs = _struct("PackArgs", ("query_src", "weights_src", "scale_src", "positions_src", "gather_indices", "query_valid",
+                                "query_dst", "weights_dst", "scale_dst", "position_scratch", "query_ends"),
+                   [(n, u32) for n in ("rows", "tokens", "heads", "query_row_bytes", "weights_row_bytes", "reserved0")])
+
 ColdArgs = _struct("ColdArgs", ("scores", "key_lengths", "query_ends", "prefix_topk", "prefix_scores", "threshold_keys",
                                 "bitmap", "counts"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "resident", "bitmap_words", "reserved0")])
@@ -116,7 +120,8 @@ class Workspace(ctypes.Structure):
 _STAGES = {
     "kvip_b200_li_score": LiArgs, "kvip_b200_li_score_simt": LiArgs, "kvip_b200_topk": TopkArgs,
     "kvip_b200_topk_static": TopkArgs,
-    "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
+    "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs,
+    "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs,
 }

@@ -260,6 +260,53 @@ extern "C" uint32_t kvip_b200_gather(const KvipGatherArgs* a, void* stream) {
   return kvip::launch_gather(*a, static_cast<cudaStream_t>(stream));
 }
 
+namespace kvip {
+namespace {
+// QueryInputs.pack / bind_positions as one gather kernel: row r of the bound buffers takes token
+// gather_indices[r] of the caller's tensors (adapters/vllm/inputs.py:121-152 does this with index_select calls).
+__global__ void __launch_bounds__(256) pack_rows(const KvipPackArgs a) {
+  const uint32_t row = blockIdx.x, tid = threadIdx.x;
+  int64_t token = a.gather_indices[row];
+  if (token < 0 || token >= static_cast<int64_t>(a.tokens)) token = 0;
+  if (a.query_src) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.query_src + static_cast<uint64_t>(token) * a.query_row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(a.query_dst + static_cast<uint64_t>(row) * a.query_row_bytes);
+    for (uint32_t i = tid; i < a.query_row_bytes / 16u; i += 256u) dst[i] = src[i];
+  }
+  if (a.weights_src) {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.weights_src + static_cast<uint64_t>(token) * a.weights_row_bytes);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(a.weights_dst + static_cast<uint64_t>(row) * a.weights_row_bytes);
+    for (uint32_t i = tid; i < a.weights_row_bytes / 4u; i += 256u) dst[i] = src[i];
+  }
+  if (a.scale_src)
+    for (uint32_t i = tid; i < a.heads; i += 256u)
+      a.scale_dst[static_cast<uint64_t>(row) * a.heads + i] = a.scale_src[static_cast<uint64_t>(token) * a.heads + i];
+  if (a.positions_src && tid == 0) {
+    const int64_t end = (a.positions_src[token] + 1) * a.query_valid[row];
+    a.position_scratch[row] = end;
+    a.query_ends[row] = static_cast<int32_t>(end);
+  }
+}
+}  // namespace
+}  // namespace kvip
+
+extern "C" uint32_t kvip_b200_pack_inputs(const KvipPackArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->gather_indices && a->rows >= 1 && a->tokens >= 1, "pack_inputs: null pointer or empty batch");
+  KVIP_REQUIRE(!a->query_src || (a->query_dst && a->query_row_bytes % 16u == 0 &&
+                                 (reinterpret_cast<uintptr_t>(a->query_src) & 15u) == 0 &&
+                                 (reinterpret_cast<uintptr_t>(a->query_dst) & 15u) == 0),
+               "pack_inputs: query rows must be 16-byte aligned multiples of 16 bytes");
+  KVIP_REQUIRE(!a->weights_src || (a->weights_dst && a->weights_row_bytes % 4u == 0 &&
+                                   (reinterpret_cast<uintptr_t>(a->weights_src) & 3u) == 0),
+               "pack_inputs: weight rows must be multiples of 4 bytes");
+  KVIP_REQUIRE(!a->scale_src || a->scale_dst, "pack_inputs: scale destination missing");
+  KVIP_REQUIRE(!a->positions_src || (a->query_valid && a->position_scratch && a->query_ends),
+               "pack_inputs: position outputs missing");
+  kvip::pack_rows<<<a->rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::count_launch();
+  return kvip::check_launch("pack_rows");
+}
+
 extern "C" uint32_t kvip_b200_ingest(const KvipIngestArgs* a, void* stream) {
   KVIP_REQUIRE(a && a->source_keys && a->slot_mapping && a->gather_indices && a->query_ends && a->row_owners &&
                    a->keys && a->scales, "ingest: null pointer");

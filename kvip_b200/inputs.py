@@ -101,8 +101,28 @@ class QueryInputs:
             event.record(self.torch.cuda.current_stream(self.device))
         self.turn += 1
 
+    def _pack_kernel(self, *, query=None, weights=None, scale=None, positions=None, tokens):
+        """One gather launch on the bound device (kvip_b200_pack_inputs)."""
+        import ctypes
+
+        from . import _lib
+        p = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+        args = _lib.PackArgs(
+            query_src=p(query), weights_src=p(weights), scale_src=p(scale), positions_src=p(positions),
+            gather_indices=p(self.gather_indices), query_valid=p(self.query_valid), query_dst=p(self.query),
+            weights_dst=p(self.weights), scale_dst=p(self.scale), position_scratch=p(self.position_scratch),
+            query_ends=p(self.query_ends), rows=self.batch * self.queries, tokens=tokens, heads=self.index_heads,
+            query_row_bytes=self.index_heads * INDEX_WIDTH * self.query.element_size(),
+            weights_row_bytes=self.index_heads * self.weights.element_size())
+        stream = ctypes.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)
+        lib = _lib.load_library()
+        _lib.check(lib.kvip_b200_pack_inputs(ctypes.byref(args), stream), "pack_inputs", lib)
+
     def bind_positions(self, positions):
         """Enqueue once per forward, after the runner corrects MTP positions."""
+        if self.device.type == "cuda" and positions.is_cuda and positions.dtype == self.torch.int64 and positions.is_contiguous():
+            self._pack_kernel(positions=positions, tokens=positions.numel())
+            return self.query_ends.view(self.batch, self.queries)
         self.torch.index_select(positions, 0, self.gather_indices, out=self.position_scratch)
         self.position_scratch.add_(1).mul_(self.query_valid)
         self.query_ends.copy_(self.position_scratch)
@@ -127,6 +147,11 @@ class QueryInputs:
                 scale = scale.view(tokens, self.index_heads)
             if tuple(scale.shape) != (tokens, self.index_heads):
                 raise ValueError("LIFetch requires one scale per token/head")
+        if (self.device.type == "cuda" and query.is_cuda and query.is_contiguous() and weights.is_contiguous()
+                and (scale is None or scale.is_contiguous())):
+            self._pack_kernel(query=query, weights=weights, scale=scale, tokens=tokens)
+            return self.query, self.weights, self.scale
+        if scale is not None:
             torch.index_select(scale, 0, self.gather_indices, out=self.scale)
         raw = torch.uint8 if self.query.element_size() == 1 else torch.int16
         torch.index_select(query.view(raw), 0, self.gather_indices, out=self.query.view(raw))
