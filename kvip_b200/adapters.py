@@ -10,7 +10,7 @@ python/kvip/adapters/vllm/binding.py:20-200, python/kvip/runtime/build.py:40-91)
 def bind_selectors(*_args, **_kwargs):
     raise NotImplementedError(
         "bind_selectors binds vLLM-Ascend layer objects; on CUDA build the path from LIFetchWorkspace, "
-        "IndexCacheStorage, CudaBinding, IndexUpdate and LIFetch (see INTEGRATION.md)")
+        "IndexCacheStorage, CudaBinding, IndexUpdate and LIFetch, or use IndexSelector")
 
 
 def build_libraries(force=False):

@@ -28,7 +28,7 @@ class IndexCacheStorage:
             self.keys, self.scales, self.addresses, self.identity, self.logical_ids, self.hot_valid))
 
     def prepare(self, plans):
-        """Invalidate recycled owner metadata before queuing this round."""
+        """Invalidate recycled owner metadata before this step is queued."""
         for plan in plans:
             if self.requests.get(plan.owner) == plan.request:
                 continue

@@ -85,7 +85,7 @@ class SlotLRU:
                        self.active_rows)
 
     def commit(self, destinations):
-        """Consume the slots actually accessed this round (any int32 tensor/array with one row of
+        """Consume the slots actually accessed in this step (any int32 tensor/array with one row of
         slots per LRU row, or a flat vector for a single row). Slots outside [0, active) are ignored."""
         if not torch.is_tensor(destinations):
             destinations = torch.from_numpy(np.ascontiguousarray(destinations, dtype=np.int32))

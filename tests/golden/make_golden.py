@@ -1,6 +1,6 @@
 """Regenerates the golden vectors under tests/golden/ by RUNNING THE REFERENCE's own CPU code.
 
-Run it only where the reference checkout is mounted (default /root/reference):
+Run it only where a checkout of the reference is available (its path is the first argument):
 
     python tests/golden/make_golden.py [/path/to/reference]
 
