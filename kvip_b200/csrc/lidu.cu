@@ -20,7 +20,7 @@ constexpr uint32_t kThreads = 1024;
 constexpr uint32_t kBuckets = 16384;
 constexpr uint32_t kEmpty = 0xffffffffu;
 constexpr uint32_t kMaxCacheTokens = (1u << 17) + 20u * 128u;   // lidu_..._ops.cpp:17
-constexpr uint32_t kRowWords = 2u * kSlots + 16u;               // scratch per request
+constexpr uint32_t kRowWords = 3u * kSlots + 16u;               // scratch per request: three descriptor lists + control
 constexpr int32_t kErrLayout = -100, kErrRow = -101, kErrDuplicatePool = -102, kErrToken = -103,
                   kErrCapacity = -106, kErrNoSlots = -107, kErrResolved = -109;
 
@@ -46,12 +46,9 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
                              uint32_t cta) {
   const uint32_t r = blockIdx.x / ctas, tid = threadIdx.x, B = a.batch, T = a.packed_queries;
   int32_t* work = a.scratch + static_cast<uint64_t>(r) * kRowWords;
-  int32_t* u_tokens = work;            // [8192] unique miss tokens, first-occurrence order
-  int32_t* u_slots = work + kSlots;    // [8192] their destination slots
-  int32_t* control = work + 2 * kSlots;  // 0 status, 1 unique, 2 new cursor (-1 = keep)
+  int32_t* control = work + 3 * kSlots;  // 0 status, 1 unique, 2 new cursor (-1 = keep)
   __shared__ int32_t status;
   __shared__ uint32_t scan[33];
-  __shared__ uint32_t miss_total[4];
   if (tid == 0) status = 0;
   __syncthreads();
   // ---- layout of the packed query rows ---------------------------------------------------
@@ -123,7 +120,6 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
     for (uint32_t w = tid; w < a.bitmap_words; w += kThreads)
       prot[w] = static_cast<uint32_t>(a.miss_slot_bitmap[static_cast<uint64_t>(r) * a.bitmap_words + w]);
     for (uint32_t i = tid; i < kBuckets; i += kThreads) { keys[i] = kEmpty; ranks[i] = kEmpty; }
-    if (tid < 4) miss_total[tid] = 0;
   }
   cluster.sync();  // every staged entry has landed in rank 0's shared memory (a block barrier for one CTA)
   if (cta != 0) return;
@@ -182,7 +178,6 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
         dest[hit_at++] = slot[q][j];
         atomicOr(prot + (slot[q][j] >> 5), 1u << (slot[q][j] & 31));
       }
-    if (tid == 0) miss_total[q] = misses;
     }
   }
   // hash insert of every miss; the first occurrence in (query row, TopK position) order keeps the bucket's rank
@@ -226,8 +221,7 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
     for (uint32_t j = 0; j < 2; ++j)
       if ((fresh >> (2u * q + j)) & 1u) {
         ranks[find_bucket(keys, static_cast<uint32_t>(token[q][j]))] = offset;  // every rank was compared before the scans
-        su_tokens[offset] = token[q][j];
-        u_tokens[offset++] = token[q][j];
+        su_tokens[offset++] = token[q][j];
       }
     unique += row_total[q];
   }
@@ -244,7 +238,6 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
         const int32_t s = half ? listed1 : listed0;
         if (s < 0 || s >= budget) atomicMin(&status, kErrResolved);
         su_slots[i] = s;
-        u_slots[i] = s;
       }
     }
     if (unique > kLruSlots) {
@@ -278,7 +271,6 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
           while (bits && out < extra) {
             const uint32_t s = base + __ffs(bits) - 1u;
             su_slots[kLruSlots + out] = static_cast<int32_t>(s);
-            u_slots[kLruSlots + out] = static_cast<int32_t>(s);
             if (out == extra - 1u) control[3] = static_cast<int32_t>((s + 1u) % static_cast<uint32_t>(budget));
             ++out;
             bits &= bits - 1u;
@@ -325,6 +317,33 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
           dest[miss_at++] = su_slots[ranks[find_bucket(keys, static_cast<uint32_t>(token[q][j]))]];
     }
   }
+  // the unique misses' fetch descriptors, final values: into this request's scratch lists (the compaction then
+  // only copies) or, when the call has one request, straight into the output lists
+  {
+    const bool single = B == 1u;
+    int32_t* d_index = single ? a.indices : work;
+    int32_t* d_offset = single ? a.offsets : work + kSlots;
+    int32_t* d_out = single ? a.output_indices : work + 2 * kSlots;
+    const int64_t table_row = static_cast<int64_t>((static_cast<int64_t>(pool) * a.num_layers + a.layer_id) * a.qcap);
+    for (uint32_t base = 0; base < unique; base += 2u * kThreads) {  // two entries per thread: their loads overlap
+      const uint32_t i0 = base + tid, i1 = base + kThreads + tid;
+      const int32_t s0 = i0 < unique ? su_slots[i0] : 0, s1 = i1 < unique ? su_slots[i1] : 0;
+      const int32_t b0 = a.resident_block_table[static_cast<uint64_t>(r) * a.resident_blocks + (s0 >> 7)];
+      const int32_t b1 = a.resident_block_table[static_cast<uint64_t>(r) * a.resident_blocks + (s1 >> 7)];
+      if (i0 < unique) {
+        const int32_t t0 = su_tokens[i0];
+        d_index[i0] = static_cast<int32_t>(table_row + (t0 >> 7));
+        d_offset[i0] = (t0 & 127) * 656;
+        d_out[i0] = b0 < 0 ? -1 : b0 * 128 + (s0 & 127);
+      }
+      if (i1 < unique) {
+        const int32_t t1 = su_tokens[i1];
+        d_index[i1] = static_cast<int32_t>(table_row + (t1 >> 7));
+        d_offset[i1] = (t1 & 127) * 656;
+        d_out[i1] = b1 < 0 ? -1 : b1 * 128 + (s1 & 127);
+      }
+    }
+  }
   if (tid == 0) {
     control[0] = 0;
     control[1] = static_cast<int32_t>(unique);
@@ -339,7 +358,7 @@ __device__ void lidu_compact(const KvipLiduArgs& a) {
   const uint32_t tid = threadIdx.x, B = a.batch;
   uint32_t mine = 0;
   if (tid < B) {  // B <= 1024 = kThreads
-    const int32_t* control = a.scratch + static_cast<uint64_t>(tid) * kRowWords + 2 * kSlots;
+    const int32_t* control = a.scratch + static_cast<uint64_t>(tid) * kRowWords + 3 * kSlots;
     const int32_t st = control[0], unique = control[1];
     if (st == 0) mine = static_cast<uint32_t>(unique);
     a.miss_counts[tid] = st == 0 ? unique : -1;
@@ -362,10 +381,11 @@ __device__ void lidu_compact(const KvipLiduArgs& a) {
     a.miss_counts[B] = static_cast<int32_t>(total);
   }
   __syncthreads();
-  // four descriptors per thread and round: their loads are issued together (two dependent loads each)
+  if (B == 1u) return;  // a single request wrote its descriptors in place
+  // four descriptors per thread and round, all loads first: the request CTAs left final values in their scratch
   for (uint32_t base = 0; base < total; base += 4u * kThreads) {
-    uint32_t request[4], at[4];
-    int32_t token[4], slot[4], block[4];
+    const int32_t* from[4];
+    int32_t index[4], offset[4], output[4];
 #pragma unroll
     for (uint32_t u = 0; u < 4; ++u) {
       const uint32_t o = base + u * kThreads + tid;
@@ -374,29 +394,21 @@ __device__ void lidu_compact(const KvipLiduArgs& a) {
         const uint32_t mid = (lo + hi) >> 1;
         if (offsets[mid] <= o) lo = mid; else hi = mid;
       }
-      request[u] = lo;
-      at[u] = o < total ? o - offsets[lo] : 0u;
+      from[u] = a.scratch + static_cast<uint64_t>(lo) * kRowWords + (o < total ? o - offsets[lo] : 0u);
     }
 #pragma unroll
     for (uint32_t u = 0; u < 4; ++u) {
-      const int32_t* work = a.scratch + static_cast<uint64_t>(request[u]) * kRowWords;
-      token[u] = work[at[u]];
-      slot[u] = work[kSlots + at[u]];
-    }
-#pragma unroll
-    for (uint32_t u = 0; u < 4; ++u) {
-      const uint32_t o = base + u * kThreads + tid;
-      const uint32_t entry = o < total ? static_cast<uint32_t>(slot[u]) >> 7 : 0u;
-      block[u] = a.resident_block_table[static_cast<uint64_t>(request[u]) * a.resident_blocks + entry];
+      index[u] = from[u][0];
+      offset[u] = from[u][kSlots];
+      output[u] = from[u][2 * kSlots];
     }
 #pragma unroll
     for (uint32_t u = 0; u < 4; ++u) {
       const uint32_t o = base + u * kThreads + tid;
       if (o < total) {
-        const int64_t pool = a.req_pool_entries[request[u]];
-        a.indices[o] = static_cast<int32_t>((pool * a.num_layers + a.layer_id) * a.qcap + (token[u] >> 7));
-        a.offsets[o] = (token[u] & 127) * 656;
-        a.output_indices[o] = block[u] < 0 ? -1 : block[u] * 128 + (slot[u] & 127);
+        a.indices[o] = index[u];
+        a.offsets[o] = offset[u];
+        a.output_indices[o] = output[u];
       }
     }
   }
