@@ -6,7 +6,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import TOPK, SLOTS, LRU_SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS
+from ._lib import TOPK, SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS
 
 
 def _stream(device):
