@@ -50,20 +50,51 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs 
 }
 
 // ---- dense gather --------------------------------------------------------------------------
+// A warp gathers kGatherPerWarp consecutive entries of an output row: their slot numbers come with one load
+// (one lane each), then every source row's three 512-byte requests are in flight together before the first
+// store, so a warp keeps 4.5 KB moving instead of 1.1 KB behind a dependent index load.
+constexpr uint32_t kGatherPerWarp = 4;
+
 __global__ void __launch_bounds__(256) gather_rows(const KvipGatherArgs a) {
   const uint32_t row = blockIdx.y, lane = threadIdx.x & 31u;
-  const uint32_t k = blockIdx.x * 8u + (threadIdx.x >> 5);
+  const uint32_t k0 = (blockIdx.x * 8u + (threadIdx.x >> 5)) * kGatherPerWarp;
   const uint32_t b = row / a.queries;
   const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
-  const int32_t slot = a.slots[static_cast<uint64_t>(row) * kTop + k];
-  uint8_t* dst = a.out + (static_cast<uint64_t>(row) * kTop + k) * a.tokenBytes;
-  if (slot < 0 || static_cast<uint32_t>(slot) >= a.outputStride) {
-    uint4* d = reinterpret_cast<uint4*>(dst);
-    for (uint32_t p = lane; p < (a.tokenBytes >> 4); p += 32u) d[p] = make_uint4(0, 0, 0, 0);
+  const int32_t my_slot = lane < kGatherPerWarp ? a.slots[static_cast<uint64_t>(row) * kTop + k0 + lane] : -1;
+  const uint32_t pieces = a.tokenBytes >> 4;
+  uint8_t* dst0 = a.out + (static_cast<uint64_t>(row) * kTop + k0) * a.tokenBytes;
+  if (pieces > 96u) {  // rows beyond 1536 bytes: one entry after the other
+    for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
+      const int32_t slot = __shfl_sync(0xffffffffu, my_slot, e);
+      uint4* d = reinterpret_cast<uint4*>(dst0 + static_cast<uint64_t>(e) * a.tokenBytes);
+      if (slot < 0 || static_cast<uint32_t>(slot) >= a.outputStride) {
+        for (uint32_t p = lane; p < pieces; p += 32u) d[p] = make_uint4(0, 0, 0, 0);
+      } else {
+        copy_row_warp(reinterpret_cast<uint8_t*>(d),
+                      a.pool + (static_cast<uint64_t>(owner) * a.outputStride + static_cast<uint32_t>(slot)) * a.tokenBytes,
+                      a.tokenBytes, lane);
+      }
+    }
     return;
   }
-  const uint8_t* src = a.pool + (static_cast<uint64_t>(owner) * a.outputStride + static_cast<uint32_t>(slot)) * a.tokenBytes;
-  copy_row_warp(dst, src, a.tokenBytes, lane);
+  uint4 v[kGatherPerWarp][3];
+#pragma unroll
+  for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
+    const int32_t slot = __shfl_sync(0xffffffffu, my_slot, e);
+    const bool live = slot >= 0 && static_cast<uint32_t>(slot) < a.outputStride;
+    const uint4* s = reinterpret_cast<const uint4*>(
+        a.pool + (static_cast<uint64_t>(owner) * a.outputStride + (live ? static_cast<uint32_t>(slot) : 0u)) * a.tokenBytes);
+#pragma unroll
+    for (uint32_t k = 0; k < 3; ++k)
+      v[e][k] = (live && lane + 32u * k < pieces) ? __ldcs(s + lane + 32u * k) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
+    uint4* d = reinterpret_cast<uint4*>(dst0 + static_cast<uint64_t>(e) * a.tokenBytes);
+#pragma unroll
+    for (uint32_t k = 0; k < 3; ++k)
+      if (lane + 32u * k < pieces) d[lane + 32u * k] = v[e][k];
+  }
 }
 
 // ---- paged Index-cache ingest ----------------------------------------------------------------
@@ -233,7 +264,7 @@ uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream) {
 }
 
 uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream) {
-  dim3 grid(kTop / 8u, a.rows);
+  dim3 grid(kTop / (8u * kGatherPerWarp), a.rows);
   gather_rows<<<grid, 256, 0, stream>>>(a);
   count_launch();
   return check_launch("gather_rows");
