@@ -2,7 +2,7 @@
 //
 // A full radix pass costs one shared-memory atomic per score, and those atomics (not the memory
 // traffic) are what a histogram-per-pass selection spends its time on. Here only a SAMPLE of the row
-// (256 evenly spaced 128-byte lines, 8192 scores) goes through a 12-bit histogram. From it a pivot bin
+// (128 evenly spaced 128-byte lines per CTA, 4096 scores) goes through a 12-bit histogram. From it a pivot bin
 // is chosen that, with a 4-sigma margin, holds at least 2048 keys at or above its lower edge. One
 // streaming pass over the row then keeps every score at or above the pivot, in position order, in a
 // shared-memory list (ballot + prefix sums, no atomics): typically 3000-6000 of 131072. The exact
@@ -28,7 +28,7 @@ namespace {
 
 using namespace topk_core;
 
-constexpr uint32_t kSampleLines = 256;        // 128-byte lines of the row that feed the pivot histogram
+constexpr uint32_t kSampleLines = 128;        // 128-byte lines per CTA that feed the pivot histogram (4096 scores)
 constexpr uint32_t kPivotCandidates = 8192;   // capacity of the filtered list (keys + positions: 64 KiB)
 constexpr uint32_t kRoundChunks = 8;          // chunks of 16384 scores whose pass masks a thread keeps in registers
 
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   for (uint32_t i = tid; i < 4096; i += kThreads) hist[i] = 0;
   __syncthreads();
   const uint32_t lines = (L + 31u) >> 5;                       // <= 65536
-  const uint32_t sample_lines = min(lines, kSampleLines * ranks);   // every CTA of the cluster samples up to 256 lines
+  const uint32_t sample_lines = min(lines, kSampleLines * ranks);   // every CTA of the cluster samples up to 128 lines
   {
     constexpr uint32_t kPerWarp = kSampleLines / (kThreads / 32u);  // every warp: the same trip count
     float x[kPerWarp];
