@@ -71,32 +71,58 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
   __syncthreads();
 
   // ---- 1. classification of all queries ------------------------------------------------
-  for (uint32_t i = tid; i < Q * kTop; i += kThreads) {
-    const int32_t token = selected[i];
-    uint32_t slot = kMissing;
-    if (token >= 0) {
-      if (static_cast<uint32_t>(token) >= H) {
-        atomicOr(ctl + 1, KVIP_ERR_TOKEN_RANGE);
-      } else if (static_cast<uint32_t>(token) < R && valid[token] != 0 && reserved[token] < 0) {
-        slot = static_cast<uint32_t>(token);
-        atomicOr(bitmap + (slot >> 5), 1u << (slot & 31u));
-      }
-    }
-    loc[i] = slot;
+  // A thread owns TopK positions 2*tid and 2*tid+1 of every query row and keeps their tokens and locations in
+  // registers for the whole kernel. All token loads are issued first, then all residency lookups, so the four
+  // rows cost one pair of memory round trips instead of one per row.
+  int32_t token[KVIP_MAX_QUERIES][2];
+  uint32_t where[KVIP_MAX_QUERIES][2];
+#pragma unroll
+  for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q) {
+    const int2 pair = *reinterpret_cast<const int2*>(selected + min(q, Q - 1u) * kTop + tid * 2u);
+    token[q][0] = q < Q ? pair.x : -1;
+    token[q][1] = q < Q ? pair.y : -1;
   }
+  int32_t is_valid[KVIP_MAX_QUERIES][2], ordinal[KVIP_MAX_QUERIES][2];
+#pragma unroll
+  for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q)
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+      const bool resident_position = token[q][j] >= 0 && static_cast<uint32_t>(token[q][j]) < R;
+      is_valid[q][j] = valid[resident_position ? token[q][j] : 0];
+      ordinal[q][j] = reserved[resident_position ? token[q][j] : 0];
+    }
+#pragma unroll
+  for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q)
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+      uint32_t slot = kMissing;
+      if (q < Q && token[q][j] >= 0) {
+        if (static_cast<uint32_t>(token[q][j]) >= H) {
+          atomicOr(ctl + 1, KVIP_ERR_TOKEN_RANGE);
+        } else if (static_cast<uint32_t>(token[q][j]) < R && is_valid[q][j] != 0 && ordinal[q][j] < 0) {
+          slot = static_cast<uint32_t>(token[q][j]);
+          atomicOr(bitmap + (slot >> 5), 1u << (slot & 31u));
+        }
+      }
+      where[q][j] = slot;
+      if (q < Q) loc[q * kTop + tid * 2u + j] = slot;
+    }
   __syncthreads();
 
   // ---- 2. queries in order ---------------------------------------------------------------
-  for (uint32_t q = 0; q < Q && !ctl[1]; ++q) {
+#pragma unroll
+  for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q) {
+    if (q >= Q || ctl[1]) break;   // block-uniform
     const uint32_t begin = q * kTop, old_count = ctl[0];
     // 2a. hash insert, first occurrence by atomicMin on the position
-    for (uint32_t i = begin + tid; i < begin + kTop; i += kThreads) {
-      const int32_t token = selected[i];
-      if (token < 0 || static_cast<uint32_t>(token) >= H || loc[i] != kMissing) continue;
-      uint32_t h = sparse_hash(static_cast<uint32_t>(token)) & (kBuckets - 1u);
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+      const uint32_t i = begin + tid * 2u + j;
+      if (token[q][j] < 0 || static_cast<uint32_t>(token[q][j]) >= H || where[q][j] != kMissing) continue;
+      uint32_t h = sparse_hash(static_cast<uint32_t>(token[q][j])) & (kBuckets - 1u);
       for (uint32_t probe = 0; probe < kBuckets; ++probe) {
-        const uint32_t prev = atomicCAS(keys + h, kEmpty, static_cast<uint32_t>(token));
-        if (prev == kEmpty || prev == static_cast<uint32_t>(token)) {
+        const uint32_t prev = atomicCAS(keys + h, kEmpty, static_cast<uint32_t>(token[q][j]));
+        if (prev == kEmpty || prev == static_cast<uint32_t>(token[q][j])) {
           // a tagged rank belongs to an earlier query: its slot is reused, not re-ranked
           if (!(ranks[h] != kEmpty && (ranks[h] & kRankTag))) atomicMin(ranks + h, i);
           break;
@@ -107,12 +133,12 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
     __syncthreads();
     // 2b. rank the first occurrences by ascending position (2 consecutive positions / thread)
     uint32_t is_new[2] = {0, 0}, bucket[2] = {0, 0};
+#pragma unroll
     for (uint32_t j = 0; j < 2; ++j) {
       const uint32_t i = begin + tid * 2u + j;
-      const int32_t token = selected[i];
-      if (token < 0 || static_cast<uint32_t>(token) >= H || loc[i] != kMissing) continue;
-      uint32_t h = sparse_hash(static_cast<uint32_t>(token)) & (kBuckets - 1u), probes = 0;
-      while (keys[h] != static_cast<uint32_t>(token) && probes < kBuckets) { h = (h + 1u) & (kBuckets - 1u); ++probes; }
+      if (token[q][j] < 0 || static_cast<uint32_t>(token[q][j]) >= H || where[q][j] != kMissing) continue;
+      uint32_t h = sparse_hash(static_cast<uint32_t>(token[q][j])) & (kBuckets - 1u), probes = 0;
+      while (keys[h] != static_cast<uint32_t>(token[q][j]) && probes < kBuckets) { h = (h + 1u) & (kBuckets - 1u); ++probes; }
       if (probes == kBuckets) { atomicOr(ctl + 1, KVIP_ERR_HASH); continue; }
       bucket[j] = h;
       is_new[j] = ranks[h] == i ? 1u : 0u;
@@ -123,7 +149,7 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
       if (!is_new[j]) continue;
       const uint32_t rank = old_count + offset++;
       ranks[bucket[j]] = kRankTag | rank;
-      ev_src[rank] = selected[begin + tid * 2u + j];
+      ev_src[rank] = token[q][j];
     }
     __syncthreads();
     // 2c. victims from the LRU candidate list, in list order, unprotected only
@@ -193,13 +219,13 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
     __syncthreads();
     if (ctl[1]) break;
     // 2e. publish locations of this query and the per-slot records
-    for (uint32_t i = begin + tid; i < begin + kTop; i += kThreads) {
-      const int32_t token = selected[i];
-      if (token < 0 || loc[i] != kMissing) continue;
-      uint32_t h = sparse_hash(static_cast<uint32_t>(token)) & (kBuckets - 1u), probes = 0;
-      while (keys[h] != static_cast<uint32_t>(token) && probes < kBuckets) { h = (h + 1u) & (kBuckets - 1u); ++probes; }
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+      if (token[q][j] < 0 || where[q][j] != kMissing) continue;
+      uint32_t h = sparse_hash(static_cast<uint32_t>(token[q][j])) & (kBuckets - 1u), probes = 0;
+      while (keys[h] != static_cast<uint32_t>(token[q][j]) && probes < kBuckets) { h = (h + 1u) & (kBuckets - 1u); ++probes; }
       if (probes == kBuckets) { atomicOr(ctl + 1, KVIP_ERR_HASH); continue; }
-      loc[i] = static_cast<uint32_t>(ev_dst[ranks[h] & ~kRankTag]);
+      loc[begin + tid * 2u + j] = static_cast<uint32_t>(ev_dst[ranks[h] & ~kRankTag]);
     }
     for (uint32_t i = tid; i < added; i += kThreads) {
       const uint32_t rank = old_count + i;
