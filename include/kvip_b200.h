@@ -324,6 +324,27 @@ uint32_t kvip_b200_update_abc(int32_t* token_to_slot, int32_t* slot_to_token,
                               uint32_t requests, uint32_t pool, uint32_t tokens,
                               uint32_t slots, uint32_t history, uint32_t tail, void* stream);
 
+/* ---- Appended host pages (python/kvip/cache/page_updates.py:5-62; the Triton program it
+ * replaces is python/kvip/cache/_page_updates_kernel.py:8-40). One launch publishes every
+ * page appended this step, over all requests and groups: addresses[index] = address,
+ * valid[index] = 1, token_to_slot[clear : clear+block] = -1 when clear >= 0, and for fused
+ * groups the per-token addresses fused[group][owner, page*block + lane] =
+ * address + lane * bytes_per_token[group] for tokens below `history`.
+ * A row whose index or clear range is out of bounds is skipped and counted in *errors. */
+typedef struct KvipPagesArgs {
+  const int64_t* rows;         /* [count,3]: flat page index, host address, first map entry to clear or -1 */
+  int64_t* addresses;          /* [owners, groups, pages] */
+  int32_t* valid;              /* [owners, groups, pages] */
+  int32_t* token_to_slot;      /* flat, map_entries long */
+  const int64_t* fused_table;  /* [groups,2]: device pointer of an int64 [owners, history] table, bytes per
+                                  token; NULL when no group keeps per-token addresses */
+  int32_t* errors;             /* [1] in/out: rows skipped; may be NULL */
+  uint64_t map_entries;
+  uint32_t count, owners, groups, pages;
+  uint32_t block, history, reserved0, reserved1;
+} KvipPagesArgs;
+uint32_t kvip_b200_publish_pages(const KvipPagesArgs* args, void* stream);
+
 /* ---- LIDU: the serial-chain slot resolver -------------------------------------------
  * Same 24 arguments, in the same order, as
  * nanovllm_dsa::lidu_fused_batch_get_prepare_mtp_out

@@ -23,6 +23,7 @@ _EXPORTS = {
     "IndexSelector": ("adapters", "IndexSelector"),
     "PagedIndexer": ("adapters", "PagedIndexer"),
     "RequestPlan": ("adapters", "RequestPlan"),
+    "PageUpdates": ("cache.page_updates", "PageUpdates"),  # reference: kvip.cache.page_updates.PageUpdates
     "FusedQueryInputs": ("inputs", "QueryInputs"),
     "FusedWorkspace": ("operators.lifetch", "LIFetchWorkspace"),
 }

@@ -96,6 +96,11 @@ LiduArgs = _struct("LiduArgs", (
                         "resident_blocks", "bitmap_words", "reserved0")] + [("scratch", vp)])
 
 
+PagesArgs = _struct("PagesArgs", ("rows", "addresses", "valid", "token_to_slot", "fused_table", "errors"),
+                    [("map_entries", u64)] + [(n, u32) for n in (
+                        "count", "owners", "groups", "pages", "block", "history", "reserved0", "reserved1")])
+
+
 class Context(ctypes.Structure):
     """KvipContext; reference: rotating::Context (include/context.h:36-52)."""
 
@@ -123,7 +128,7 @@ _STAGES = {
     "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs,
     "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
-    "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs,
+    "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs, "kvip_b200_publish_pages": PagesArgs,
 }
 # every symbol include/kvip_b200.h declares
 EXPORTS = tuple(_STAGES) + (

@@ -254,6 +254,38 @@ __global__ void __launch_bounds__(256) abc_rows(int32_t* t2s, int32_t* s2t, cons
   }
 }
 
+// ---- appended host pages ---------------------------------------------------------------------------
+// One CTA per appended page; the lanes cover the page's tokens.
+__global__ void __launch_bounds__(128) publish_pages(const KvipPagesArgs a) {
+  const int64_t* row = a.rows + static_cast<uint64_t>(blockIdx.x) * 3u;
+  const int64_t index = row[0], address = row[1], clear = row[2];
+  const uint64_t per_owner = static_cast<uint64_t>(a.groups) * a.pages;
+  const bool bad = index < 0 || static_cast<uint64_t>(index) >= per_owner * a.owners ||
+                   (clear >= 0 && static_cast<uint64_t>(clear) + a.block > a.map_entries);
+  if (bad) {
+    if (threadIdx.x == 0 && a.errors) atomicAdd(a.errors, 1);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    a.addresses[index] = address;
+    a.valid[index] = 1;
+  }
+  if (clear >= 0)
+    for (uint32_t lane = threadIdx.x; lane < a.block; lane += blockDim.x) a.token_to_slot[clear + lane] = -1;
+  if (a.fused_table) {
+    const uint64_t owner = static_cast<uint64_t>(index) / per_owner;
+    const uint32_t group = static_cast<uint32_t>(static_cast<uint64_t>(index) / a.pages % a.groups);
+    const uint64_t page = static_cast<uint64_t>(index) % a.pages;
+    int64_t* table = reinterpret_cast<int64_t*>(a.fused_table[group * 2u]);
+    const int64_t bytes = a.fused_table[group * 2u + 1u];
+    if (table)
+      for (uint32_t lane = threadIdx.x; lane < a.block; lane += blockDim.x) {
+        const uint64_t token = page * a.block + lane;
+        if (token < a.history) table[owner * a.history + token] = address + static_cast<int64_t>(lane) * bytes;
+      }
+  }
+}
+
 }  // namespace
 
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream) {
@@ -355,6 +387,16 @@ extern "C" uint32_t kvip_b200_lru_commit(const KvipLruArgs* a, void* stream) {
   kvip::lru_commit<<<a->rows, kvip::kLruThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
   kvip::count_launch();
   return kvip::check_launch("lru_commit");
+}
+
+extern "C" uint32_t kvip_b200_publish_pages(const KvipPagesArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->rows && a->addresses && a->valid && a->token_to_slot, "publish_pages: null pointer");
+  KVIP_REQUIRE(a->owners >= 1 && a->groups >= 1 && a->pages >= 1 && a->block >= 1, "publish_pages: geometry");
+  KVIP_REQUIRE(a->fused_table == nullptr || a->history >= 1, "publish_pages: fused groups need a history length");
+  if (a->count == 0) return 0u;
+  kvip::publish_pages<<<a->count, 128, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::count_launch();
+  return kvip::check_launch("publish_pages");
 }
 
 extern "C" uint32_t kvip_b200_update_abc(int32_t* token_to_slot, int32_t* slot_to_token, const int32_t* descriptors,

@@ -464,6 +464,25 @@ def update_abc(token_to_slot, slot_to_token, descriptors, requests, history, tai
             reverse[tokens % tail] = tokens
 
 
+def publish_pages(rows, addresses, valid, token_to_slot, fused=(), widths=(), token_bytes=656, block=128):
+    """python/kvip/cache/page_updates.py:49-62 (CPU branch), rows applied in order; the per-token table of a
+    fused group is clipped at its history length as the device program does
+    (python/kvip/cache/_page_updates_kernel.py:33-40)."""
+    owners, groups, pages = addresses.shape
+    for index, address, clear in np.asarray(rows, dtype=np.int64).reshape(-1, 3):
+        owner, rem = divmod(int(index), groups * pages)
+        group, page = divmod(rem, pages)
+        addresses.reshape(-1)[index] = address
+        valid.reshape(-1)[index] = 1
+        if clear >= 0:
+            token_to_slot.reshape(-1)[clear : clear + block] = -1
+        if len(fused):
+            history = fused[group].shape[1]
+            first = page * block
+            live = max(0, min(block, history - first))
+            fused[group][owner, first : first + live] = address + np.arange(live, dtype=np.int64) * widths[group] * token_bytes
+
+
 # ---------------------------------------------------------------------------------------------
 # LIDU (csrc/operators/lidu/op_kernel/a5_lidu_fused_batch_get_prepare_mtp.cpp, lines cited in
 # kvip_b200/csrc/lidu.cu); unique misses ordered by (query, TopK position) of first occurrence

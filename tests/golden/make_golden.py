@@ -8,7 +8,8 @@ What is imported and executed (paths inside the reference project):
   * tests/operators/lifetch/support/workloads.py: prepare_fixture, prepare_full_chain_fixture,
     prepare_compact_fixture (their logical_scores.npy are the reference's score goldens);
   * tests/operators/lifetch/support/correctness.py: validate_topk (kept as a cross-check here);
-  * python/kvip/cache/lru.py (+ numba kernels), python/kvip/cache/abc.py (CPU branch);
+  * python/kvip/cache/lru.py (+ numba kernels), python/kvip/cache/abc.py (CPU branch),
+    python/kvip/cache/page_updates.py (CPU branch);
   * python/kvip/adapters/vllm/inputs.py + index_import.py (QueryInputs, ingest_decode on CPU);
   * oracle/_ref/hot_slot_ref: the reference's csrc/operators/lidu/op_kernel/hot_slot_selection.h
     compiled by oracle/Makefile, fed the cases of tests/operators/lidu/test_hot_slot_selection.py.
@@ -84,10 +85,39 @@ def lru_trace(SlotLRU):
     return steps, snapshots
 
 
+def page_updates_fixture(torch):
+    """Two submits through the reference's PageUpdates on CPU tensors (its sequential branch): two groups with
+    656- and 2624-byte rows, per-token address tables, and map ranges to clear."""
+    from kvip.cache.page_updates import PageUpdates
+    rng = np.random.default_rng(31)
+    owners, groups, pages, block = 3, 2, 8, 128
+    addresses = torch.zeros((owners, groups, pages), dtype=torch.int64)
+    valid = torch.zeros((owners, groups, pages), dtype=torch.int32)
+    token_to_slot = torch.from_numpy(rng.integers(0, 4096, owners * 2048).astype(np.int32))
+    fused = [torch.full((owners, pages * block), -7, dtype=torch.int64) for _ in range(groups)]
+    updates = PageUpdates(torch, addresses, valid, token_to_slot, fused=fused, widths=(1, 4), token_bytes=656,
+                          block_size=block)
+    store = dict(map0=token_to_slot.numpy().copy(), shape=np.asarray([owners, groups, pages, block], np.int64))
+    for ring in (0, 1):
+        indices = rng.permutation(owners * groups * pages)[:11]
+        rows = [[int(i), int(rng.integers(1, 1 << 40)) & ~0xFF, int(rng.choice([-1, 128 * int(rng.integers(0, 47))]))]
+                for i in indices]
+        updates.submit(rows, ring)
+        store.update({f"rows{ring}": np.asarray(rows, np.int64), f"addresses{ring}": addresses.numpy().copy(),
+                      f"valid{ring}": valid.numpy().copy(), f"map{ring + 1}": token_to_slot.numpy().copy(),
+                      f"fused{ring}_0": fused[0].numpy().copy(), f"fused{ring}_1": fused[1].numpy().copy()})
+    np.savez_compressed(HERE / "page_updates.npz", **store)
+
+
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    arguments = [a for a in sys.argv[1:] if not a.startswith("--only=")]
+    only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
+    reference = Path(arguments[0] if arguments else "/root/reference")
     sys.path[:0] = [str(reference / "python"), str(reference / "tests/operators/lifetch/support")]
     import torch
+    if only == ["page_updates"]:  # regenerate this fixture alone
+        page_updates_fixture(torch)
+        return
     import workloads
     from correctness import validate_topk
 
@@ -134,6 +164,8 @@ def main():
         stages.append((descriptors.numpy().copy(), t2s.numpy().copy(), s2t.numpy().copy()))
     np.savez_compressed(HERE / "abc_maps.npz", d0=stages[0][0], t0=stages[0][1], s0=stages[0][2], d1=stages[1][0],
                         t1=stages[1][1], s1=stages[1][2])
+
+    page_updates_fixture(torch)
 
     # ---- QueryInputs + paged Index ingest --------------------------------------------------------
     from kvip.adapters.vllm.index_import import VllmIndexCacheStorage

@@ -8,7 +8,7 @@ import torch
 import kvip_oracle as oracle
 import workloads
 from golden_cases import GOLDEN, li_fixture_case
-from kvip_b200 import IndexCacheStorage, QueryInputs, SlotLRU, lidu, ops, update_abc
+from kvip_b200 import IndexCacheStorage, PageUpdates, QueryInputs, SlotLRU, lidu, ops, update_abc
 
 pytestmark = pytest.mark.gpu
 TOPK = 2048
@@ -89,6 +89,65 @@ def test_update_abc_matches_reference(device):
         assert np.array_equal(s2t.cpu().numpy(), data[f"s{stage}"])
     with pytest.raises(ValueError):
         update_abc(t2s.cpu(), s2t, torch.zeros((1, 1, 4), dtype=torch.int32, device=device), 1, 1024, 384)
+
+
+def test_page_updates_match_reference(device):
+    """PageUpdates.submit on the device against the arrays the reference's PageUpdates left after the same two
+    submits (python/kvip/cache/page_updates.py): committed addresses, valid flags, cleared map ranges and the
+    per-token address tables of a 656-byte and a 2624-byte group."""
+    data = np.load(GOLDEN / "page_updates.npz")
+    owners, groups, pages, block = (int(x) for x in data["shape"])
+    addresses = torch.zeros((owners, groups, pages), dtype=torch.int64, device=device)
+    valid = torch.zeros((owners, groups, pages), dtype=torch.int32, device=device)
+    token_to_slot = torch.from_numpy(data["map0"]).to(device)
+    fused = [torch.full((owners, pages * block), -7, dtype=torch.int64, device=device) for _ in range(groups)]
+    updates = PageUpdates(torch, addresses, valid, token_to_slot, fused=fused, widths=(1, 4), token_bytes=656,
+                          block_size=block)
+    for ring in (0, 1):
+        updates.submit(data[f"rows{ring}"].tolist(), ring)
+        torch.cuda.synchronize()
+        assert np.array_equal(addresses.cpu().numpy(), data[f"addresses{ring}"])
+        assert np.array_equal(valid.cpu().numpy(), data[f"valid{ring}"])
+        assert np.array_equal(token_to_slot.cpu().numpy(), data[f"map{ring + 1}"])
+        for g in range(groups):
+            assert np.array_equal(fused[g].cpu().numpy(), data[f"fused{ring}_{g}"])
+    assert int(updates.errors.item()) == 0
+    updates.submit([], 0)  # nothing appended: no launch
+    with pytest.raises(IndexError):
+        updates.submit([[owners * groups * pages, 0, -1]], 0)
+    with pytest.raises(IndexError):
+        updates.submit([[0, 0, token_to_slot.numel() - block + 1]], 0)
+    with pytest.raises(ValueError):
+        updates.submit([[1, 8, -1], [1, 16, -1]], 0)
+    with pytest.raises(ValueError):
+        PageUpdates(torch, addresses.cpu(), valid, token_to_slot)
+
+
+@pytest.mark.parametrize("fused_groups", [False, True])
+def test_page_updates_ragged_history_and_every_page(device, fused_groups):
+    """Every page of every owner and group in one submit, a history that ends inside the last page (the
+    per-token table is clipped there), a block size that is not the thread count, against the oracle."""
+    rng = np.random.default_rng(5)
+    owners, groups, pages, block, history = 5, 3, 7, 96, 7 * 96 - 40
+    addresses_h = rng.integers(0, 1 << 40, (owners, groups, pages)).astype(np.int64)
+    valid_h = np.zeros((owners, groups, pages), np.int32)
+    map_h = rng.integers(0, 1 << 20, 120 * block).astype(np.int32)
+    fused_h = [rng.integers(0, 99, (owners, history)).astype(np.int64) for _ in range(groups)] if fused_groups else []
+    order = rng.permutation(owners * groups * pages)
+    starts = rng.permutation(len(map_h) // block)[:len(order)] * block  # disjoint map ranges
+    rows = [[int(i), int(rng.integers(0, 1 << 44)), int(s) if k % 3 else -1] for k, (i, s) in enumerate(zip(order, starts))]
+    addresses, valid, token_to_slot = (torch.from_numpy(x.copy()).to(device) for x in (addresses_h, valid_h, map_h))
+    fused = [torch.from_numpy(x.copy()).to(device) for x in fused_h]
+    updates = PageUpdates(torch, addresses, valid, token_to_slot, fused=fused, widths=(1, 4, 2) if fused_groups else (),
+                          token_bytes=1152, block_size=block)
+    updates.submit(rows, 1)
+    torch.cuda.synchronize()
+    oracle.publish_pages(rows, addresses_h, valid_h, map_h, fused_h, (1, 4, 2), 1152, block)
+    assert np.array_equal(addresses.cpu().numpy(), addresses_h) and np.array_equal(valid.cpu().numpy(), valid_h)
+    assert np.array_equal(token_to_slot.cpu().numpy(), map_h)
+    for g in range(len(fused)):
+        assert np.array_equal(fused[g].cpu().numpy(), fused_h[g])
+    assert int(updates.errors.item()) == 0 and (valid_h == 1).all()
 
 
 def test_index_storage_ingest_decode_matches_reference(device):

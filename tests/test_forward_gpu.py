@@ -385,3 +385,48 @@ def test_status_reports_exhausted_pool(device):
     assert int(p.update.status[0]) == oracle.ERR_NO_SLOT
     assert (p.update.slot_output.cpu().numpy() == -1).all()
     assert int(p.storage.hot_valid.sum()) == 0
+
+
+def _sparse_attention(query, rows):
+    """The consumer's arithmetic over 2048 selected KV rows of 576 bf16 values (512 latent + 64 rotary): keys are
+    the whole row, values its first 512 entries; softmax in fp32, probabilities rounded to bf16 before the
+    value product, as the reference's check does (tests/operators/lifetch/support/correctness.py:281-296)."""
+    kv = rows.view(torch.bfloat16).float()                       # [2048, 576]
+    logits = query.float() @ kv.T * 576 ** -0.5                   # [8, 2048]
+    prob = torch.softmax(logits, dim=-1).to(torch.bfloat16).float()
+    return prob @ kv[:, :512]
+
+
+def test_sparse_attention_over_slot_output_equals_attention_over_logical_tokens(device):
+    """End-to-end consumer check (reference: check_sfa, tests/operators/lifetch/support/correctness.py:262-339):
+    sparse attention that reads the resident pool through `slot_output` (and, separately, the dense gathered
+    rows) must give what attention over the same logical tokens' rows of the backing pool gives. Tolerances are
+    the reference's (atol 0.006, rtol 0.025); since the rows must be the same bytes in the same order, the
+    results are also required to be identical. Steps mix misses (first step, new queries) and hits (repeat)."""
+    history, resident = 8192, 4096
+    p = DecodePipeline(device, batch=3, queries=2, heads=64, history=history, resident=resident, len_lo=6000,
+                       len_hi=8192, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152, seed=41, host_pool=False)
+    generator = torch.Generator(device=device).manual_seed(181)
+    kv = torch.rand(p.source.shape[0], 576, generator=generator, device=device) * 2 - 1
+    p.source.view(torch.bfloat16).copy_(kv.to(torch.bfloat16))
+    query = (torch.rand(p.batch * 2, 8, 576, generator=generator, device=device) * 0.4 - 0.2).to(torch.bfloat16)
+    fetched = []
+    for step, seed in enumerate((41, 141, 41)):
+        p.new_queries(seed)
+        p.step()
+        torch.cuda.synchronize()
+        assert int(p.update.status.abs().sum()) == 0
+        fetched.append(int(p.rotating.query_counts[:, 4].sum()))
+        for row in range(p.batch * 2):
+            owner = p.row_owner_list[row // 2]
+            logical = p.update.logical_output[row, 0].long()
+            slots = p.update.slot_output[row, 0].long()
+            assert int(logical.min()) >= 0 and int(slots.min()) >= 0 and int(slots.max()) < resident
+            expected = _sparse_attention(query[row], p.source[owner * history + logical])
+            through_slots = _sparse_attention(query[row], p.pool_hbm[owner * p.output_stride + slots])
+            through_gather = _sparse_attention(query[row], p.gather_out[row])
+            assert bool(torch.isfinite(through_slots).all())
+            for actual in (through_slots, through_gather):
+                assert torch.allclose(actual, expected, atol=0.006, rtol=0.025)
+                assert torch.equal(actual, expected)
+    assert fetched[0] > 0 and fetched[1] > 0 and fetched[2] < fetched[0]   # misses, misses, mostly hits

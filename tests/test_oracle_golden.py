@@ -97,6 +97,21 @@ def test_abc_matches_reference():
         assert np.array_equal(t2s, data[f"t{stage}"]) and np.array_equal(s2t, data[f"s{stage}"])
 
 
+def test_publish_pages_matches_reference():
+    """Two submits recorded from the reference's PageUpdates (python/kvip/cache/page_updates.py, CPU branch)."""
+    data = np.load(GOLDEN / "page_updates.npz")
+    owners, groups, pages, block = (int(x) for x in data["shape"])
+    addresses = np.zeros((owners, groups, pages), np.int64)
+    valid = np.zeros((owners, groups, pages), np.int32)
+    token_to_slot = data["map0"].copy()
+    fused = [np.full((owners, pages * block), -7, np.int64) for _ in range(groups)]
+    for ring in (0, 1):
+        oracle.publish_pages(data[f"rows{ring}"], addresses, valid, token_to_slot, fused, (1, 4), 656, block)
+        assert np.array_equal(addresses, data[f"addresses{ring}"]) and np.array_equal(valid, data[f"valid{ring}"])
+        assert np.array_equal(token_to_slot, data[f"map{ring + 1}"])
+        assert all(np.array_equal(fused[g], data[f"fused{ring}_{g}"]) for g in range(groups))
+
+
 def test_ingest_decode_matches_reference():
     """VllmIndexCacheStorage.ingest_decode (python/kvip/adapters/vllm/index_import.py:38-52) on CPU torch."""
     d = np.load(GOLDEN / "ingest_decode.npz")
