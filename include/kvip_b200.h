@@ -37,6 +37,7 @@ extern "C" {
 #define KVIP_OPTION_DIAGNOSTICS 0x80000000u
 #define KVIP_OPTION_DEFERRED_FETCH 0x40000000u /* descriptors only: no fetch, no gather */
 #define KVIP_OPTION_SELECT_ONLY 0x20000000u    /* LI score -> TopK -> resolver, then return */
+#define KVIP_OPTION_SCORES_READY 0x08000000u   /* the score rows were written by earlier launches: the select phase starts at TopK */
 #define KVIP_OPTION_COMMIT_ONLY 0x10000000u    /* the rest of a SELECT_ONLY call: outputs -> exchange -> fetch (-> gather) */
 #define KVIP_BAD_ARGUMENT 100000u
 #define KVIP_CUDA_ERROR_BASE 200000u
@@ -345,6 +346,61 @@ typedef struct KvipPagesArgs {
 } KvipPagesArgs;
 uint32_t kvip_b200_publish_pages(const KvipPagesArgs* args, void* stream);
 
+/* ---- Speculative prefetch windows ------------------------------------------------------
+ * While the score kernel is still working on later key windows, rows of cold positions
+ * (>= resident) whose score already beats the resident threshold are pulled from the host
+ * pool (prefetch.h:577-821; budgets prefetch_budget.h:7-17: 512 rows per request and round,
+ * 480 per window; predicate indexer_score.h:976-1017). The threshold of a score row is the
+ * smallest score of the TopK over its resident prefix: every cold position of the final
+ * TopK beats it, so the candidates are a superset of the misses. Rows are staged in a
+ * separate HBM area keyed by source address, not in victim slots: the resolver, the Index
+ * exchange and the slot maps behave exactly as without speculation, and the final fetch
+ * copies a staged row from HBM instead of crossing the host link again. */
+typedef struct KvipWindowArgs {          /* per-window bounds for windowed score launches */
+  const int32_t* key_lengths;            /* [batch] */
+  const int32_t* query_ends;             /* [batch*queries] */
+  int32_t* window_lengths;               /* [windows, batch] out: clamp(length - first_w, 0, last_w - first_w) */
+  int32_t* window_ends;                  /* [windows, batch*queries] out, same clamp of the causal bound */
+  int32_t* staged_count;                 /* [batch] out: 0 */
+  int32_t* staged_rows;                  /* [batch] out: 0 */
+  int32_t* staged_hits;                  /* [batch] out: 0, or NULL */
+  uint32_t batch, queries, windows, reserved0;
+  uint32_t first[9];                     /* window w covers positions [first[w], first[w+1]); windows <= 8 */
+  uint32_t reserved1;
+} KvipWindowArgs;
+uint32_t kvip_b200_window_bounds(const KvipWindowArgs* args, void* stream);
+
+typedef struct KvipThresholdArgs {
+  const int32_t* prefix_topk;            /* [rows, 2048] TopK over the resident prefix */
+  const float* prefix_scores;            /* [rows, 2048] their scores */
+  uint32_t* thresholds;                  /* [rows] out: smallest selected key (order-preserving u32 image of the
+                                            score); 0 while the prefix holds fewer than 2048 valid positions */
+  uint32_t rows, reserved0;
+} KvipThresholdArgs;
+uint32_t kvip_b200_resident_threshold(const KvipThresholdArgs* args, void* stream);
+
+typedef struct KvipSpeculateArgs {
+  const float* scores;                   /* [batch*queries, scoreStride] */
+  const uint32_t* thresholds;            /* [batch*queries] keys from kvip_b200_resident_threshold */
+  const int32_t* key_lengths;            /* [batch] */
+  const int32_t* query_ends;             /* [batch*queries] */
+  const int32_t* row_owners;             /* [batch] or NULL */
+  const int64_t* addresses;              /* [owners, address_stride] source address of each Index position */
+  const uint8_t* source_base;            /* device-visible base of the host pool */
+  int64_t* staged_sources;               /* [batch, capacity] in/out */
+  int32_t* staged_count;                 /* [batch] in/out: candidates listed so far (clamped to the limit) */
+  int32_t* staged_rows;                  /* [batch] in/out: rows complete in the staging area */
+  uint8_t* staging;                      /* [batch, capacity, tokenBytes] */
+  uint64_t source_bytes;
+  uint32_t batch, queries, scoreStride, address_stride;
+  uint32_t first, last;                  /* cold window of positions, first >= resident */
+  uint32_t capacity;                     /* rows per request and round (<= 512) */
+  uint32_t limit;                        /* rows per request listed once this window is done (<= capacity) */
+  uint32_t tokenBytes, reserved0;
+} KvipSpeculateArgs;
+/* Two launches: list the window's candidates, then copy their rows into the staging area. */
+uint32_t kvip_b200_speculate_window(const KvipSpeculateArgs* args, void* stream);
+
 /* ---- LIDU: the serial-chain slot resolver -------------------------------------------
  * Same 24 arguments, in the same order, as
  * nanovllm_dsa::lidu_fused_batch_get_prepare_mtp_out
@@ -406,7 +462,14 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
   uint64_t dense_shadow, packed_fetch;
   uint64_t gather_out, topk_scores, li_status, topk_histogram, topk_split;
   uint64_t slots_ready_event;   /* optional cudaEvent_t recorded on the stream once the output rows are written */
-  uint8_t reserved[64];
+  /* rows staged by kvip_b200_speculate_window (all 0 = none): the fetch takes a missing row from the
+     staging area when its source address is listed there, and from the host pool otherwise */
+  uint64_t staged_sources;      /* int64 [batch, staged_capacity] */
+  uint64_t staged_rows;         /* int32 [batch]: rows of each request that are complete in the staging area */
+  uint64_t staging;             /* uint8 [batch, staged_capacity, tokenBytes] */
+  uint64_t staged_hits;         /* int32 [batch] or 0: incremented per missing row served from the staging area */
+  uint32_t staged_capacity, reserved2;
+  uint8_t reserved[24];
 } KvipWorkspace;
 
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,

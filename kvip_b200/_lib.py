@@ -11,7 +11,7 @@ u32, i32, u64, i64, vp, f32 = (ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64,
 
 TOPK, SLOTS, LRU_SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS, MAX_QUERIES = 2048, 8192, 2048, 10240, 128, 4
 OPTION_DIAGNOSTICS, OPTION_DEFERRED_FETCH = 0x80000000, 0x40000000
-OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY = 0x20000000, 0x10000000
+OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY, OPTION_SCORES_READY = 0x20000000, 0x10000000, 0x08000000
 TOPK_SPLIT_WORDS = 20544
 BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
@@ -101,6 +101,21 @@ PagesArgs = _struct("PagesArgs", ("rows", "addresses", "valid", "token_to_slot",
                         "count", "owners", "groups", "pages", "block", "history", "reserved0", "reserved1")])
 
 
+class WindowArgs(ctypes.Structure):
+    _fields_ = [(n, vp) for n in ("key_lengths", "query_ends", "window_lengths", "window_ends", "staged_count",
+                                  "staged_rows", "staged_hits")] + [
+        (n, u32) for n in ("batch", "queries", "windows", "reserved0")] + [("first", u32 * 9), ("reserved1", u32)]
+
+
+ThresholdArgs = _struct("ThresholdArgs", ("prefix_topk", "prefix_scores", "thresholds"), [("rows", u32), ("reserved0", u32)])
+
+SpeculateArgs = _struct("SpeculateArgs", (
+    "scores", "thresholds", "key_lengths", "query_ends", "row_owners", "addresses", "source_base", "staged_sources",
+    "staged_count", "staged_rows", "staging"), [("source_bytes", u64)] + [(n, u32) for n in (
+        "batch", "queries", "scoreStride", "address_stride", "first", "last", "capacity", "limit", "tokenBytes",
+        "reserved0")])
+
+
 class Context(ctypes.Structure):
     """KvipContext; reference: rotating::Context (include/context.h:36-52)."""
 
@@ -119,7 +134,8 @@ class Workspace(ctypes.Structure):
         "worker_status", "times")] + [(n, u32) for n in ("history", "resident", "options", "max_events")] + [
             (n, u64) for n in ("query_bitmaps", "query_errors", "update_bindings", "dense_shadow", "packed_fetch",
                                "gather_out", "topk_scores", "li_status", "topk_histogram", "topk_split",
-                               "slots_ready_event")] + [("reserved", ctypes.c_uint8 * 64)]
+                               "slots_ready_event", "staged_sources", "staged_rows", "staging", "staged_hits")] + [
+            ("staged_capacity", u32), ("reserved2", u32), ("reserved", ctypes.c_uint8 * 24)]
 
 
 _STAGES = {
@@ -129,6 +145,8 @@ _STAGES = {
     "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs, "kvip_b200_publish_pages": PagesArgs,
+    "kvip_b200_window_bounds": WindowArgs, "kvip_b200_resident_threshold": ThresholdArgs,
+    "kvip_b200_speculate_window": SpeculateArgs,
 }
 # every symbol include/kvip_b200.h declares
 EXPORTS = tuple(_STAGES) + (

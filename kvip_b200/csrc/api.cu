@@ -14,6 +14,7 @@ uint32_t launch_resolve_requests(const KvipResolveArgs& a, cudaStream_t stream);
 uint32_t launch_publish_outputs(const KvipResolveArgs& a, cudaStream_t stream);
 uint32_t launch_exchange(const KvipExchangeArgs& a, cudaStream_t stream);
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream);
+uint32_t launch_fetch_staged(const KvipFetchArgs& a, const KvipWorkspace& ws, cudaStream_t stream);
 uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream);
 
 namespace {
@@ -127,7 +128,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   li.scoreMode = s.scoreMode; li.ctas = s.smCount;
   KVIP_REQUIRE(li.query && li.keys && li.weights && li.key_lengths && li.query_ends && li.block_table && li.scores && li.status,
                "forward: an LI operand is unbound");
-  if (select_phase) {
+  if (select_phase && !(ws->options & KVIP_OPTION_SCORES_READY)) {
     rc = s.liVariant ? launch_li_score_simt(li, stream) : launch_li_score(li, stream);
     if (rc) return rc;
   }
@@ -187,7 +188,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
     ft.source_bytes = ctx->source_bytes; ft.batch = s.batch; ft.resident = s.resident; ft.outputStride = s.outputStride;
     ft.tokenBytes = s.tokenBytes;
     KVIP_REQUIRE(ft.source_base && ft.pool, "forward: the KV pools are unbound");
-    if ((rc = launch_fetch(ft, stream))) return rc;
+    if ((rc = ws->staging ? launch_fetch_staged(ft, *ws, stream) : launch_fetch(ft, stream))) return rc;
     if (s.gatherRows && ws->gather_out) {
       KvipGatherArgs ga{};
       ga.pool = ft.pool; ga.slots = rs.locations; ga.row_owners = rs.row_owners; ga.out = ptr<uint8_t>(ws->gather_out);

@@ -24,6 +24,9 @@ class HostDecodeLoop:
     def __init__(self, torch, forward, inputs, outputs, *, host_query, host_weights, host_scale, host_positions,
                  host_outputs, capture=True):
         device = outputs.device
+        if getattr(forward, "prefetch", None) is not None:
+            # select() would leave the prefetch stream unjoined at the end of its graph
+            raise ValueError("HostDecodeLoop captures select() and commit() separately: use a forward without prefetch windows")
         for name, tensor in (("host_query", host_query), ("host_weights", host_weights),
                              ("host_positions", host_positions), ("host_outputs", host_outputs)):
             if tensor.device.type != "cpu" or not tensor.is_pinned():

@@ -178,8 +178,8 @@ class CudaBinding:
         self.device = arguments[0].device
         if self.device.type != "cuda" or any(x.device != self.device or not x.is_contiguous() for x in arguments):
             raise ValueError("LIFetch requires 14 contiguous input buffers on the same CUDA device")
-        if prefetch_limit:
-            raise ValueError("Speculative prefetch windows are not part of this build: prefetch_limit must be 0")
+        if not 0 <= prefetch_limit <= 512:
+            raise ValueError("prefetch_limit: at most 512 speculative rows per request and round")
         query, keys, weights = arguments[0], arguments[1], arguments[2]
         queries = queries or query.shape[0] // batch
         heads = query.numel() // (batch * queries * 128)
@@ -195,7 +195,7 @@ class CudaBinding:
             keyRows=keys.numel() // 128, gatherRows=int(gather_output is not None), liVariant=li_variant)
         self.shape = self.runtime_shape
         self.shape_pointer = ctypes.byref(self.runtime_shape)
-        self.prefetch_limit = 0
+        self.prefetch_limit = prefetch_limit
         self.final_workers = 4
         self.queries, self.batch = queries, batch
         for name, (shape, dtype_name) in rotation_spec(batch, history, resident, queries).items():
@@ -238,6 +238,7 @@ class CudaBinding:
             self.source = source
         else:
             raise ValueError("LIFetch needs a host KV pool (lease) or a device-visible source tensor")
+        self.source_base, self.source_bytes = source_base, source_bytes
         context = _lib.Context(
             locations=self.locations.data_ptr(), lru_slots=self.lru_slots.data_ptr(),
             reserved_hot=self.reserved_hot.data_ptr(), changes=self.changes.data_ptr(),
@@ -327,7 +328,8 @@ class LIFetch:
     two halves of `__call__()` for callers that overlap host copies with the step: `select()` reads the query
     inputs and writes no output row, `commit()` reads no query input."""
 
-    def __init__(self, rotating, update, *, q_workers=2, lru=None):
+    def __init__(self, rotating, update, *, q_workers=2, lru=None, prefetch_limit=None, prefetch_windows=3, prefetch_ctas=0,
+                 prefetch_last_window=False):
         if rotating.device != update.device:
             raise ValueError("Fetch and Index update must use the same device")
         if update.bindings.numel() != 28:
@@ -390,6 +392,17 @@ class LIFetch:
         if torch.cuda.is_available():
             rotating.bindings = rotating.bindings.pin_memory()
         self.set_options()
+        # speculative prefetch windows: `prefetch_limit` rows per request and round (0 = off, at most 512)
+        self.prefetch = None
+        if prefetch_limit is None:
+            prefetch_limit = rotating.prefetch_limit
+        if prefetch_limit:
+            from .prefetch import PrefetchWindows
+            self.prefetch = PrefetchWindows(self, limit=prefetch_limit, window_limit=min(480, prefetch_limit),
+                                            cold_windows=prefetch_windows, li_ctas=prefetch_ctas,
+                                            last_window=prefetch_last_window)
+            self.prefetch_limit = prefetch_limit
+            self.set_options()
 
     def _enqueue(self, phase):
         lease = self.rotating.lease
@@ -401,7 +414,7 @@ class LIFetch:
         self._options_word[0] = self._options
         if result:
             raise RuntimeError(f"streaming LIFetch launch failed: {result} ({_lib.last_error(self.rotating.library)})")
-        if self.lru is not None and phase != _lib.OPTION_SELECT_ONLY:
+        if self.lru is not None and not phase & _lib.OPTION_SELECT_ONLY:
             # fork: LRU feedback beside fetch + gather; join before the caller's next work on this stream
             self._side.wait_event(self._slots_ready)
             with self.torch.cuda.stream(self._side):
@@ -410,14 +423,28 @@ class LIFetch:
             stream.wait_event(self._lru_done)
 
     def __call__(self):
-        self._enqueue(0)
+        if self.prefetch is None:
+            self._enqueue(0)
+        else:
+            self.select()
+            self.commit()
 
     def select(self):
-        """First half: LI score -> TopK -> resolver. Reads the query inputs; writes no output row."""
-        self._enqueue(_lib.OPTION_SELECT_ONLY)
+        """First half: LI score -> TopK -> resolver. Reads the query inputs; writes no output row. With
+        prefetch windows the score pass is issued window by window here, and rows of likely misses are staged
+        on a second stream meanwhile."""
+        if self.prefetch is None:
+            self._enqueue(_lib.OPTION_SELECT_ONLY)
+            return
+        lease = self.rotating.lease
+        main = lease.check_stream() if lease is not None else self.torch.cuda.current_stream(self.rotating.device)
+        self.prefetch.enqueue(main)
+        self._enqueue(_lib.OPTION_SELECT_ONLY | _lib.OPTION_SCORES_READY)
 
     def commit(self):
         """Second half: output rows -> Index exchange -> fetch (-> gather) and the LRU feedback."""
+        if self.prefetch is not None:   # the fetch reads the staging area: join the second stream
+            self.torch.cuda.current_stream(self.rotating.device).wait_event(self.prefetch.staged)
         self._enqueue(_lib.OPTION_COMMIT_ONLY)
 
     def set_options(self, *, diagnostics=False, deferred_fetch=False):

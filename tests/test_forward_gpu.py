@@ -430,3 +430,89 @@ def test_sparse_attention_over_slot_output_equals_attention_over_logical_tokens(
                 assert torch.allclose(actual, expected, atol=0.006, rtol=0.025)
                 assert torch.equal(actual, expected)
     assert fetched[0] > 0 and fetched[1] > 0 and fetched[2] < fetched[0]   # misses, misses, mostly hits
+
+
+def test_prefetch_windows_change_only_where_missing_rows_come_from(device):
+    """Speculative prefetch windows (reference: op_kernel/prefetch.h:577-821; predicate indexer_score.h:976-1017):
+    the score pass runs window by window, rows of cold positions that beat the resident threshold are staged
+    meanwhile, and the final fetch takes listed rows from the staging area. Scores, outputs, Index rows, pool
+    bytes and LRU order must equal those of the plain forward bit for bit; thresholds and candidate lists must
+    equal the oracle's cold predicate; the rows served from the staging area are exactly the final descriptors
+    whose source is listed."""
+    config = dict(batch=3, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=656, seed=51, host_pool=False, fill_payload=True)
+    plain = DecodePipeline(device, **config)
+    spec = DecodePipeline(device, prefetch_limit=512, prefetch_last_window=True, **config)   # every cold window staged
+    prefetch = spec.forward.prefetch
+    assert prefetch.first == [0, 4096, 5504, 6912, 8192]
+    lengths = spec.workspace.key_lengths.cpu().numpy()
+    total_hits = total_listed = 0
+    for step in range(4):
+        for p in (plain, spec):
+            p.new_queries(500 + step)
+        addresses_before = spec.storage.addresses.cpu().numpy().copy()
+        plain.step()
+        spec.step()
+        torch.cuda.synchronize()
+        assert int(spec.forward.li_status.item()) == 0 and int(spec.update.status.abs().sum()) == 0
+        assert torch.equal(spec.workspace.scores, plain.workspace.scores)
+        assert torch.equal(spec.workspace.topk, plain.workspace.topk)
+        assert torch.equal(spec.update.outputs, plain.update.outputs)
+        assert torch.equal(spec.gather_out, plain.gather_out)
+        assert torch.equal(spec.pool_hbm, plain.pool_hbm)
+        assert torch.equal(spec.storage.logical_ids, plain.storage.logical_ids)
+        assert torch.equal(spec.storage.keys, plain.storage.keys)
+        assert torch.equal(spec.lru.order, plain.lru.order)
+        scores = spec.workspace.scores.cpu().numpy()
+        ends = spec.workspace.inputs.query_ends.cpu().numpy().reshape(spec.batch, -1)[:, :2]
+        _, thresholds, bitmap, _ = oracle.cold_predicate(scores, lengths, ends, 4096)
+        assert np.array_equal(prefetch.thresholds.cpu().numpy().view(np.uint32), thresholds)
+        staged_rows = prefetch.staged_rows.cpu().numpy()
+        staged_sources = prefetch.staged_sources.cpu().numpy()
+        hits = prefetch.staged_hits.cpu().numpy()
+        counts = spec.rotating.query_counts.cpu().numpy()[:, 4]
+        descriptors = spec.rotating.fallback_addresses.cpu().numpy()
+        for b in range(spec.batch):
+            owner = spec.row_owner_list[b]
+            marked = np.bitwise_or.reduce(bitmap[2 * b: 2 * b + 2], axis=0)
+            positions = 4096 + np.flatnonzero(np.unpackbits(marked.view(np.uint8), bitorder="little"))
+            expected = set(addresses_before[owner, positions].tolist())
+            listed = staged_sources[b, :staged_rows[b]].tolist()
+            assert len(set(listed)) == len(listed) and set(listed) <= expected
+            if len(expected) <= 480:
+                assert set(listed) == expected
+            else:
+                assert len(listed) >= 480
+            wanted = descriptors[b, :counts[b]].tolist()
+            assert hits[b] == sum(1 for source in wanted if source in set(listed))
+            total_hits += int(hits[b])
+            total_listed += len(listed)
+    assert total_listed > 0 and total_hits > 0
+
+
+def test_prefetch_windows_replay_from_a_graph(device):
+    """The windowed score launches, the second stream's work and both joins are captured in one CUDA graph; its
+    replays equal the eager steps of a plain pipeline."""
+    config = dict(batch=2, queries=1, heads=64, history=8192, resident=4096, len_lo=7000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=61, host_pool=False, fill_payload=True)
+    plain = DecodePipeline(device, **config)
+    spec = DecodePipeline(device, prefetch_limit=256, prefetch_windows=2, **config)
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        plain.step()
+        spec.step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            spec.step()
+        for step in range(3):
+            for p in (plain, spec):
+                p.new_queries(700 + step)
+            plain.step()
+            graph.replay()
+            stream.synchronize()
+            assert torch.equal(spec.update.outputs, plain.update.outputs)
+            assert torch.equal(spec.pool_hbm, plain.pool_hbm)
+            assert torch.equal(spec.gather_out, plain.gather_out)
+            assert torch.equal(spec.lru.order, plain.lru.order)
+    assert int(spec.forward.prefetch.staged_rows.sum()) > 0
