@@ -737,6 +737,70 @@ def run_lidu(args):
     }), flush=True)
 
 
+def run_miss_prefetch(args):
+    """`--workload miss_path_prefetch`: the drifting-query miss path (AR(1) queries, rho = 0.95; 128k context,
+    25 % resident pool, misses from the pinned host pool, one new Index row per token) with and without
+    speculative prefetch windows, the forward replayed from a CUDA graph. Not a headline line: it reports what the
+    windows cost (extra score launches) and what they move off the post-score fetch."""
+    import torch
+
+    from kvip_b200.synthetic import DecodePipeline
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    stream = torch.cuda.Stream(device)
+    lib = _load_counter()
+    batch = args.batch or 32
+    cfg = dict(batch=batch, queries=1, heads=64, history=131072, resident=32768, len_lo=131072, len_hi=131072,
+               key_dtype="fp8", weight_dtype="bf16", token_bytes=1152)
+    variants = [("plain", {}), ("plain", {})] + [
+        (f"windows{w}_limit{n}", dict(prefetch_limit=n, prefetch_windows=w)) for n in (512, 128) for w in (2, 3)]
+    steps, warm, results = max(args.steps, 8), max(args.warmup, 4), []
+    launches_before = lib.kvip_b200_launch_count()
+    for name, extra in variants:   # the first plain run also warms the host pool mapping and is dropped below
+        with torch.cuda.stream(stream):
+            p = DecodePipeline(device, seed=0, gather=True, host_pool=True, **cfg, **extra)
+            p.make_query_bank(steps + warm, correlation=0.95)
+            for i in range(warm):
+                p.load_queries(i)
+                p.step(ingest=True)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                p.forward()
+            counts = torch.zeros((3, steps), dtype=torch.int64, device=device)
+
+            def drifting():
+                for i in range(steps):
+                    p.load_queries(warm + i)
+                    p.ingest_new_tokens()
+                    graph.replay()
+                    counts[0, i] = p.rotating.query_counts[:, 4].sum()
+                    if p.forward.prefetch is not None:
+                        counts[1, i] = p.forward.prefetch.staged_rows.sum()
+                        counts[2, i] = p.forward.prefetch.staged_hits.sum()
+
+            stream.synchronize()
+            seconds = time_region(torch, stream, drifting, 1)
+            p.load_queries(0)
+            for _ in range(3):
+                graph.replay()
+            steady = time_region(torch, stream, graph.replay, 10) / 10
+            misses, listed, served = (counts.float().mean(dim=1)).tolist()
+            results.append({"variant": name, "ms_per_step": seconds / steps * 1e3, "misses_per_step": misses,
+                            "rows_staged_per_step": listed, "misses_served_from_staging": served,
+                            "steady_no_miss_ms": steady * 1e3,
+                            "status": int(p.update.status.max().item()) | int(p.forward.li_status.item())})
+            p.close()
+            del p, graph
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "miss-path step time with and without prefetch windows", "unit": "ms", "n_gpus": 1,
+                      "higher_is_better": False, "data": "synthetic", "dtype": "fp8_e4m3 x fp8_e4m3 -> f32",
+                      "config": {"workload": "miss_path_prefetch", **{k: cfg[k] for k in ("batch", "history", "resident", "token_bytes")},
+                                 "query_drift": "AR(1), rho = 0.95", "cuda_graph": True, "steps": steps},
+                      "results": results[1:], "gpu_launches": lib.kvip_b200_launch_count() - launches_before}), flush=True)
+
+
 def _load_counter():
     from kvip_b200 import _lib
     return _lib.load_library()
@@ -748,7 +812,7 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu"], default="decode_128k_b64")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch"], default="decode_128k_b64")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")
     parser.add_argument("--device-source", action="store_true", help="serve misses from HBM instead of the host pool")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -767,6 +831,8 @@ def main():
         run_seqshard(args)
     elif args.workload == "lidu":
         run_lidu(args)
+    elif args.workload == "miss_path_prefetch":
+        run_miss_prefetch(args)
     else:
         run_ours(args)
 
