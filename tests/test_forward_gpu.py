@@ -432,15 +432,17 @@ def test_sparse_attention_over_slot_output_equals_attention_over_logical_tokens(
     assert fetched[0] > 0 and fetched[1] > 0 and fetched[2] < fetched[0]   # misses, misses, mostly hits
 
 
-def test_prefetch_windows_change_only_where_missing_rows_come_from(device):
+@pytest.mark.parametrize("len_lo", [6000, 1500], ids=["long", "some_shorter_than_the_pool"])
+def test_prefetch_windows_change_only_where_missing_rows_come_from(len_lo, device):
     """Speculative prefetch windows (reference: op_kernel/prefetch.h:577-821; predicate indexer_score.h:976-1017):
     the score pass runs window by window, rows of cold positions that beat the resident threshold are staged
     meanwhile, and the final fetch takes listed rows from the staging area. Scores, outputs, Index rows, pool
     bytes and LRU order must equal those of the plain forward bit for bit; thresholds and candidate lists must
     equal the oracle's cold predicate; the rows served from the staging area are exactly the final descriptors
     whose source is listed."""
-    config = dict(batch=3, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
-                  weight_dtype="bf16", token_bytes=656, seed=51, host_pool=False, fill_payload=True)
+    config = dict(batch=5 if len_lo < 4096 else 3, queries=2, heads=64, history=8192, resident=4096, len_lo=len_lo,
+                  len_hi=8192, key_dtype="fp8", weight_dtype="bf16", token_bytes=656, seed=51, host_pool=False,
+                  fill_payload=True)
     plain = DecodePipeline(device, **config)
     spec = DecodePipeline(device, prefetch_limit=512, prefetch_last_window=True, **config)   # every cold window staged
     prefetch = spec.forward.prefetch
