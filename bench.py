@@ -30,6 +30,9 @@ WORKLOADS = {
     # configs[1]: decode LI+TopK, B=64, 2 MTP tokens, ctx U[16k,32k]
     "decode_32k_b64_mtp2": dict(batch=64, queries=2, heads=64, history=32768, resident=8192, len_lo=16384,
                                 len_hi=32768, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+    # one GPU's share of the 8-GPU serving configuration: 256 requests over 8 GPUs, ctx U[64k,128k], 50 % pool
+    "decode_64k_128k_b32": dict(batch=32, queries=1, heads=64, history=131072, resident=65536, len_lo=65536,
+                                len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
     # small cases for profiler captures and smoke runs
     "decode_16k_b16": dict(batch=16, queries=1, heads=64, history=16384, resident=4096, len_lo=16384, len_hi=16384,
                            key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
