@@ -40,7 +40,7 @@ class PrefetchWindows:
         while first[-1] < history:
             first.append(min(history, first[-1] + per))
         self.first, self.windows = first, len(first) - 1
-        self.forward, self.torch, self.library = forward, torch, rotating.library
+        self.torch, self.library = torch, rotating.library   # no reference back to `forward`: it owns this object
         self.limit, self.window_limit = limit, window_limit
         # rows listed after the last window cannot be copied behind the score pass any more: by default they are
         # left to the final fetch, which reads exactly the missing ones
