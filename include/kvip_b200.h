@@ -33,12 +33,20 @@ extern "C" {
 #define KVIP_BLOCK_TOKENS 128u       /* paged Index cache block */
 #define KVIP_INDEX_WIDTH 128u        /* d_I */
 #define KVIP_TOPK_SPLIT_WORDS 20544u /* u32 words of TopK scratch per score row for the multi-CTA path */
-/* bits of KvipWorkspace.options (bits 0-15: prefetch limit, 16-23: resolver workers) */
-#define KVIP_OPTION_DIAGNOSTICS 0x80000000u
+/* Bits of KvipWorkspace.options. Bits 0-15: prefetch limit, 16-18: fetch workers per query, both as the
+ * reference packs them (python/kvip/operators/lifetch/streaming.py:133-146). The reference's own flag bits keep
+ * their positions: diagnostics and deferred fetch mean what they mean there; parallel finalize (0x10000000),
+ * prepare metadata (0x08000000) and UBmem overlap (0x04000000) choose between schedules of the Ascend pipeline
+ * that give the same results, so they are accepted and have no effect here; the legacy scratch layout
+ * (0x20000000) cannot be honoured and is rejected with KVIP_BAD_ARGUMENT. The bits this build adds sit where
+ * the reference has none. */
+#define KVIP_OPTION_DIAGNOSTICS 0x80000000u    /* device timestamps of every stage into KvipWorkspace.times */
 #define KVIP_OPTION_DEFERRED_FETCH 0x40000000u /* descriptors only: no fetch, no gather */
-#define KVIP_OPTION_SELECT_ONLY 0x20000000u    /* LI score -> TopK -> resolver, then return */
-#define KVIP_OPTION_SCORES_READY 0x08000000u   /* the score rows were written by earlier launches: the select phase starts at TopK */
-#define KVIP_OPTION_COMMIT_ONLY 0x10000000u    /* the rest of a SELECT_ONLY call: outputs -> exchange -> fetch (-> gather) */
+#define KVIP_OPTION_LEGACY_LAYOUT 0x20000000u  /* reference only: rejected */
+#define KVIP_OPTION_SCHEDULING_HINTS 0x1c000000u /* reference only: accepted, no effect */
+#define KVIP_OPTION_SELECT_ONLY 0x02000000u    /* LI score -> TopK -> resolver, then return */
+#define KVIP_OPTION_COMMIT_ONLY 0x01000000u    /* the rest of a SELECT_ONLY call: outputs -> exchange -> fetch (-> gather) */
+#define KVIP_OPTION_SCORES_READY 0x00800000u   /* the score rows were written by earlier launches: the select phase starts at TopK */
 #define KVIP_BAD_ARGUMENT 100000u
 #define KVIP_CUDA_ERROR_BASE 200000u
 
@@ -48,10 +56,16 @@ extern "C" {
 #define KVIP_ERR_HASH 8u             /* hash probe overflow, also the wait-limit code (streaming.cpp:191) */
 #define KVIP_ERR_EXCHANGE 16u        /* Index exchange plan invalid (shadow_exchange_parallel.h:40) */
 #define KVIP_ERR_PIPELINE 32u        /* a bounded mbarrier wait inside the LI kernel gave up */
+#define KVIP_ERR_SOURCE 64u          /* a missing row's source address lies outside the host pool (streaming.cpp:399-400) */
 
 enum { KVIP_KEY_FP8_E4M3 = 0, KVIP_KEY_BF16 = 1 };
 enum { KVIP_WEIGHT_BF16 = 0, KVIP_WEIGHT_FP32 = 1 };
 enum { KVIP_SCORE_FP32 = 0, KVIP_SCORE_BF16_AWAY = 1 };
+/* The weighted sum over index heads: on the CUDA cores in fp32 (the reference's arithmetic,
+ * indexer_score.h:59-140), or on the tensor core as a second, small MMA over bf16-rounded operands (wide query
+ * tiles only; fp32 score mode only). AUTO picks the tensor core when a key page meets 128 or more
+ * (query, head) columns, where the register reduction and not HBM sets the pace. */
+enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_REGISTERS = 1, KVIP_HEAD_SUM_TENSOR = 2 };
 
 /* Geometry bound before graph capture. Same size (80 bytes, 20 x u32) and the same
  * leading fields as rotating::RuntimeShape (include/runtime_shape.h:5-27); the fields
@@ -75,7 +89,7 @@ typedef struct KvipRuntimeShape {
   uint32_t keyRows;        /* rows of the paged key tensor = owners * history */
   uint32_t gatherRows;     /* 1 = also write the dense [T,2048,tokenBytes] gather */
   uint32_t liVariant;      /* 0 = tcgen05 kernel, 1 = CUDA-core cross-check kernel */
-  uint32_t reserved0;
+  uint32_t headSum;        /* KVIP_HEAD_SUM_* for the tcgen05 kernel */
   uint32_t reserved1;
 } KvipRuntimeShape;
 
@@ -100,8 +114,11 @@ typedef struct KvipLiArgs {
   uint32_t scoreMode, ctas;
   uint32_t stages;            /* key pages in flight per CTA; 0 = as many as shared memory holds */
   uint32_t withhold_tile;     /* test hook for the bounded waits: when n > 0, CTA 0 never loads its n-th key page,
-                                 so the wait for that page runs out (about a second) and the kernel returns with
+                                 so the wait for that page runs out and the kernel returns with
                                  KVIP_ERR_PIPELINE in *status; 0 in production */
+  uint32_t wait_kilocycles;   /* limit of every barrier wait inside the kernel, in units of 1024 SM clock cycles;
+                                 0 = the default of about one second */
+  uint32_t head_sum;          /* KVIP_HEAD_SUM_*: where the weighted sum over heads is computed */
 } KvipLiArgs;
 uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
 /* CUDA-core restatement of the same formula with the oracle's accumulation order;
@@ -196,7 +213,26 @@ uint32_t kvip_b200_cold_predicate(const KvipColdArgs* args, void* stream);
 /* ---- stage 3: classification + resolver + service outputs + fetch descriptors ---
  * Replaces ClassifyTopkHalf / StagedInitializeReady / StagedQuery / PackStagedUrmaQuery /
  * PublishQueryOutputs (op_kernel/staged_topk_classify.h:9-46,
- * resolver_staged_dma2.h:83-237, staged_urma_pack.h:6-71, streaming.cpp:66-90). */
+ * resolver_staged_dma2.h:83-237, staged_urma_pack.h:6-71, streaming.cpp:66-90).
+ *
+ * ABC tail (common/lifetch/cache_metadata.h:22-26, 100-105; prefetch.h:26-44): with tail_bounds bound, the
+ * positions [begin, end) of a request are tokens written since the last commit to the host pool. Their KV rows
+ * live in a ring of outputStride - resident dedicated slots behind the hot slots. Such a position is never a hot
+ * hit by position, never a miss and never a victim: while begin <= p < begin + ring size its location is
+ * resident + p % ring size (the reference stores the code resident + 8192 + p % ring in its mapping and resolves
+ * it to the same slot); a tail position beyond the ring is resolved like any cold position.
+ *
+ * Final posts (common/lifetch/final_post.h:2-12; include/context.h:9-14): one 128-byte record per (request, query)
+ * = 32 x u32 {count, pending, error, deferred, descriptor, nonconflicting, head lo, head hi, 0...}: count = new
+ * slots of the query, descriptor = index of its first descriptor in fetch_sources / fetch_destinations
+ * (request * 8192 + descriptors of the earlier queries; the reference gives every query a fixed 2048-entry
+ * region instead), nonconflicting = count (no prefetch ever writes a victim slot in this build, so every
+ * descriptor is safe to fetch at once), error = the request's status word, pending = deferred = head = 0. */
+typedef struct KvipFinalPost {
+  uint32_t count, pending, error, deferred, descriptor, nonconflicting;
+  uint32_t head_lo, head_hi;
+  uint32_t reserved[24];
+} KvipFinalPost;
 typedef struct KvipResolveArgs {
   const int32_t* topk;          /* [batch, queries, 2048] selected physical positions */
   const int32_t* row_owners;    /* [batch] or NULL (owner = row) */
@@ -222,7 +258,11 @@ typedef struct KvipResolveArgs {
   const int32_t* query_ends;    /* [batch*queries]; rows with 0 publish -1 when no routing is bound */
   int32_t* row_status;          /* [batch, 32] */
   uint32_t batch, queries, history, resident;
-  uint32_t address_stride, outputStride, reserved0, reserved1;
+  uint32_t address_stride, outputStride;
+  uint32_t tokenBytes;          /* bytes per KV row: with source_bytes, the range check of the source addresses */
+  uint32_t reserved1;
+  uint64_t source_bytes;        /* size of the miss source; 0 = addresses are not checked here */
+  KvipFinalPost* final_posts;   /* [batch, 4] out, or NULL */
 } KvipResolveArgs;
 uint32_t kvip_b200_resolve(const KvipResolveArgs* args, void* stream);
 
@@ -244,6 +284,9 @@ typedef struct KvipFetchArgs {
   int32_t* hot_valid;              /* [owners, resident] */
   uint64_t source_bytes;           /* size of the source window, for the bounds check */
   uint32_t batch, resident, outputStride, tokenBytes;
+  int32_t* status;                 /* [batch] Index-update status or NULL: a descriptor that fails the range check
+                                      ORs 4 into its request's word (index_cache_update.h:6-20) and the destination
+                                      slot loses residency, so the next step cannot read a stale row as a hit */
 } KvipFetchArgs;
 uint32_t kvip_b200_fetch(const KvipFetchArgs* args, void* stream);
 
@@ -298,6 +341,29 @@ typedef struct KvipIngestArgs {
   uint32_t batch, queries, history, source_is_bf16;
 } KvipIngestArgs;
 uint32_t kvip_b200_ingest(const KvipIngestArgs* args, void* stream);
+
+/* Prefill-side import of Index rows: one launch for every request of a forward batch
+ * (VllmIndexCacheStorage.ingest_prefill, python/kvip/adapters/vllm/index_import.py:17-36, does it with
+ * index_select / index_copy_ calls per request). A span of kind 0 restores a request's cached history: Index
+ * position p in [first, first + tokens) of `owner` takes cache row block_table[row, p / block] * block + p % block.
+ * A span of kind 1 writes the tokens of this forward: batch token t in [first, first + tokens) goes to Index
+ * position positions[t] of `owner` from cache row slot_mapping[t]. Rows whose source or target is out of range
+ * are skipped and counted in *errors. */
+typedef struct KvipIngestSpanArgs {
+  const uint8_t* source_keys;    /* [source_rows, 128] FP8 rows of the model's paged cache */
+  const float* source_scales;    /* [source_rows] */
+  const int32_t* block_table;    /* [table_rows, table_stride] */
+  const int64_t* slot_mapping;   /* [batch_tokens] */
+  const int64_t* positions;      /* [batch_tokens] */
+  const int32_t* spans;          /* [count, 8]: owner, table row, kind, first, tokens, 0, 0, 0 */
+  uint8_t* keys;                 /* [owners, history, 128] */
+  float* scales;                 /* [owners, history] */
+  int32_t* errors;               /* [1] in/out or NULL */
+  uint64_t source_rows;
+  uint32_t count, max_tokens, owners, history;
+  uint32_t block, table_rows, table_stride, batch_tokens;
+} KvipIngestSpanArgs;
+uint32_t kvip_b200_ingest_spans(const KvipIngestSpanArgs* args, void* stream);
 
 /* ---- SlotLRU commit on the device -------------------------------------------------
  * Same list semantics as _commit_lru_rows / _write_oldest_victims
@@ -452,11 +518,13 @@ typedef struct KvipContext {          /* reference: rotating::Context, include/c
   uint64_t token_addresses, address_stride, output_stride, tail_bounds, row_status;
   uint64_t query_counts, pool, source_base, source_bytes;
   KvipRuntimeShape shape;
+  uint64_t final_posts;          /* KvipFinalPost [batch, 4] or 0 */
 } KvipContext;
 
 typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_types.h:17-22 */
   uint64_t context, keys, scales, addresses, logical_ids, hot_valid;
-  uint64_t flags, events_src, events_dst, worker_status, times;
+  uint64_t flags, events_src, events_dst, worker_status;
+  uint64_t times;               /* int64 [KVIP_TIME_STAMPS] or 0; written only with KVIP_OPTION_DIAGNOSTICS */
   uint32_t history, resident, options, max_events;      /* options word at byte 96 */
   uint64_t query_bitmaps, query_errors, update_bindings;
   uint64_t dense_shadow, packed_fetch;
@@ -475,6 +543,13 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,
                                         void* stream, const KvipRuntimeShape* shape,
                                         uint32_t workers);
+/* Device timestamps of the fused forward (reference: the `times` buffer of streaming.cpp:107-108, 390-465, whose
+ * per-core layout is specific to the Ascend pipeline). With KVIP_OPTION_DIAGNOSTICS the call enqueues a
+ * one-thread kernel between its stages that stores the GPU's nanosecond timer: times[i] is the moment stage i
+ * could start, times[i + 1] the moment it had finished, for the stages in the order below; a stage the call
+ * skips repeats the previous stamp. The stamps cost a launch each: a profiling mode, off by default. */
+enum { KVIP_TIME_START = 0, KVIP_TIME_LI, KVIP_TIME_TOPK, KVIP_TIME_RESOLVE, KVIP_TIME_OUTPUTS, KVIP_TIME_EXCHANGE,
+       KVIP_TIME_FETCH, KVIP_TIME_GATHER, KVIP_TIME_STAMPS };
 uint32_t kvip_prepare_shape(KvipRuntimeShape* shape);    /* include/api.h:9 */
 
 /* ---- host-DDR KV pool ---------------------------------------------------------------

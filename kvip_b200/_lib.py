@@ -11,12 +11,17 @@ u32, i32, u64, i64, vp, f32 = (ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64,
 
 TOPK, SLOTS, LRU_SLOTS, CHANGE_CAPACITY, BLOCK_TOKENS, MAX_QUERIES = 2048, 8192, 2048, 10240, 128, 4
 OPTION_DIAGNOSTICS, OPTION_DEFERRED_FETCH = 0x80000000, 0x40000000
-OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY, OPTION_SCORES_READY = 0x20000000, 0x10000000, 0x08000000
+OPTION_LEGACY_LAYOUT, OPTION_SCHEDULING_HINTS = 0x20000000, 0x1C000000
+OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY, OPTION_SCORES_READY = 0x02000000, 0x01000000, 0x00800000
 TOPK_SPLIT_WORDS = 20544
+ERR_TOKEN_RANGE, ERR_NO_SLOT, ERR_HASH, ERR_EXCHANGE, ERR_PIPELINE, ERR_SOURCE = 1, 4, 8, 16, 32, 64
+# boundaries of KvipWorkspace.times (KVIP_TIME_*)
+TIME_STAGES = ("li_score", "topk", "resolve", "outputs", "exchange", "fetch", "gather")
 BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
 WEIGHT_BF16, WEIGHT_FP32 = 0, 1
 SCORE_FP32, SCORE_BF16_AWAY = 0, 1
+HEAD_SUM_AUTO, HEAD_SUM_REGISTERS, HEAD_SUM_TENSOR = 0, 1, 2
 
 
 def _struct(name, pointer_fields, scalar_fields):
@@ -30,7 +35,7 @@ class RuntimeShape(ctypes.Structure):
     _fields_ = [(name, u32) for name in (
         "batch", "history", "resident", "indexHeads", "smCount", "queries", "keyDtype", "weightDtype",
         "scoreMode", "pagesPerRequest", "finalWorkers", "scoreStride", "outputStride", "owners",
-        "tokenBytes", "keyRows", "gatherRows", "liVariant", "reserved0", "reserved1")]
+        "tokenBytes", "keyRows", "gatherRows", "liVariant", "headSum", "reserved1")]
 
     @classmethod
     def prepare(cls, library, **fields):
@@ -44,7 +49,7 @@ LiArgs = _struct("LiArgs", (
     "query", "keys", "weights", "query_scale", "key_scale", "key_lengths", "query_ends", "block_table",
     "scores", "status"), [(n, u32) for n in (
         "batch", "queries", "heads", "pagesPerRequest", "keyRows", "scoreStride", "keyDtype", "weightDtype",
-        "scoreMode", "ctas", "stages", "withhold_tile")])
+        "scoreMode", "ctas", "stages", "withhold_tile", "wait_kilocycles", "head_sum")])
 
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])
@@ -64,11 +69,13 @@ ResolveArgs = _struct("ResolveArgs", (
     "locations", "changes", "change_slots", "change_count", "events_src", "events_dst", "query_counts",
     "fetch_sources", "fetch_destinations", "logical_output", "slot_output", "unpack_indices", "output_valid",
     "query_ends", "row_status"), [(n, u32) for n in (
-        "batch", "queries", "history", "resident", "address_stride", "outputStride", "reserved0", "reserved1")])
+        "batch", "queries", "history", "resident", "address_stride", "outputStride", "tokenBytes", "reserved1")] + [
+            ("source_bytes", u64), ("final_posts", vp)])
 
 FetchArgs = _struct("FetchArgs", (
     "source_base", "fetch_sources", "fetch_destinations", "query_counts", "row_owners", "row_status", "pool",
-    "hot_valid"), [("source_bytes", u64)] + [(n, u32) for n in ("batch", "resident", "outputStride", "tokenBytes")])
+    "hot_valid"), [("source_bytes", u64)] + [(n, u32) for n in ("batch", "resident", "outputStride", "tokenBytes")] + [
+        ("status", vp)])
 
 GatherArgs = _struct("GatherArgs", ("pool", "slots", "row_owners", "out"),
                      [(n, u32) for n in ("rows", "queries", "outputStride", "tokenBytes")])
@@ -81,6 +88,11 @@ ExchangeArgs = _struct("ExchangeArgs", (
 IngestArgs = _struct("IngestArgs", (
     "source_keys", "source_scales", "slot_mapping", "gather_indices", "query_ends", "row_owners", "keys", "scales"),
     [(n, u32) for n in ("batch", "queries", "history", "source_is_bf16")])
+
+IngestSpanArgs = _struct("IngestSpanArgs", (
+    "source_keys", "source_scales", "block_table", "slot_mapping", "positions", "spans", "keys", "scales", "errors"),
+    [("source_rows", u64)] + [(n, u32) for n in ("count", "max_tokens", "owners", "history", "block", "table_rows",
+                                                  "table_stride", "batch_tokens")])
 
 LruArgs = _struct("LruArgs", ("order", "slots", "bitmap", "unique", "reserved_hot", "touched", "active"),
                   [(n, u32) for n in ("rows", "capacity", "words", "touched_stride", "resident", "reserved0",
@@ -123,7 +135,7 @@ class Context(ctypes.Structure):
         "locations", "lru_slots", "reserved_hot", "changes", "change_slots", "change_count", "query_ends",
         "fetch_sources", "fetch_destinations", "hot_valid", "row_owners", "token_addresses", "address_stride",
         "output_stride", "tail_bounds", "row_status", "query_counts", "pool", "source_base", "source_bytes")] + [
-            ("shape", RuntimeShape)]
+            ("shape", RuntimeShape), ("final_posts", u64)]
 
 
 class Workspace(ctypes.Structure):
@@ -144,6 +156,7 @@ _STAGES = {
     "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs,
     "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
+    "kvip_b200_ingest_spans": IngestSpanArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs, "kvip_b200_publish_pages": PagesArgs,
     "kvip_b200_window_bounds": WindowArgs, "kvip_b200_resident_threshold": ThresholdArgs,
     "kvip_b200_speculate_window": SpeculateArgs,

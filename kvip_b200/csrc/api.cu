@@ -35,6 +35,48 @@ uint32_t check_launch(const char* what) {
   return KVIP_CUDA_ERROR_BASE + static_cast<uint32_t>(e);
 }
 
+namespace {
+constexpr int kMaxDevices = 64;
+struct DeviceRecord {
+  std::atomic<uint32_t> configured{0};   // bit per KernelSlot
+  std::atomic<uint32_t> sm_count{0};
+};
+DeviceRecord g_devices[kMaxDevices];
+
+DeviceRecord* current_device_record() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  return &g_devices[device];
+}
+}  // namespace
+
+uint32_t raise_dynamic_smem(KernelSlot slot, const void* kernel, int bytes, const char* what) {
+  DeviceRecord* record = current_device_record();
+  const uint32_t bit = 1u << slot;
+  if (record && (record->configured.load(std::memory_order_acquire) & bit)) return 0;
+  // setting the attribute twice is harmless, so two threads racing here need no lock
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    return check_launch(what);
+  if (record) record->configured.fetch_or(bit, std::memory_order_release);
+  return 0;
+}
+
+uint32_t device_sm_count() {
+  DeviceRecord* record = current_device_record();
+  if (record) {
+    const uint32_t known = record->sm_count.load(std::memory_order_relaxed);
+    if (known) return known;
+  }
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return 148u;
+  }
+  if (record) record->sm_count.store(static_cast<uint32_t>(sms), std::memory_order_relaxed);
+  return static_cast<uint32_t>(sms);
+}
+
 template <typename T> T* ptr(uint64_t word) { return reinterpret_cast<T*>(static_cast<uintptr_t>(word)); }
 
 }  // namespace kvip
@@ -86,13 +128,26 @@ extern "C" uint32_t kvip_b200_host_unregister(void* host) {
 
 extern "C" uint32_t kvip_streaming_resolver_cores(void) { return 3; }
 extern "C" uint32_t kvip_streaming_flag_count(void) { return 16; }
-extern "C" uint32_t kvip_b200_abi_version(void) { return 1; }
+// 2: option bits of this build moved off the reference's flag bits; KvipLiArgs, KvipResolveArgs, KvipFetchArgs and
+//    KvipContext grew (wait limit and head-sum mode, source range check and final posts, update status, final posts)
+extern "C" uint32_t kvip_b200_abi_version(void) { return 2; }
 extern "C" uint32_t kvip_b200_context_bytes(void) { return sizeof(KvipContext); }
 extern "C" uint32_t kvip_b200_workspace_bytes(void) { return sizeof(KvipWorkspace); }
 extern "C" uint32_t kvip_b200_launch_count(void) { return kvip::g_launches.load(); }
 extern "C" const char* kvip_b200_last_error(void) { return kvip::g_error; }
 
+namespace kvip {
+namespace {
+__global__ void stage_stamp(int64_t* times, uint32_t index, uint32_t copy_previous) {
+  uint64_t now;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+  times[index] = copy_previous ? times[index - 1u] : static_cast<int64_t>(now);
+}
+}  // namespace
+}  // namespace kvip
+
 static_assert(sizeof(KvipRuntimeShape) == 80, "runtime shape ABI");
+static_assert(sizeof(KvipFinalPost) == 128, "final post ABI (common/lifetch/final_post.h: one cache line)");
 static_assert(sizeof(KvipWorkspace) == 256, "workspace ABI");
 static_assert(offsetof(KvipWorkspace, options) == 96, "options word lives at byte 96");
 
@@ -114,9 +169,22 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const KvipRuntimeShape& s = *shape;
   uint32_t rc;
+  KVIP_REQUIRE(!(ws->options & KVIP_OPTION_LEGACY_LAYOUT),
+               "forward: the reference's legacy scratch layout (option bit 0x20000000) does not exist in this build");
+  // KVIP_OPTION_SCHEDULING_HINTS (parallel finalize, prepare metadata, UBmem overlap) pick between schedules of
+  // the reference's pipeline that give the same results: accepted, nothing to do
   const bool select_phase = !(ws->options & KVIP_OPTION_COMMIT_ONLY);
   const bool commit_phase = !(ws->options & KVIP_OPTION_SELECT_ONLY);
   KVIP_REQUIRE(select_phase || commit_phase, "forward: SELECT_ONLY and COMMIT_ONLY exclude each other");
+  int64_t* times = (ws->options & KVIP_OPTION_DIAGNOSTICS) ? ptr<int64_t>(ws->times) : nullptr;
+  // stamp(i): the stage before boundary i has finished (stream order); skipped = the stage did not run in this call
+  auto stamp = [&](uint32_t index, bool skipped) -> uint32_t {
+    if (!times) return 0;
+    stage_stamp<<<1, 1, 0, stream>>>(times, index, skipped && index ? 1u : 0u);
+    count_launch();
+    return check_launch("stage_stamp");
+  };
+  if (select_phase && (rc = stamp(KVIP_TIME_START, false))) return rc;
 
   KvipLiArgs li{};
   li.query = ptr<const void>(bind[0]); li.keys = ptr<const void>(bind[1]); li.weights = ptr<const void>(bind[2]);
@@ -125,13 +193,15 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   li.block_table = ptr<const int32_t>(bind[7]); li.scores = ptr<float>(bind[12]); li.status = ptr<int32_t>(ws->li_status);
   li.batch = s.batch; li.queries = s.queries; li.heads = s.indexHeads; li.pagesPerRequest = s.pagesPerRequest;
   li.keyRows = s.keyRows; li.scoreStride = s.scoreStride; li.keyDtype = s.keyDtype; li.weightDtype = s.weightDtype;
-  li.scoreMode = s.scoreMode; li.ctas = s.smCount;
+  li.scoreMode = s.scoreMode; li.ctas = s.smCount; li.head_sum = s.headSum;
   KVIP_REQUIRE(li.query && li.keys && li.weights && li.key_lengths && li.query_ends && li.block_table && li.scores && li.status,
                "forward: an LI operand is unbound");
-  if (select_phase && !(ws->options & KVIP_OPTION_SCORES_READY)) {
+  const bool run_li = select_phase && !(ws->options & KVIP_OPTION_SCORES_READY);
+  if (run_li) {
     rc = s.liVariant ? launch_li_score_simt(li, stream) : launch_li_score(li, stream);
     if (rc) return rc;
   }
+  if (select_phase && (rc = stamp(KVIP_TIME_LI, !run_li))) return rc;
 
   KvipTopkArgs tk{};
   tk.scores = li.scores; tk.key_lengths = li.key_lengths; tk.query_ends = li.query_ends;
@@ -141,6 +211,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   tk.rows = s.batch * s.queries; tk.queries = s.queries; tk.scoreStride = s.scoreStride; tk.base_index = 0;
   KVIP_REQUIRE(tk.topk, "forward: the TopK output is unbound");
   if (select_phase && (rc = launch_topk(tk, stream))) return rc;
+  if (select_phase && (rc = stamp(KVIP_TIME_TOPK, false))) return rc;
 
   KvipResolveArgs rs{};
   rs.topk = tk.topk; rs.row_owners = ptr<const int32_t>(ctx->row_owners); rs.hot_valid = ptr<const int32_t>(ctx->hot_valid);
@@ -158,13 +229,19 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   rs.batch = s.batch; rs.queries = s.queries; rs.history = s.history; rs.resident = s.resident;
   rs.address_stride = static_cast<uint32_t>(ctx->address_stride ? ctx->address_stride : static_cast<uint64_t>(upd[7]));
   rs.outputStride = s.outputStride;
+  rs.tokenBytes = s.tokenBytes;
+  rs.source_bytes = (ws->options & KVIP_OPTION_DEFERRED_FETCH) ? 0 : ctx->source_bytes;  // descriptors only: the caller fetches
+  rs.final_posts = ptr<KvipFinalPost>(ctx->final_posts);
   KVIP_REQUIRE(rs.hot_valid && rs.reserved_hot && rs.lru_slots && rs.logical_ids && rs.addresses && rs.locations &&
                    rs.changes && rs.change_slots && rs.change_count && rs.events_src && rs.events_dst && rs.query_counts &&
                    rs.fetch_sources && rs.fetch_destinations && rs.row_status, "forward: a resolver operand is unbound");
-  KVIP_REQUIRE(rs.tail_bounds == nullptr, "forward: ABC tail bounds are not supported by this build");
+  KVIP_REQUIRE(rs.tail_bounds == nullptr || (s.outputStride - s.resident >= 384 && (s.outputStride - s.resident) % 128 == 0),
+               "forward: ABC tail bounds need at least 384 dedicated output slots behind the hot ones, in blocks of 128");
   if (select_phase && (rc = launch_resolve_requests(rs, stream))) return rc;
+  if (select_phase && (rc = stamp(KVIP_TIME_RESOLVE, false))) return rc;
   if (!commit_phase) return 0;
   if ((rc = launch_publish_outputs(rs, stream))) return rc;
+  if ((rc = stamp(KVIP_TIME_OUTPUTS, false))) return rc;
   if (ws->slots_ready_event &&
       cudaEventRecord(reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->slots_ready_event)), stream) != cudaSuccess)
     return check_launch("forward: recording the slots-ready event");
@@ -179,6 +256,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   ex.address_stride = static_cast<uint32_t>(upd[7]); ex.key_row_bytes = s.keyDtype == KVIP_KEY_BF16 ? 256u : 128u;
   KVIP_REQUIRE(ex.keys && ex.scales && ex.addresses && ex.hot_valid && ex.shadow && ex.status, "forward: an update operand is unbound");
   if ((rc = launch_exchange(ex, stream))) return rc;
+  if ((rc = stamp(KVIP_TIME_EXCHANGE, false))) return rc;
 
   if (!(ws->options & KVIP_OPTION_DEFERRED_FETCH)) {  // deferred fetch: descriptors only
     KvipFetchArgs ft{};
@@ -186,15 +264,22 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
     ft.fetch_destinations = rs.fetch_destinations; ft.query_counts = rs.query_counts; ft.row_owners = rs.row_owners;
     ft.row_status = rs.row_status; ft.pool = ptr<uint8_t>(ctx->pool); ft.hot_valid = ex.hot_valid;
     ft.source_bytes = ctx->source_bytes; ft.batch = s.batch; ft.resident = s.resident; ft.outputStride = s.outputStride;
-    ft.tokenBytes = s.tokenBytes;
+    ft.tokenBytes = s.tokenBytes; ft.status = ex.status;
     KVIP_REQUIRE(ft.source_base && ft.pool, "forward: the KV pools are unbound");
     if ((rc = ws->staging ? launch_fetch_staged(ft, *ws, stream) : launch_fetch(ft, stream))) return rc;
+    if ((rc = stamp(KVIP_TIME_FETCH, false))) return rc;
     if (s.gatherRows && ws->gather_out) {
       KvipGatherArgs ga{};
       ga.pool = ft.pool; ga.slots = rs.locations; ga.row_owners = rs.row_owners; ga.out = ptr<uint8_t>(ws->gather_out);
       ga.rows = s.batch * s.queries; ga.queries = s.queries; ga.outputStride = s.outputStride; ga.tokenBytes = s.tokenBytes;
       if ((rc = launch_gather(ga, stream))) return rc;
+      if ((rc = stamp(KVIP_TIME_GATHER, false))) return rc;
+    } else if ((rc = stamp(KVIP_TIME_GATHER, true))) {
+      return rc;
     }
+  } else {
+    if ((rc = stamp(KVIP_TIME_FETCH, true))) return rc;
+    if ((rc = stamp(KVIP_TIME_GATHER, true))) return rc;
   }
   return 0;
 }

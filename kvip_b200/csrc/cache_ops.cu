@@ -40,8 +40,16 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs 
     const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
     const bool ok = source >= 0 && static_cast<uint64_t>(source) + a.tokenBytes <= a.source_bytes &&
                     (source & 15) == 0 && dest >= 0 && slot < a.outputStride;
-    if (!ok) {  // record and skip the access (streaming.cpp:399-400 does the same range check)
-      if (lane == 0) atomicOr(a.row_status + b * 32u + 2, 1);
+    if (!ok) {
+      // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
+      // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
+      // it is revoked, and the request's update status gets the reference's code for a failed publication
+      // (CompleteEarlyUpdate, index_cache_update.h:6-20).
+      if (lane == 0) {
+        atomicOr(a.row_status + b * 32u + 2, 1);
+        if (a.status) atomicOr(a.status + b, 4);
+        if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
+      }
       continue;
     }
     copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
@@ -125,6 +133,43 @@ __global__ void __launch_bounds__(128) ingest_rows(const KvipIngestArgs a) {
   const float scale = amax > 0.f ? amax / 448.f : 1.f;
   a.keys[target * 128u + d] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x / scale, __NV_SATFINITE, __NV_E4M3));
   if (d == 0) a.scales[target] = scale;
+}
+
+// Import of whole spans of Index rows (prefill): a CTA takes 32 rows of one span, a warp 8 of them, a lane
+// 4 bytes of the 128-byte key row.
+__global__ void __launch_bounds__(128) ingest_span_rows(const KvipIngestSpanArgs a) {
+  const int32_t* span = a.spans + static_cast<uint64_t>(blockIdx.y) * 8u;
+  const int32_t owner = span[0], table_row = span[1], kind = span[2], first = span[3], tokens = span[4];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  if (static_cast<uint32_t>(owner) >= a.owners || first < 0 || tokens <= 0) return;
+#pragma unroll
+  for (uint32_t j = 0; j < 8u; ++j) {
+    const uint32_t i = blockIdx.x * 32u + warp * 8u + j;
+    if (i >= static_cast<uint32_t>(tokens)) break;
+    int64_t source, position;
+    if (kind == 0) {
+      position = static_cast<int64_t>(first) + i;
+      const uint64_t page = static_cast<uint64_t>(position) / a.block;
+      const bool ok = static_cast<uint32_t>(table_row) < a.table_rows && page < a.table_stride;
+      source = ok ? static_cast<int64_t>(a.block_table[static_cast<uint64_t>(table_row) * a.table_stride + page]) * a.block +
+                        static_cast<int64_t>(static_cast<uint64_t>(position) % a.block)
+                  : -1;
+    } else {
+      const uint64_t token = static_cast<uint64_t>(first) + i;
+      const bool ok = token < a.batch_tokens;
+      source = ok ? a.slot_mapping[token] : -1;
+      position = ok ? a.positions[token] : -1;
+    }
+    if (source < 0 || static_cast<uint64_t>(source) >= a.source_rows || position < 0 ||
+        position >= static_cast<int64_t>(a.history)) {
+      if (lane == 0 && a.errors) atomicAdd(a.errors, 1);
+      continue;
+    }
+    const uint64_t target = static_cast<uint64_t>(owner) * a.history + static_cast<uint64_t>(position);
+    reinterpret_cast<uint32_t*>(a.keys + target * 128u)[lane] =
+        reinterpret_cast<const uint32_t*>(a.source_keys + static_cast<uint64_t>(source) * 128u)[lane];
+    if (lane == 0) a.scales[target] = a.source_scales[source];
+  }
 }
 
 // ---- SlotLRU commit ---------------------------------------------------------------------------
@@ -378,6 +423,20 @@ extern "C" uint32_t kvip_b200_ingest(const KvipIngestArgs* a, void* stream) {
   kvip::ingest_rows<<<a->batch * a->queries, 128, 0, static_cast<cudaStream_t>(stream)>>>(*a);
   kvip::count_launch();
   return kvip::check_launch("ingest_rows");
+}
+
+extern "C" uint32_t kvip_b200_ingest_spans(const KvipIngestSpanArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->source_keys && a->source_scales && a->block_table && a->slot_mapping && a->positions && a->spans &&
+                   a->keys && a->scales, "ingest_spans: null pointer");
+  KVIP_REQUIRE(a->owners >= 1 && a->history >= 1 && a->block >= 1 && a->table_stride >= 1, "ingest_spans: geometry");
+  KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->source_keys) & 3u) == 0 && (reinterpret_cast<uintptr_t>(a->keys) & 3u) == 0,
+               "ingest_spans: key rows must be 4-byte aligned");
+  if (a->count == 0 || a->max_tokens == 0) return 0u;
+  KVIP_REQUIRE(a->count <= 65535u, "ingest_spans: at most 65535 spans per launch");
+  dim3 grid((a->max_tokens + 31u) / 32u, a->count);
+  kvip::ingest_span_rows<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::count_launch();
+  return kvip::check_launch("ingest_span_rows");
 }
 
 extern "C" uint32_t kvip_b200_lru_commit(const KvipLruArgs* a, void* stream) {

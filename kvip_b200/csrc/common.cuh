@@ -17,6 +17,17 @@ void count_launch(uint32_t n = 1);
 uint32_t check_launch(const char* what);
 void set_error(const char* message);
 
+// Per-device host bookkeeping. A function attribute (the dynamic shared-memory limit of a kernel) and the SM
+// count belong to ONE device: a process that drives several GPUs configures every kernel once per device.
+enum KernelSlot : uint32_t {
+  kSlotLiFp8, kSlotLiBf16, kSlotTopkSelect, kSlotTopkMerge, kSlotTopkPivot, kSlotSplitEmit, kSlotSplitFallback,
+  kSlotResolve, kSlotLidu, kSlotCount
+};
+// Raises the dynamic shared-memory limit of `kernel` on the current device the first time it is asked to there.
+// Returns 0, or the launch-error code with the message set.
+uint32_t raise_dynamic_smem(KernelSlot slot, const void* kernel, int bytes, const char* what);
+uint32_t device_sm_count();   // SMs of the current device (148 when the query fails)
+
 #define KVIP_REQUIRE(cond, msg)                 \
   do {                                          \
     if (!(cond)) {                              \

@@ -40,7 +40,7 @@ constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (5
 constexpr uint32_t kMaxBatch = 1024;
 constexpr uint32_t kMaxN = 256;            // query slots * heads
 constexpr uint32_t kAtomBytes = 128 * 128; // one 128-row x 128-byte swizzle atom
-constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock
+constexpr uint32_t kDefaultWaitKilocycles = 2000000u;  // about one second of SM clock
 
 template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kAtoms = kBf16 ? 2 : 1;           // 128-byte K slices per row
@@ -86,17 +86,21 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0u;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+struct WaitControl {
+  volatile uint32_t* abort_flag;   // set by the first wait of the CTA that gives up; read by all the others
+  long long limit;                 // SM clock cycles a wait may take
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitControl& control) {
   if (mbar_try(bar, parity)) return true;  // the common case costs one instruction
   const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try(bar, parity)) return true;
-    if ((spin & 255u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - start > kWaitCycles) break;
+    if ((spin & 63u) == 0u) {
+      if (*control.abort_flag) return false;
+      if (clock64() - start > control.limit) break;
     }
   }
-  *abort_flag = 1u;
+  *control.abort_flag = 1u;
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y,
@@ -210,6 +214,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 + 2 * kMaxAcc);
   const uint32_t kQFull = 2 * S, kQEmpty = 2 * S + 1, kAccFull = 2 * S + 2, kAccEmpty = 2 * S + 2 + kMaxAcc;
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  const WaitControl waits{abort_flag, static_cast<long long>(a.wait_kilocycles ? a.wait_kilocycles : kDefaultWaitKilocycles) << 10};
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t H = a.heads, Q = a.queries, pages = a.pagesPerRequest;
@@ -304,7 +309,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         const uint32_t b = __shfl_sync(0xffffffffu, my_request, i);
         if (lane == 0) {
           if (static_cast<int32_t>(b) != bound) {
-            if (mbar_wait(bar(kQEmpty), (loaded_q & 1u) ^ 1u, abort_flag)) {
+            if (mbar_wait(bar(kQEmpty), (loaded_q & 1u) ^ 1u, waits)) {
               const uint32_t rows = active_q[b] * H;
               mbar_expect_tx(bar(kQFull), rows * 128u * Cfg::kAtoms);
               for (uint32_t atom = 0; atom < Cfg::kAtoms; ++atom)
@@ -318,7 +323,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
               alive = 0;
             }
           }
-          if (alive && mbar_wait(bar(S + stage), phase ^ 1u, abort_flag)) {
+          if (alive && mbar_wait(bar(S + stage), phase ^ 1u, waits)) {
             // test hook: the withheld page never arrives, its consumer's bounded wait gives up
             const bool withheld = a.withhold_tile && blockIdx.x == 0 && base + i - tile_begin + 1u == a.withhold_tile;
             if (!withheld) {
@@ -353,14 +358,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       bool alive = true;
       while (alive) {
         const uint32_t request_end = min(prefix[request + 1], tile_end);
-        if (!mbar_wait(bar(kQFull), seq & 1u, abort_flag)) break;
+        if (!mbar_wait(bar(kQFull), seq & 1u, waits)) break;
         const uint32_t n = active_q[request] * H;              // live accumulator columns of this request
         const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
         bool issued = false;
         for (; t < request_end; t += issuers) {
-          if (!mbar_wait(bar(stage), phase, abort_flag)) { alive = false; break; }
+          if (!mbar_wait(bar(stage), phase, waits)) { alive = false; break; }
           for (uint32_t h = 0; h < halves; ++h) {
-            if (!mbar_wait(bar(kAccEmpty + acc + h), acc_phase ^ 1u, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(bar(kAccEmpty + acc + h), acc_phase ^ 1u, waits)) { alive = false; break; }
             const uint32_t first_column = h * 128u;
             if (n <= first_column) {                 // no live query slot in this unit: nothing to compute
               mbar_arrive(bar(kAccFull + acc + h));
@@ -443,7 +448,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       }
       const uint32_t token = (t - prefix[b]) * kBlockTokens + row;
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(kAccFull + acc), acc_phase, abort_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(kAccFull + acc), acc_phase, waits))) break;
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
       const uint32_t q_first = h * unit_queries, q_last = min(nq, q_first + unit_queries);
@@ -597,24 +602,16 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
     set_error("li_score: cuTensorMapEncodeTiled failed");
     return KVIP_BAD_ARGUMENT;
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(li_score_tcgen05<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(Cfg::kSmemLimit));
-    if (e != cudaSuccess) return check_launch("li_score attribute");
-    configured = true;
-  }
+  if (uint32_t bad = raise_dynamic_smem(kBf16 ? kSlotLiBf16 : kSlotLiFp8,
+                                        reinterpret_cast<const void*>(li_score_tcgen05<kBf16>),
+                                        static_cast<int>(Cfg::kSmemLimit), "li_score attribute"))
+    return bad;
   const uint32_t n_max = a.queries * a.heads;
   uint32_t stages = Cfg::stages_for(n_max);
   if (a.stages && a.stages >= 2 && a.stages < stages) stages = a.stages;  // tuning knob: fewer key stages
   const uint32_t smem_bytes = Cfg::fixed_bytes(n_max) + stages * Cfg::kTileBytes;
   uint32_t ctas = a.ctas;
-  if (!ctas) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    ctas = static_cast<uint32_t>(sms);
-  }
+  if (!ctas) ctas = device_sm_count();
   li_score_tcgen05<kBf16><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
   count_launch();
   return check_launch("li_score_tcgen05");

@@ -35,6 +35,12 @@ __device__ __forceinline__ uint32_t find_bucket(const uint32_t* keys, uint32_t t
   return kEmpty;
 }
 
+// The two halves of a cluster barrier. A CTA may only touch another CTA's shared memory once that CTA is known to
+// be running: every CTA arrives as its first action and waits just before its first remote store, so the
+// barrier's latency hides behind the loads in between. (Both are no-ops in effect for a cluster of one CTA.)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // One request: classification, miss numbering, victims, map update, destination rows. Leaves the request's
 // unique miss tokens / slots and its control words in the scratch for the compaction.
 //
@@ -49,6 +55,8 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
   int32_t* control = work + 3 * kSlots;  // 0 status, 1 unique, 2 new cursor (-1 = keep)
   __shared__ int32_t status;
   __shared__ uint32_t scan[33];
+  cluster_arrive();   // "this CTA is resident": matched by the wait before the staged stores below, or by the
+                      // wait of an early return (taken by every CTA of the cluster alike)
   if (tid == 0) status = 0;
   __syncthreads();
   // ---- layout of the packed query rows ---------------------------------------------------
@@ -57,7 +65,8 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
     if (hi - lo < 1 || hi - lo > 4 || hi > static_cast<int32_t>(T) || lo < 0) atomicMin(&status, kErrLayout);
   }
   __syncthreads();
-  if (status) {  // the same on every rank: nobody reaches the cluster barrier
+  if (status) {  // the same on every rank: nobody reaches the second cluster barrier
+    cluster_wait();
     if (cta != 0) return;
     for (uint32_t row = r; row < T; row += B)
       for (uint32_t k = tid; k < kTop; k += kThreads) a.destination_slots[static_cast<uint64_t>(row) * kTop + k] = -1;
@@ -75,6 +84,7 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
                       pool < static_cast<int32_t>(a.pool_size) && pool < a.max_num_reqs;
   const bool padding = budget == 0 && candidate == 0 && a.logical_seq_lengths[r] == 1 && pool == a.max_num_reqs;
   if (!row_ok) {  // the same on every rank
+    cluster_wait();
     if (cta != 0) return;
     for (uint32_t q = 0; q < q_count; ++q)
       for (uint32_t k = tid; k < kTop; k += kThreads)
@@ -112,6 +122,7 @@ __device__ void lidu_request(const KvipLiduArgs& a, uint32_t* smem, cg::cluster_
       const int32_t mapped = t2s[valid ? picked[i] : 0];
       picked[i] = valid ? mapped : -1;
     }
+    cluster_wait();   // every CTA of the cluster has started: rank 0's shared memory may be written
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i)
       if (i < per_thread) staged[first + i * kThreads] = picked[i];
@@ -478,17 +489,15 @@ extern "C" uint32_t kvip_b200_lidu(const KvipLiduArgs* a, void* stream) {
   KVIP_REQUIRE(a->layer_id >= 0 && a->num_layers > 0 && a->layer_id < a->num_layers && a->max_num_reqs >= a->batch &&
                    a->qcap > 0, "lidu: access-table geometry");
   const size_t smem = (a->bitmap_words + 2u * kvip::kBuckets + 2u * kvip::kSlots) * sizeof(uint32_t);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kvip::lidu_requests, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
-      return kvip::check_launch("lidu attribute");
-    configured = true;
-  }
+  if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotLidu, reinterpret_cast<const void*>(kvip::lidu_requests),
+                                              220 * 1024, "lidu attribute"))
+    return bad;
   KVIP_REQUIRE(smem <= 220 * 1024, "lidu: bitmap does not fit in shared memory");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // helpers per request while the clusters still fit the GPU in one wave (a cluster of eight 1024-thread CTAs
   // needs eight free SMs of one GPC)
-  const unsigned ranks = 8u * a->batch <= 111u ? 8u : (4u * a->batch <= 128u ? 4u : (2u * a->batch <= 148u ? 2u : 1u));
+  const unsigned sms = kvip::device_sm_count();
+  const unsigned ranks = 8u * a->batch <= (sms * 3u) / 4u ? 8u : (4u * a->batch <= (sms * 7u) / 8u ? 4u : (2u * a->batch <= sms ? 2u : 1u));
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(a->batch * ranks, 1, 1);
   config.blockDim = dim3(kvip::kThreads, 1, 1);

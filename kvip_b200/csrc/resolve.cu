@@ -7,8 +7,10 @@
 // PackStagedUrmaQuery/StoreFallbackSource (staged_urma_pack.h:6-71,
 // common/lifetch/cache_metadata.h:32-44) and PublishQueryOutputs (streaming.cpp:66-90):
 //
-//   1. every selected position p of every query: hot  <=>  p < resident, hot_valid[owner,p]
-//      and reserved_hot[b,p] < 0  ->  location p and protect bit p; otherwise a miss;
+//   1. every selected position p of every query: hot  <=>  p < resident, hot_valid[owner,p],
+//      reserved_hot[b,p] < 0 and p outside the ABC tail  ->  location p and protect bit p; a position
+//      of the ABC tail that its ring of dedicated slots still holds  ->  resident + p % ring (known,
+//      never protected, never a victim: cache_metadata.h:22-26, 100-105); otherwise a miss;
 //   2. queries in order: misses are de-duplicated across queries with an open-addressing
 //      hash (first occurrence wins by atomicMin on the TopK position), new misses are ranked
 //      by ascending position with a block prefix sum, victims are the LRU candidates in list
@@ -18,9 +20,12 @@
 //      before the Index rows move) and fetch destination;
 //   4. logical_output / slot_output rows, routed through unpack_indices/output_valid when
 //      bound.
+//   5. one final-post record per (request, query): count, first descriptor, error
+//      (PrepareFinalFetch, common/lifetch/final_post.h:5-12).
 // Everything is ordered by prefix sums, so the slot map is a deterministic function of the
-// inputs. Speculative prefetch windows are not part of this build: the count of candidates
-// already consumed by prefetch (`used`) is zero, so the prefetch mapping is never consulted.
+// inputs. The optional prefetch windows of this build stage rows in an area of their own and never
+// write a victim slot, so the count of candidates already consumed by prefetch (`used`) is zero
+// here: the reference's prefetch mapping has no counterpart, and every descriptor is non-conflicting.
 #include "common.cuh"
 
 namespace kvip {
@@ -59,6 +64,13 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
   int64_t* f_src = a.fetch_sources + static_cast<uint64_t>(b) * kSlots;
   int32_t* f_dst = a.fetch_destinations + static_cast<uint64_t>(b) * kSlots;
   const int64_t* address_row = a.addresses + static_cast<uint64_t>(owner) * a.address_stride;
+  // ABC tail: positions [tail_begin, tail_end) live in the ring of outputStride - resident slots behind the hot ones
+  const uint32_t ring = a.outputStride - R;
+  uint32_t tail_begin = 0, tail_end = 0;
+  if (a.tail_bounds && ring) {
+    tail_begin = static_cast<uint32_t>(max(a.tail_bounds[b * 2u], 0));
+    tail_end = static_cast<uint32_t>(max(a.tail_bounds[b * 2u + 1u], 0));
+  }
 
   // ---- round init (v9_init_kernel, lifecycle.cpp:32-81): per-request scratch ----------
   for (uint32_t i = tid; i < words; i += kThreads) bitmap[i] = 0;
@@ -97,9 +109,12 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
     for (uint32_t j = 0; j < 2; ++j) {
       uint32_t slot = kMissing;
       if (q < Q && token[q][j] >= 0) {
-        if (static_cast<uint32_t>(token[q][j]) >= H) {
+        const uint32_t p = static_cast<uint32_t>(token[q][j]);
+        if (p >= H) {
           atomicOr(ctl + 1, KVIP_ERR_TOKEN_RANGE);
-        } else if (static_cast<uint32_t>(token[q][j]) < R && is_valid[q][j] != 0 && ordinal[q][j] < 0) {
+        } else if (p >= tail_begin && p < tail_end) {
+          if (p - tail_begin < ring) slot = R + p % ring;   // held by the ring; otherwise resolved like a cold position
+        } else if (p < R && is_valid[q][j] != 0 && ordinal[q][j] < 0) {
           slot = static_cast<uint32_t>(token[q][j]);
           atomicOr(bitmap + (slot >> 5), 1u << (slot & 31u));
         }
@@ -234,10 +249,17 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
       const uint32_t record = ordinal >= 0 ? static_cast<uint32_t>(ordinal) : kLruSlots + rank;
       change_slots[record] = slot;
       changes[record] = token;
-      f_src[rank] = address_row[token];
+      const int64_t source = address_row[token];
+      // a source outside the pool fails the request HERE, before the Index rows move (streaming.cpp:399-400
+      // range-checks the same descriptors): nothing is exchanged or fetched for it and it keeps no residency
+      if (a.source_bytes && (source < 0 || (source & 15) != 0 ||
+                             static_cast<uint64_t>(source) + a.tokenBytes > a.source_bytes))
+        atomicOr(ctl + 1, KVIP_ERR_SOURCE);
+      f_src[rank] = source;
       f_dst[rank] = static_cast<int32_t>(owner * a.outputStride) + slot;
     }
     __syncthreads();
+    if (ctl[1]) break;   // a source address failed its range check
     if (tid == 0) {
       ctl[0] = old_count + added;
       a.query_counts[b * 8u + q] = static_cast<int32_t>(added);
@@ -253,6 +275,16 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
     a.change_count[b] = static_cast<int32_t>(kLruSlots + (error ? 0u : ctl[0]));
     a.row_status[b * 32u + 0] = static_cast<int32_t>(error);
     a.row_status[b * 32u + 1] = static_cast<int32_t>(ctl[0]);
+  }
+  __syncthreads();   // the final counts are in place
+  if (a.final_posts && tid < 4u * 32u) {   // four 128-byte records, one word per thread
+    const uint32_t q = tid >> 5, word = tid & 31u;
+    const uint32_t error = ctl[1];
+    uint32_t first = 0;
+    for (uint32_t earlier = 0; earlier < q; ++earlier) first += static_cast<uint32_t>(a.query_counts[b * 8u + earlier]);
+    const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + q]);
+    const uint32_t value = word == 0u ? count : (word == 2u ? error : (word == 4u ? b * kSlots + first : (word == 5u ? count : 0u)));
+    reinterpret_cast<uint32_t*>(a.final_posts + static_cast<uint64_t>(b) * 4u + q)[word] = value;
   }
 }
 
@@ -294,12 +326,9 @@ __global__ void __launch_bounds__(256) publish_outputs(const KvipResolveArgs a) 
 uint32_t launch_resolve_requests(const KvipResolveArgs& a, cudaStream_t stream) {
   const uint32_t words = (a.resident + 31u) >> 5;
   const size_t smem = (words + 2u * kBuckets + 33u + 8u) * sizeof(uint32_t);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(resolve_requests, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-      return check_launch("resolve attribute");
-    configured = true;
-  }
+  if (uint32_t bad = raise_dynamic_smem(kSlotResolve, reinterpret_cast<const void*>(resolve_requests), 200 * 1024,
+                                        "resolve attribute"))
+    return bad;
   resolve_requests<<<a.batch, kThreads, smem, stream>>>(a);
   count_launch();
   return check_launch("resolve_requests");
@@ -324,7 +353,8 @@ extern "C" uint32_t kvip_b200_resolve(const KvipResolveArgs* a, void* stream) {
                    a->addresses && a->locations && a->changes && a->change_slots && a->change_count &&
                    a->events_src && a->events_dst && a->query_counts && a->fetch_sources &&
                    a->fetch_destinations && a->row_status, "resolve: null pointer");
-  KVIP_REQUIRE(a->tail_bounds == nullptr, "resolve: ABC tail bounds are not supported by this build");
+  KVIP_REQUIRE(a->tail_bounds == nullptr || (a->outputStride - a->resident >= 384 && (a->outputStride - a->resident) % 128 == 0),
+               "resolve: ABC tail bounds need at least 384 dedicated slots behind the hot ones, in blocks of 128");
   KVIP_REQUIRE(a->batch >= 1 && a->queries >= 1 && a->queries <= KVIP_MAX_QUERIES, "resolve: bad batch/queries");
   KVIP_REQUIRE(a->resident >= KVIP_TOPK && a->resident <= 131072 && a->resident % 128 == 0,
                "resolve: resident must be in 2048..131072, multiple of 128");

@@ -143,8 +143,12 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows_staged(const KvipFet
     const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
     const bool ok = source >= 0 && static_cast<uint64_t>(source) + a.tokenBytes <= a.source_bytes &&
                     (source & 15) == 0 && dest >= 0 && slot < a.outputStride;
-    if (!ok) {
-      if (lane == 0) atomicOr(a.row_status + b * 32u + 2, 1);
+    if (!ok) {  // as in fetch_rows: recorded, skipped, and the destination slot loses residency
+      if (lane == 0) {
+        atomicOr(a.row_status + b * 32u + 2, 1);
+        if (a.status) atomicOr(a.status + b, 4);
+        if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
+      }
       continue;
     }
     uint32_t found = 0xffffffffu;

@@ -118,17 +118,15 @@ uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream);
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream) {
   if (a.split_scratch) return launch_topk_split(a, stream);
   if (!a.histogram) return launch_topk_pivot(a, stream);
-  uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
+  uint32_t segments = (4u * device_sm_count() + a.rows - 1u) / a.rows;
   segments = segments < 1u ? 1u : (segments > 32u ? 32u : segments);
   topk_histogram<<<dim3(segments, a.rows), kHistThreads, 0, stream>>>(a);
   count_launch();
   if (uint32_t bad = check_launch("topk_histogram")) return bad;
-  static bool configured = false;  // static + dynamic shared memory exceeds the 48 KiB default
-  if (!configured) {
-    if (cudaFuncSetAttribute(topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
-      return check_launch("topk_select attribute");
-    configured = true;
-  }
+  // static + dynamic shared memory exceeds the 48 KiB default
+  if (uint32_t bad = raise_dynamic_smem(kSlotTopkSelect, reinterpret_cast<const void*>(topk_select), 64 * 1024,
+                                        "topk_select attribute"))
+    return bad;
   topk_select<<<a.rows, kThreads, kCandidates * sizeof(uint32_t), stream>>>(a);
   count_launch();
   return check_launch("topk_select");
@@ -191,12 +189,9 @@ extern "C" uint32_t kvip_b200_topk_merge(const KvipMergeArgs* a, void* stream) {
   uint32_t padded = 2048;
   while (padded < a->shards * KVIP_TOPK) padded <<= 1;
   const size_t smem = static_cast<size_t>(padded) * sizeof(uint64_t);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kvip::topk_merge, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8) != cudaSuccess)
-      return kvip::check_launch("topk_merge attribute");
-    configured = true;
-  }
+  if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotTopkMerge, reinterpret_cast<const void*>(kvip::topk_merge),
+                                              16384 * 8, "topk_merge attribute"))
+    return bad;
   kvip::topk_merge<<<a->rows, kvip::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a, padded);
   kvip::count_launch();
   return kvip::check_launch("topk_merge");

@@ -62,6 +62,7 @@ static __device__ void select_row(const KvipTopkArgs& a, const uint32_t row, uin
     } else {
       for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
     }
+    if (tid == 0) { found[0] = 0; found[1] = 0; }   // defined even when a supplied histogram was inconsistent
     __syncthreads();
     // every lane of a warp runs the same number of iterations (hist_add uses warp votes)
     const uint32_t rounds = (pass == 0 && global_hist) ? 0u : (in_smem ? (cand_count + kThreads - 1) / kThreads
@@ -126,11 +127,18 @@ static __device__ void select_row(const KvipTopkArgs& a, const uint32_t row, uin
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j) {
             const uint32_t key = sortable_key(e[j]);
-            if ((v * 4u + j) < L && (key & prefix_mask) == prefix) cand_keys[atomicAdd(&cand_count, 1u)] = key;
+            if ((v * 4u + j) < L && (key & prefix_mask) == prefix) {
+              // the bound holds whenever the histogram told the truth; a histogram that undercounted the bin
+              // (a caller's scratch that was not all-zero, two calls racing on one scratch) must not write
+              // past the list: the count then exceeds the capacity and the global passes take over
+              const uint32_t at = atomicAdd(&cand_count, 1u);
+              if (at < kCandidates) cand_keys[at] = key;
+            }
           }
         }
-        in_smem = true;
       }
+      __syncthreads();
+      in_smem = want <= kCandidates && cand_count <= kCandidates;   // block-uniform
       __syncthreads();
     }
   }
@@ -168,11 +176,13 @@ static __device__ void select_row(const KvipTopkArgs& a, const uint32_t row, uin
       const uint32_t mask_eq = __ballot_sync(0xffffffffu, position < L && key == kth);
       if ((mask_gt >> lane) & 1u) {
         const uint32_t at = g + __popc(mask_gt & below);
-        out[at] = static_cast<int32_t>(position + a.base_index);
-        if (out_scores) out_scores[at] = e[j];
+        if (at < kTop) {   // always true for a consistent selection; keeps a corrupted scratch from writing past the row
+          out[at] = static_cast<int32_t>(position + a.base_index);
+          if (out_scores) out_scores[at] = e[j];
+        }
       } else if ((mask_eq >> lane) & 1u) {
         const uint32_t rank = q + __popc(mask_eq & below);
-        if (rank < need_eq) {
+        if (rank < need_eq && count_gt + rank < kTop) {
           out[count_gt + rank] = static_cast<int32_t>(position + a.base_index);
           if (out_scores) out_scores[count_gt + rank] = e[j];
         }

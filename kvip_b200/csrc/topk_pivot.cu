@@ -316,22 +316,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
 
 uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
   constexpr int kSmem = static_cast<int>(2u * kPivotCandidates * sizeof(uint32_t));
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(topk_pivot, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
-      return check_launch("topk_pivot attribute");
-    configured = true;
-  }
+  if (uint32_t bad = raise_dynamic_smem(kSlotTopkPivot, reinterpret_cast<const void*>(topk_pivot), kSmem,
+                                        "topk_pivot attribute"))
+    return bad;
   // two, four or eight CTAs per row while the clusters still fit the GPU in one wave (a cluster of eight
   // 1024-thread CTAs needs eight free SMs of one GPC: about two of them fit per GPC)
-  static int sm_count = 0;
-  if (!sm_count) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
-      sm_count = 148;
-  }
-  const unsigned sms = static_cast<unsigned>(sm_count);
+  const unsigned sms = device_sm_count();
   const unsigned ranks = 8u * a.rows <= (sms * 3u) / 4u ? 8u : (4u * a.rows <= (sms * 7u) / 8u ? 4u : (2u * a.rows <= sms ? 2u : 1u));
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(a.rows * ranks, 1, 1);

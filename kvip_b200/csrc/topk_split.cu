@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(topk_core::kThreads) split_fallback(const Kvip
 uint32_t launch_topk(const KvipTopkArgs& a, cudaStream_t stream);
 
 uint32_t launch_topk_split(const KvipTopkArgs& a, cudaStream_t stream) {
-  uint32_t segments = (4u * 148u + a.rows - 1u) / a.rows;
+  uint32_t segments = (4u * device_sm_count() + a.rows - 1u) / a.rows;
   segments = segments < 1u ? 1u : (segments > kMaxSegments ? kMaxSegments : segments);
   // a slice must fit the registers of split_emit: 16 warps x kMaxGroups x 32 positions
   const uint32_t slice_limit = (kSplitThreads / 32u) * kMaxGroups * 32u - 1024u;
@@ -295,13 +295,12 @@ uint32_t launch_topk_split(const KvipTopkArgs& a, cudaStream_t stream) {
   }
   const size_t emit_smem = (2u * kCandidates + 1024u + 33u + 8u) * sizeof(uint32_t);
   const size_t fallback_smem = kCandidates * sizeof(uint32_t);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(split_emit, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(split_fallback, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
-      return check_launch("topk split attribute");
-    configured = true;
-  }
+  if (uint32_t bad = raise_dynamic_smem(kSlotSplitEmit, reinterpret_cast<const void*>(split_emit), 80 * 1024,
+                                        "topk split attribute"))
+    return bad;
+  if (uint32_t bad = raise_dynamic_smem(kSlotSplitFallback, reinterpret_cast<const void*>(split_fallback), 64 * 1024,
+                                        "topk split attribute"))
+    return bad;
   const dim3 grid(segments, a.rows);
   split_histogram<<<grid, kSplitThreads, 0, stream>>>(a);
   split_filter<<<grid, kSplitThreads, 0, stream>>>(a);

@@ -170,7 +170,7 @@ class CudaBinding:
     def __init__(self, torch, arguments, lease, output, *, batch, history, resident, query_ends, hot_valid,
                  token_addresses, row_owners=None, tail_bounds=None, output_stride=None, scratch=None,
                  token_bytes=None, queries=None, score_mode=_lib.SCORE_FP32, sm_count=0, gather_output=None,
-                 li_variant=0, prefetch_limit=0, source=None, library=None):
+                 li_variant=0, prefetch_limit=0, source=None, library=None, head_sum=_lib.HEAD_SUM_AUTO):
         self.torch, self.lease = torch, lease
         self.library = _lib.load_library(library)
         if len(arguments) != 14:
@@ -183,16 +183,25 @@ class CudaBinding:
         query, keys, weights = arguments[0], arguments[1], arguments[2]
         queries = queries or query.shape[0] // batch
         heads = query.numel() // (batch * queries * 128)
+        output_stride = output_stride or resident
+        tail_tokens = output_stride - resident
+        if tail_tokens < 0 or tail_tokens % 128:
+            raise ValueError("Output stride must preserve hot and optional ABC slots")
         if tail_bounds is not None:
-            raise ValueError("ABC tail bounds are not supported by this build")
+            if tail_tokens < 384:
+                raise ValueError("Serving ABC bounds require at least 384 dedicated output slots")
+            if (tail_bounds.device != self.device or tail_bounds.dtype != torch.int32
+                    or tuple(tail_bounds.shape) != (batch, 2) or not tail_bounds.is_contiguous()):
+                raise ValueError("LIFetch tail_bounds must be contiguous int32 [batch, 2]")
         token_bytes = token_bytes or (lease.token_bytes if lease is not None else output.shape[-1])
         owners = hot_valid.shape[0]
         self.runtime_shape = _lib.RuntimeShape.prepare(
             self.library, batch=batch, history=history, resident=resident, indexHeads=heads, smCount=sm_count,
             queries=queries, keyDtype=_lib.KEY_BF16 if keys.dtype == torch.bfloat16 else _lib.KEY_FP8,
             weightDtype=_lib.WEIGHT_FP32 if weights.dtype == torch.float32 else _lib.WEIGHT_BF16,
-            scoreMode=score_mode, outputStride=output_stride or resident, owners=owners, tokenBytes=token_bytes,
-            keyRows=keys.numel() // 128, gatherRows=int(gather_output is not None), liVariant=li_variant)
+            scoreMode=score_mode, outputStride=output_stride, owners=owners, tokenBytes=token_bytes,
+            keyRows=keys.numel() // 128, gatherRows=int(gather_output is not None), liVariant=li_variant,
+            headSum=head_sum)
         self.shape = self.runtime_shape
         self.shape_pointer = ctypes.byref(self.runtime_shape)
         self.prefetch_limit = prefetch_limit
@@ -205,7 +214,9 @@ class CudaBinding:
                 raise ValueError(f"Shared LIFetch scratch mismatch: {name}")
             setattr(self, name, value)
         self.reserved_hot.fill_(-1)
-        self.final_posts = self.mapping = self.final_status = self.prefetch_status = None
+        # one 128-byte record per (request, query): count, first descriptor, error (include/kvip_b200.h: KvipFinalPost)
+        self.final_posts = torch.zeros((batch * self.final_workers, 32), dtype=torch.int32, device=self.device)
+        self.mapping = self.final_status = self.prefetch_status = None
         self.output, self.query_ends, self.hot_valid, self.row_owners = output, query_ends, hot_valid, row_owners
         self.token_addresses, self.tail_bounds, self.gather_output = token_addresses, tail_bounds, gather_output
         for name, tensor, expected in (("query_ends", query_ends, (batch * queries,)),
@@ -246,9 +257,11 @@ class CudaBinding:
             query_ends=query_ends.data_ptr(), fetch_sources=self.fallback_addresses.data_ptr(),
             fetch_destinations=self.destinations.data_ptr(), hot_valid=hot_valid.data_ptr(),
             row_owners=0 if row_owners is None else row_owners.data_ptr(), token_addresses=token_addresses.data_ptr(),
-            address_stride=token_addresses.stride(0), output_stride=self.output_stride, tail_bounds=0,
+            address_stride=token_addresses.stride(0), output_stride=self.output_stride,
+            tail_bounds=0 if tail_bounds is None else tail_bounds.data_ptr(),
             row_status=self.row_status.data_ptr(), query_counts=self.query_counts.data_ptr(),
-            pool=output.data_ptr(), source_base=source_base, source_bytes=source_bytes, shape=self.runtime_shape)
+            pool=output.data_ptr(), source_base=source_base, source_bytes=source_bytes, shape=self.runtime_shape,
+            final_posts=self.final_posts.data_ptr())
         self.context = _host_blob(torch, bytes(context))
         self.arguments = tuple(arguments) + (self.context,)
         self.bindings = None  # completed by LIFetch (needs the workspace record)
@@ -306,7 +319,7 @@ class IndexUpdate:
         words = [keys.data_ptr(), scales.data_ptr(), addresses.data_ptr(), logical_ids.data_ptr(),
                  rotating.change_slots.data_ptr(), rotating.changes.data_ptr(), self.status.data_ptr(),
                  addresses.stride(0), rotating.rows.data_ptr(), owners_tensor.data_ptr(), rotating.row_status.data_ptr(),
-                 0, 0, 0, rotating.final_workers, 128, rotating.hot_valid.data_ptr(), 0,
+                 rotating.final_posts.data_ptr(), 0, 0, rotating.final_workers, 128, rotating.hot_valid.data_ptr(), 0,
                  rotating.arguments[9].data_ptr(), rotating.locations.data_ptr(),
                  0 if query_inputs is None else query_inputs.unpack_indices.data_ptr(),
                  0 if query_inputs is None else query_inputs.output_valid.data_ptr(),
@@ -454,3 +467,12 @@ class LIFetch:
                          | (_lib.OPTION_DEFERRED_FETCH if deferred_fetch else 0))
         self._options_word = self.workspace.numpy()[96:100].view("<u4")   # same host memory as the record
         self._options_word[0] = self._options
+
+    def stage_times(self):
+        """Device time of every stage of the last call made with `set_options(diagnostics=True)`, in microseconds,
+        plus `total`. Reads the `times` buffer on the host (a synchronising copy): for use after the step, outside
+        any capture. A stage includes the gap to its predecessor; a stage the call skipped reports 0."""
+        stamps = self.times[: len(_lib.TIME_STAGES) + 1].cpu().tolist()
+        result = {name: (stamps[i + 1] - stamps[i]) / 1e3 for i, name in enumerate(_lib.TIME_STAGES)}
+        result["total"] = (stamps[-1] - stamps[0]) / 1e3
+        return result

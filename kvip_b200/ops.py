@@ -31,7 +31,8 @@ def _require(tensor, name, dtype=None, device=None):
 
 
 def li_score(query, keys, weights, query_scale, key_scale, key_lengths, query_ends, block_table, scores=None, *,
-             status=None, score_mode=_lib.SCORE_FP32, ctas=0, stages=0, simt=False, withhold_tile=0):
+             status=None, score_mode=_lib.SCORE_FP32, ctas=0, stages=0, simt=False, withhold_tile=0,
+             wait_kilocycles=0, head_sum=_lib.HEAD_SUM_AUTO):
     """scores[t, s] = kscale[s] * sum_h W[t,h] * relu(q[t,h,:] . k[s,:]) over the paged Index cache.
 
     query [B*Q, H, 128] float8_e4m3fn/uint8 or bfloat16; keys [rows, 128] same element type;
@@ -63,7 +64,8 @@ def li_score(query, keys, weights, query_scale, key_scale, key_lengths, query_en
         heads=heads, pagesPerRequest=pages, keyRows=keys.numel() // 128, scoreStride=scores.shape[1],
         keyDtype=_lib.KEY_BF16 if bf16 else _lib.KEY_FP8,
         weightDtype=_lib.WEIGHT_FP32 if weights.dtype == torch.float32 else _lib.WEIGHT_BF16,
-        scoreMode=score_mode, ctas=ctas, stages=stages, withhold_tile=withhold_tile)
+        scoreMode=score_mode, ctas=ctas, stages=stages, withhold_tile=withhold_tile,
+        wait_kilocycles=wait_kilocycles, head_sum=head_sum)
     lib = _lib.load_library()
     fn = lib.kvip_b200_li_score_simt if simt else lib.kvip_b200_li_score
     _lib.check(fn(ctypes.byref(args), _stream(device)), "li_score")
@@ -151,30 +153,36 @@ class ResolveState:
         self.row_status = torch.zeros((batch, 32), **i32)
         self.logical_output = torch.full((batch * queries, TOPK), -1, **i32)
         self.slot_output = torch.full((batch * queries, TOPK), -1, **i32)
+        self.final_posts = torch.zeros((batch * 4, 32), **i32)   # KvipFinalPost records, one per (request, query)
 
 
 def resolve(selected, hot_valid, reserved_hot, lru_slots, logical_ids, addresses, state, *, history, resident,
-            output_stride=None, row_owners=None, unpack_indices=None, output_valid=None, query_ends=None):
-    """Classify, resolve and publish one round. selected [B, Q, 2048] int32."""
+            output_stride=None, row_owners=None, unpack_indices=None, output_valid=None, query_ends=None,
+            tail_bounds=None, source_bytes=0, token_bytes=0):
+    """Classify, resolve and publish one round. selected [B, Q, 2048] int32. `tail_bounds` [B, 2] int32 marks the
+    ABC tail of every request (its rows live in the output_stride - resident slots behind the hot ones);
+    `source_bytes` / `token_bytes` switch on the range check of the missing rows' source addresses."""
     device = selected.device
     batch, queries = selected.shape[0], selected.shape[1]
     for name, t, dt in (("selected", selected, torch.int32), ("hot_valid", hot_valid, torch.int32),
                         ("reserved_hot", reserved_hot, torch.int32), ("lru_slots", lru_slots, torch.int32),
                         ("logical_ids", logical_ids, torch.int64), ("addresses", addresses, torch.int64),
                         ("row_owners", row_owners, torch.int32), ("unpack_indices", unpack_indices, torch.int64),
-                        ("output_valid", output_valid, torch.int64), ("query_ends", query_ends, torch.int32)):
+                        ("output_valid", output_valid, torch.int64), ("query_ends", query_ends, torch.int32),
+                        ("tail_bounds", tail_bounds, torch.int32)):
         _require(t, name, dt, device)
     s = state
     args = _lib.ResolveArgs(
         topk=_ptr(selected), row_owners=_ptr(row_owners), hot_valid=_ptr(hot_valid), reserved_hot=_ptr(reserved_hot),
-        lru_slots=_ptr(lru_slots), tail_bounds=None, logical_ids=_ptr(logical_ids), addresses=_ptr(addresses),
+        lru_slots=_ptr(lru_slots), tail_bounds=_ptr(tail_bounds), logical_ids=_ptr(logical_ids), addresses=_ptr(addresses),
         locations=_ptr(s.locations), changes=_ptr(s.changes), change_slots=_ptr(s.change_slots),
         change_count=_ptr(s.change_count), events_src=_ptr(s.events_src), events_dst=_ptr(s.events_dst),
         query_counts=_ptr(s.query_counts), fetch_sources=_ptr(s.fetch_sources),
         fetch_destinations=_ptr(s.fetch_destinations), logical_output=_ptr(s.logical_output),
         slot_output=_ptr(s.slot_output), unpack_indices=_ptr(unpack_indices), output_valid=_ptr(output_valid),
         query_ends=_ptr(query_ends), row_status=_ptr(s.row_status), batch=batch, queries=queries, history=history,
-        resident=resident, address_stride=addresses.stride(0), outputStride=output_stride or resident)
+        resident=resident, address_stride=addresses.stride(0), outputStride=output_stride or resident,
+        tokenBytes=token_bytes, source_bytes=source_bytes, final_posts=_ptr(getattr(s, "final_posts", None)))
     _lib.check(_lib.load_library().kvip_b200_resolve(ctypes.byref(args), _stream(device)), "resolve")
     return state
 
@@ -204,9 +212,11 @@ def make_shadow(batch, history, device):
     return identity.repeat(batch, 2).contiguous()
 
 
-def fetch(source, source_bytes, pool, hot_valid, state, *, resident, output_stride, token_bytes, row_owners=None):
+def fetch(source, source_bytes, pool, hot_valid, state, *, resident, output_stride, token_bytes, row_owners=None,
+          status=None):
     """Copy every descriptor's row from `source` (a device-visible tensor or a raw device pointer to
-    the mapped host pool) into its resident slot and publish residency."""
+    the mapped host pool) into its resident slot and publish residency. `status` [B] int32 (the Index-update
+    status) receives code 4 for a request with a descriptor outside the source."""
     device = pool.device
     batch = state.fetch_sources.shape[0]
     _require(pool, "pool", torch.uint8, device)
@@ -216,7 +226,7 @@ def fetch(source, source_bytes, pool, hot_valid, state, *, resident, output_stri
         source_base=base, fetch_sources=_ptr(state.fetch_sources), fetch_destinations=_ptr(state.fetch_destinations),
         query_counts=_ptr(state.query_counts), row_owners=_ptr(row_owners), row_status=_ptr(state.row_status),
         pool=_ptr(pool), hot_valid=_ptr(hot_valid), source_bytes=source_bytes, batch=batch, resident=resident,
-        outputStride=output_stride, tokenBytes=token_bytes)
+        outputStride=output_stride, tokenBytes=token_bytes, status=_ptr(status))
     _lib.check(_lib.load_library().kvip_b200_fetch(ctypes.byref(args), _stream(device)), "fetch")
 
 
@@ -249,6 +259,28 @@ def ingest(keys, scales, source_keys, source_scales, slot_mapping, gather_indice
         keys=_ptr(keys), scales=_ptr(scales), batch=row_owners.numel(), queries=queries, history=history,
         source_is_bf16=int(bf16))
     _lib.check(_lib.load_library().kvip_b200_ingest(ctypes.byref(args), _stream(device)), "ingest")
+
+
+def ingest_spans(keys, scales, source_keys, source_scales, block_table, slot_mapping, positions, spans, *, history,
+                 block, max_tokens, errors=None):
+    """Import whole spans of Index rows in one launch (prefill): `spans` int32 [n, 8] rows of
+    (owner, block-table row, kind, first, tokens, 0, 0, 0); kind 0 restores cached history through the block
+    table, kind 1 writes this forward's tokens through slot_mapping / positions."""
+    device = keys.device
+    for name, t, dt in (("keys", keys, torch.uint8), ("scales", scales, torch.float32),
+                        ("source_keys", source_keys, torch.uint8), ("source_scales", source_scales, torch.float32),
+                        ("block_table", block_table, torch.int32), ("slot_mapping", slot_mapping, torch.int64),
+                        ("positions", positions, torch.int64), ("spans", spans, torch.int32),
+                        ("errors", errors, torch.int32)):
+        _require(t, name, dt, device)
+    table = block_table.reshape(-1, block_table.shape[-1])
+    args = _lib.IngestSpanArgs(
+        source_keys=_ptr(source_keys), source_scales=_ptr(source_scales), block_table=_ptr(table),
+        slot_mapping=_ptr(slot_mapping), positions=_ptr(positions), spans=_ptr(spans), keys=_ptr(keys),
+        scales=_ptr(scales), errors=_ptr(errors), source_rows=source_scales.numel(), count=spans.shape[0],
+        max_tokens=max_tokens, owners=keys.shape[0], history=history, block=block, table_rows=table.shape[0],
+        table_stride=table.shape[1], batch_tokens=min(slot_mapping.numel(), positions.numel()))
+    _lib.check(_lib.load_library().kvip_b200_ingest_spans(ctypes.byref(args), _stream(device)), "ingest_spans")
 
 
 def lru_commit(order, slots, bitmap, unique, reserved_hot, touched, active):

@@ -28,7 +28,7 @@ CHANGE_CAPACITY = 10240
 BLOCK = 128
 MISSING = -1
 
-ERR_TOKEN_RANGE, ERR_NO_SLOT, ERR_HASH = 1, 4, 8
+ERR_TOKEN_RANGE, ERR_NO_SLOT, ERR_HASH, ERR_SOURCE = 1, 4, 8, 64
 
 
 # ---------------------------------------------------------------------------------------------
@@ -245,10 +245,23 @@ def free_slots_ring(protected_words, budget, begin, count):
 # classification + resolver (staged_topk_classify.h:9-46; resolver_staged_dma2.h:83-237;
 # staged_urma_pack.h:6-71; streaming.cpp:66-90)
 # ---------------------------------------------------------------------------------------------
-def resolve_request(selected, hot_valid, reserved_hot, lru_slots, history, resident):
+def resolve_request(selected, hot_valid, reserved_hot, lru_slots, history, resident, *, tail_bounds=None,
+                    output_stride=None, addresses=None, source_bytes=0, token_bytes=0, request=0):
     """One request. selected [Q,2048] positions (-1 = none). Returns a dict with locations [Q,2048],
-    events (src, dst), per-query counts, change records and the error word."""
+    events (src, dst), per-query counts, change records, the final posts and the error word.
+
+    ABC tail (common/lifetch/cache_metadata.h:22-26, 100-105; prefetch.h:26-44): with tail_bounds = (begin, end)
+    and ring = output_stride - resident dedicated slots, a position begin <= p < end is never hot by position;
+    while p - begin < ring its location is resident + p % ring (the reference's mapping code
+    resident + 8192 + p % ring, resolved by ResolvePhysicalSlot), otherwise it is resolved like a cold position.
+    Source check (streaming.cpp:399-400): with source_bytes, a new slot whose source address is negative, not
+    16-byte aligned or beyond the pool fails the request with ERR_SOURCE before anything moves.
+    Final posts (common/lifetch/final_post.h:5-12): per query {count, pending 0, error, deferred 0, first
+    descriptor = request * 8192 + descriptors of earlier queries, nonconflicting = count}."""
     queries = selected.shape[0]
+    ring = (output_stride or resident) - resident
+    tail_begin, tail_end = (int(tail_bounds[0]), int(tail_bounds[1])) if tail_bounds is not None and ring else (0, 0)
+    tail_begin, tail_end = max(tail_begin, 0), max(tail_end, 0)
     loc = np.full((queries, TOPK), MISSING, dtype=np.int64)
     protect = np.zeros(resident, dtype=bool)
     error = 0
@@ -259,6 +272,10 @@ def resolve_request(selected, hot_valid, reserved_hot, lru_slots, history, resid
                 continue
             if p >= history:
                 error |= ERR_TOKEN_RANGE
+                continue
+            if tail_begin <= p < tail_end:
+                if p - tail_begin < ring:
+                    loc[q, k] = resident + p % ring
                 continue
             if p < resident and hot_valid[p] != 0 and reserved_hot[p] < 0:
                 loc[q, k] = p
@@ -304,6 +321,13 @@ def resolve_request(selected, hot_valid, reserved_hot, lru_slots, history, resid
         if error:
             break
         base = len(ev_src)
+        if source_bytes and addresses is not None:
+            for token in new_tokens:
+                source = int(addresses[token])
+                if source < 0 or source % 16 or source + token_bytes > source_bytes:
+                    error |= ERR_SOURCE
+        if error:
+            break
         for i, (token, slot) in enumerate(zip(new_tokens, victims)):
             assigned[token] = slot
             ordinal = int(reserved_hot[slot])
@@ -319,7 +343,12 @@ def resolve_request(selected, hot_valid, reserved_hot, lru_slots, history, resid
                 loc[q, k] = assigned[p]
     if error:
         counts = [0] * 4
-    return dict(locations=loc.astype(np.int32), events_src=np.array(ev_src, dtype=np.int32),
+    posts = np.zeros((4, 32), dtype=np.uint32)
+    for q in range(4):
+        posts[q, 0] = posts[q, 5] = counts[q]
+        posts[q, 2] = error
+        posts[q, 4] = request * SLOTS + sum(counts[:q])
+    return dict(final_posts=posts, locations=loc.astype(np.int32), events_src=np.array(ev_src, dtype=np.int32),
                 events_dst=np.array(ev_dst, dtype=np.int32), counts=counts, total=0 if error else len(ev_src),
                 changes=changes, change_slots=change_slots,
                 change_count=LRU_SLOTS + (0 if error else len(ev_src)), error=error)

@@ -1,8 +1,8 @@
 """Regenerates the golden vectors under tests/golden/ by RUNNING THE REFERENCE's own CPU code.
 
-Run it only where a checkout of the reference is available (its path is the first argument):
+Run it only where a checkout of the reference is available; its path is the first argument, or $KVIP_REFERENCE:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference [--only=page_updates|ingest_prefill]
 
 What is imported and executed (paths inside the reference project):
   * tests/operators/lifetch/support/workloads.py: prepare_fixture, prepare_full_chain_fixture,
@@ -10,7 +10,7 @@ What is imported and executed (paths inside the reference project):
   * tests/operators/lifetch/support/correctness.py: validate_topk (kept as a cross-check here);
   * python/kvip/cache/lru.py (+ numba kernels), python/kvip/cache/abc.py (CPU branch),
     python/kvip/cache/page_updates.py (CPU branch);
-  * python/kvip/adapters/vllm/inputs.py + index_import.py (QueryInputs, ingest_decode on CPU);
+  * python/kvip/adapters/vllm/inputs.py + index_import.py (QueryInputs, ingest_decode and ingest_prefill on CPU);
   * oracle/_ref/hot_slot_ref: the reference's csrc/operators/lidu/op_kernel/hot_slot_selection.h
     compiled by oracle/Makefile, fed the cases of tests/operators/lidu/test_hot_slot_selection.py.
 Only inputs the CUDA path needs and the reference's outputs are stored (compressed .npz); the
@@ -109,14 +109,59 @@ def page_updates_fixture(torch):
     np.savez_compressed(HERE / "page_updates.npz", **store)
 
 
+def ingest_prefill_fixture(torch):
+    """A mixed batch through the reference's VllmIndexCacheStorage.ingest_prefill on CPU (index_import.py:17-36):
+    a request with cached history that is restored once, a fresh prefill, a decode row, and a second forward of the
+    first request (its history is not imported again)."""
+    from kvip.adapters.vllm.index_import import VllmIndexCacheStorage
+    rng = np.random.default_rng(23)
+    owners, history, block, blocks = 5, 512, 128, 12
+    storage = VllmIndexCacheStorage(torch, owners, history, 256, torch.device("cpu"))
+    # few distinct byte values: the fixture compresses well and every row is still distinguishable by its scale
+    storage.keys.copy_(torch.from_numpy(rng.integers(0, 4, tuple(storage.keys.shape), dtype=np.uint8)))
+    storage.scales.copy_(torch.from_numpy(rng.random(tuple(storage.scales.shape), dtype=np.float32)))
+    cache_keys = torch.from_numpy(rng.integers(4, 12, (blocks, block, 1, 128), dtype=np.uint8))
+    cache_scales = torch.from_numpy(rng.random((blocks, block, 1), dtype=np.float32))
+    table = torch.from_numpy(rng.permutation(blocks).astype(np.int32).reshape(3, 4))
+    store = dict(before_keys=storage.keys.numpy().copy(), before_scales=storage.scales.numpy().copy(),
+                 cache_keys=cache_keys.numpy(), cache_scales=cache_scales.numpy(), block_table=table.numpy(),
+                 block_size=np.int64(block))
+    # plan rows: (request, owner, begin, stop, decode, start)
+    forwards = [[("a", 3, 0, 40, 0, 300), ("b", 1, 40, 100, 0, 0), ("c", 4, 100, 101, 1, 450)],
+                [("a", 3, 0, 25, 0, 340), ("b", 1, 25, 26, 1, 60), ("c", 4, 26, 27, 1, 451)]]
+    for step, rows in enumerate(forwards):
+        plans = [SimpleNamespace(request=r, owner=o, begin=b, stop=e, decode=bool(d), start=s) for r, o, b, e, d, s in rows]
+        storage.prepare(plans)
+        tokens = rows[-1][3]
+        positions = torch.cat([torch.arange(s, s + (e - b), dtype=torch.int64) for _, _, b, e, _, s in rows])
+        slot_mapping = torch.cat([table[i].long()[(positions[b:e] // block)] * block + positions[b:e] % block
+                                  for i, (_, _, b, e, _, _) in enumerate(rows)])
+        metadata = SimpleNamespace(block_table=table, block_size=block, slot_mapping=slot_mapping)
+        storage.ingest_prefill((cache_keys, cache_scales), metadata, plans, positions)
+        store.update({f"plans{step}": np.asarray([[o, b, e, d, s] for _, o, b, e, d, s in rows], np.int64),
+                      f"requests{step}": np.frombuffer("".join(r for r, *_ in rows).encode(), np.uint8),
+                      f"positions{step}": positions.numpy(), f"slot_mapping{step}": slot_mapping.numpy(),
+                      f"after_keys{step}": storage.keys.numpy().copy(), f"after_scales{step}": storage.scales.numpy().copy(),
+                      f"tokens{step}": np.int64(tokens)})
+    np.savez_compressed(HERE / "ingest_prefill.npz", **store)
+
+
 def main():
+    """python tests/golden/make_golden.py REFERENCE_CHECKOUT [--only=NAME]  (or the checkout in $KVIP_REFERENCE)"""
+    import os
     arguments = [a for a in sys.argv[1:] if not a.startswith("--only=")]
     only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
-    reference = Path(arguments[0] if arguments else "/root/reference")
+    checkout = arguments[0] if arguments else os.environ.get("KVIP_REFERENCE")
+    if not checkout:
+        raise SystemExit(main.__doc__)
+    reference = Path(checkout)
     sys.path[:0] = [str(reference / "python"), str(reference / "tests/operators/lifetch/support")]
     import torch
     if only == ["page_updates"]:  # regenerate this fixture alone
         page_updates_fixture(torch)
+        return
+    if only == ["ingest_prefill"]:
+        ingest_prefill_fixture(torch)
         return
     import workloads
     from correctness import validate_topk
@@ -166,6 +211,7 @@ def main():
                         t1=stages[1][1], s1=stages[1][2])
 
     page_updates_fixture(torch)
+    ingest_prefill_fixture(torch)
 
     # ---- QueryInputs + paged Index ingest --------------------------------------------------------
     from kvip.adapters.vllm.index_import import VllmIndexCacheStorage

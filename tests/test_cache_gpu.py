@@ -167,8 +167,47 @@ def test_index_storage_ingest_decode_matches_reference(device):
     storage.ingest_decode(cache, metadata, inputs, inputs.row_owners)
     torch.cuda.synchronize()
     assert np.array_equal(inputs.metadata.cpu().numpy(), d["metadata"])
+    assert np.array_equal(inputs.query_ends.cpu().numpy(), d["query_ends"])
+    assert np.array_equal(inputs.block_table.cpu().numpy(), d["block_table"])
+    assert inputs.token_count == int(d["token_count"])
     assert np.array_equal(storage.keys.cpu().numpy(), d["after_keys"])
     assert np.array_equal(storage.scales.cpu().numpy(), d["after_scales"])
+
+
+def test_index_storage_ingest_prefill_matches_reference(device):
+    """IndexCacheStorage.ingest_prefill (one kvip_b200_ingest_spans launch per forward) against what the reference's
+    VllmIndexCacheStorage.ingest_prefill left on CPU (index_import.py:17-36) over two forwards of a mixed batch:
+    cached history restored once through the block table, then the forward's own rows."""
+    from types import SimpleNamespace
+
+    from kvip_b200 import RequestPlan
+    d = np.load(GOLDEN / "ingest_prefill.npz")
+    storage = IndexCacheStorage(torch, 5, 512, 256, device)
+    storage.keys.copy_(torch.from_numpy(d["before_keys"]))
+    storage.scales.copy_(torch.from_numpy(d["before_scales"]))
+    cache = (torch.from_numpy(d["cache_keys"]).to(device), torch.from_numpy(d["cache_scales"]).to(device))
+    table = torch.from_numpy(d["block_table"]).to(device)
+    for step in (0, 1):
+        names = bytes(d[f"requests{step}"]).decode()
+        plans = [RequestPlan(names[i], int(o), int(b), int(e), decode=bool(dec), start=int(s))
+                 for i, (o, b, e, dec, s) in enumerate(d[f"plans{step}"])]
+        storage.prepare(plans)
+        metadata = SimpleNamespace(block_table=table, block_size=int(d["block_size"]),
+                                   slot_mapping=torch.from_numpy(d[f"slot_mapping{step}"]).to(device))
+        storage.ingest_prefill(cache, metadata, plans, torch.from_numpy(d[f"positions{step}"]).to(device))
+        torch.cuda.synchronize()
+        assert np.array_equal(storage.keys.cpu().numpy(), d[f"after_keys{step}"]), step
+        assert np.array_equal(storage.scales.cpu().numpy(), d[f"after_scales{step}"]), step
+    assert int(storage.ingest_errors.item()) == 0
+    # a span that points outside the cache is skipped and counted, nothing is written out of range
+    bad = SimpleNamespace(block_table=table, block_size=128,
+                          slot_mapping=torch.full((4,), 1 << 40, dtype=torch.int64, device=device))
+    plan = [RequestPlan("z", 0, 0, 4, decode=False, start=0)]
+    storage.prepare(plan)
+    before = storage.keys.clone()
+    storage.ingest_prefill(cache, bad, plan, torch.arange(4, dtype=torch.int64, device=device))
+    torch.cuda.synchronize()
+    assert int(storage.ingest_errors.item()) == 4 and torch.equal(before, storage.keys)
 
 
 @pytest.mark.parametrize("name,mode", [("li_exact_fixture.npz", 1), ("li_exact_causal_fixture.npz", 1),

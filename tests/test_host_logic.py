@@ -87,33 +87,40 @@ def test_product_has_no_cpu_fallback():
             f"{path} must not reach into the oracle")
 
 
-def test_query_inputs_packing_matches_reference_golden():
-    """QueryInputs.prepare / bind_positions on CPU tensors against the metadata the reference produced
-    (python/kvip/adapters/vllm/inputs.py:73-126; tests/adapters/test_inputs.py)."""
-    from kvip_b200 import QueryInputs
+def test_query_slot_layout_matches_reference_golden():
+    """The host layout of a step (`slot_layout`, what QueryInputs.prepare uploads) against the metadata block the
+    reference produced (python/kvip/adapters/vllm/inputs.py:73-113; tests/adapters/test_inputs.py). The device
+    half (query ends, block table) is checked on the GPU against the same golden."""
+    from kvip_b200.inputs import QueryInputs, slot_layout
     d = np.load(GOLDEN / "ingest_decode.npz")
-    inputs = QueryInputs(torch, 3, torch.device("cpu"), pin_memory=False, history=512)
-    inputs.prepare(tuple(int(x) for x in d["counts"]), query_starts=tuple(int(x) for x in d["starts"]),
-                   query_owners=tuple(int(x) for x in d["owners"]))
-    ends = inputs.bind_positions(torch.from_numpy(d["positions"]))
-    assert np.array_equal(inputs.metadata.numpy(), d["metadata"])
-    assert np.array_equal(ends.numpy().reshape(-1), d["query_ends"])
-    assert np.array_equal(inputs.block_table.numpy(), d["block_table"])
-    assert inputs.token_count == int(d["token_count"])
-    with pytest.raises(ValueError):
-        inputs.prepare((5,))
-    with pytest.raises(ValueError):
-        QueryInputs(torch, 1, torch.device("cpu"), index_heads=48)
+    layout, tokens = slot_layout(tuple(int(x) for x in d["counts"]), batch=3,
+                                 query_starts=tuple(int(x) for x in d["starts"]),
+                                 query_owners=tuple(int(x) for x in d["owners"]))
+    assert np.array_equal(layout, d["metadata"]) and tokens == int(d["token_count"])
+    for bad in (dict(query_counts=(5,)), dict(query_counts=(1, 1, 1, 1)), dict(query_counts=(1,), query_starts=(-1,)),
+                dict(query_counts=(1, 2), query_starts=(0,)), dict(query_counts=(1,), query_owners=(1 << 31,)),
+                dict(query_counts=(1.0,))):
+        with pytest.raises(ValueError):
+            slot_layout(batch=3, **bad)
+    with pytest.raises(ValueError, match="CUDA"):   # the buffers live on the GPU: no CPU path
+        QueryInputs(torch, 1, torch.device("cpu"))
 
 
-def test_query_inputs_generalised_slots():
-    from kvip_b200 import QueryInputs
-    inputs = QueryInputs(torch, 4, torch.device("cpu"), pin_memory=False, history=256, queries=2)
-    inputs.prepare((2, 1, 0, 2), query_owners=(3, 1, 0, 2))
-    assert inputs.gather_indices.tolist() == [0, 1, 2, 0, 0, 0, 3, 4]
-    assert inputs.query_valid.tolist() == [1, 1, 1, 0, 0, 0, 1, 1]
-    assert inputs.unpack_indices.tolist()[:5] == [0, 1, 2, 6, 7] and inputs.output_valid.tolist() == [1] * 5 + [0] * 3
-    assert inputs.block_table[:, 0].tolist() == [6, 2, 0, 4]
+def test_query_slot_layout_generalised_slots():
+    from kvip_b200.inputs import slot_layout
+    layout, tokens = slot_layout((2, 1, 0, 2), batch=4, queries=2, query_owners=(3, 1, 0, 2))
+    assert tokens == 5
+    assert layout[0].tolist() == [0, 1, 2, 0, 0, 0, 3, 4]
+    assert layout[1].tolist() == [1, 1, 1, 0, 0, 0, 1, 1]
+    assert layout[2].tolist()[:5] == [0, 1, 2, 6, 7] and layout[3].tolist() == [1] * 5 + [0] * 3
+    assert layout[4].view(np.int32)[:4].tolist() == [3, 1, 0, 2]
+
+
+def test_committed_candidates_keep_the_committed_prefix_first():
+    from kvip_b200.inputs import committed_candidates
+    candidates = np.array([7, 2, 9, 4, 11, 0], dtype=np.int32)
+    assert committed_candidates(candidates, 16, 12) is candidates               # whole pool committed
+    assert committed_candidates(candidates, 5, 12).tolist() == [2, 4, 0, 1, 3, 7]   # inside, missing inside, rest; cut
 
 
 def test_partition_requests_balances_cost():

@@ -123,7 +123,8 @@ def test_li_tcgen05_ragged_query_slots_two_units(key_dtype, device):
 
 def test_li_bounded_wait_gives_up_and_reports(device):
     """Every wait inside the tensor-core kernel is bounded. With the test hook one key page of CTA 0 is never
-    loaded: the wait for it runs out (about a second of SM clock), the CTA leaves its pipeline in order, the
+    loaded: the wait for it runs out (the limit is a launch argument: 20 million cycles, about 10 ms, here), the CTA
+    leaves its pipeline in order, the
     kernel returns with KVIP_ERR_PIPELINE in the status word, and the next ordinary call on the same context
     is correct again."""
     case = workloads.li_case(seed=12, batch=2, queries=1, heads=64, len_lo=4000, len_hi=5000, key_dtype="fp8",
@@ -131,7 +132,7 @@ def test_li_bounded_wait_gives_up_and_reports(device):
     t = workloads.to_torch(case, device)
     args = (t["query"], t["keys"], t["weights"], t["query_scale"], t["key_scale"], t["key_lengths"], t["query_ends"],
             t["block_table"])
-    _, status = ops.li_score(*args, ctas=2, withhold_tile=3)
+    _, status = ops.li_score(*args, ctas=2, withhold_tile=3, wait_kilocycles=20000)
     torch.cuda.synchronize()
     assert int(status.item()) & 32, "the kernel must report the abandoned wait"
     expected, _ = _li(case, device, simt=True)
