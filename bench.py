@@ -120,7 +120,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     from kvip_b200 import _lib, ops
-    from kvip_b200.synthetic import DecodePipeline
+    from decode_harness import DecodePipeline
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -672,7 +672,7 @@ def run_lidu(args):
     import torch
 
     from kvip_b200 import lidu
-    from kvip_b200.synthetic import lidu_state
+    from decode_harness import lidu_state
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
@@ -747,7 +747,7 @@ def run_miss_prefetch(args):
     windows cost (extra score launches) and what they move off the post-score fetch."""
     import torch
 
-    from kvip_b200.synthetic import DecodePipeline
+    from decode_harness import DecodePipeline
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)

@@ -1,7 +1,9 @@
-"""Seeded synthetic decode workloads with the shapes and value distributions of the benchmark
+"""Harness of bench.py, the smoke check and the end-to-end tests; not part of the `kvip_b200` package.
+
+Seeded synthetic decode workloads with the shapes and value distributions of the benchmark
 configs, built directly in device memory, and a `DecodePipeline` that wires the public objects
 (IndexCacheStorage, LIFetchWorkspace, HostKVPool, CudaBinding, IndexUpdate, SlotLRU, LIFetch) the way
-a serving adapter would. Used by bench.py, the smoke check and the end-to-end tests.
+a serving adapter would.
 
 The reference measures on captured decode traces and a calibrated generator that are not shipped;
 these inputs stand in for them: q_I / k_I ~ N(0,1) (bf16, or FP8 e4m3 with per-token key scales and
@@ -10,10 +12,10 @@ context lengths uniform in [len_lo, len_hi], KV rows that identify (owner, token
 import numpy as np
 import torch
 
-from . import _lib
-from .cache.index_storage import IndexCacheStorage
-from .cache.lru import SlotLRU
-from .operators.lifetch import CudaBinding, HostKVPool, IndexUpdate, LIFetch, LIFetchWorkspace
+from kvip_b200 import _lib
+from kvip_b200.cache.index_storage import IndexCacheStorage
+from kvip_b200.cache.lru import SlotLRU
+from kvip_b200.operators.lifetch import CudaBinding, HostKVPool, IndexUpdate, LIFetch, LIFetchWorkspace
 
 TOPK = 2048
 
@@ -71,7 +73,7 @@ class DecodePipeline:
                  weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
                  score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0,
                  overlap_lru=True, prefetch_limit=0, prefetch_windows=3, prefetch_ctas=0,
-                 prefetch_last_window=False):
+                 prefetch_last_window=False, tail_slots=0, head_sum=_lib.HEAD_SUM_AUTO):
         self.device = device = torch.device(device)
         self.batch, self.queries, self.heads, self.history, self.resident = batch, queries, heads, history, resident
         self.token_bytes, self.key_dtype = token_bytes, key_dtype
@@ -111,7 +113,10 @@ class DecodePipeline:
         self.workspace.key_lengths.copy_(torch.from_numpy(self.lengths))
         self.new_queries(seed)
         # ---- KV pools ----------------------------------------------------------------------------------
-        self.output_stride = resident
+        # ABC tail: `tail_slots` dedicated slots per owner behind the hot ones, bounds [B, 2] set by the caller
+        self.tail_slots = tail_slots
+        self.output_stride = resident + tail_slots
+        self.tail_bounds = torch.zeros((batch, 2), dtype=torch.int32, device=device) if tail_slots else None
         self.pool_hbm = torch.zeros((owners * self.output_stride, token_bytes), dtype=torch.uint8, device=device)
         self.host_pool = None
         source = None
@@ -141,7 +146,8 @@ class DecodePipeline:
             resident=resident, query_ends=inputs.query_ends, hot_valid=self.storage.hot_valid,
             token_addresses=self.storage.addresses, row_owners=inputs.row_owners, scratch=self.workspace.scratch,
             token_bytes=token_bytes, queries=queries, score_mode=score_mode, gather_output=self.gather_out,
-            li_variant=li_variant, source=source, sm_count=sm_count)
+            li_variant=li_variant, source=source, sm_count=sm_count, tail_bounds=self.tail_bounds,
+            output_stride=self.output_stride, head_sum=head_sum)
         self.update = IndexUpdate(
             torch, keys=self.storage.keys, scales=self.storage.scales, addresses=self.storage.addresses,
             logical_ids=self.storage.logical_ids, row_owners=inputs.row_owners, rotating=self.rotating,

@@ -7,7 +7,7 @@ import torch
 import kvip_oracle as oracle
 import oracle_c
 from kvip_b200 import _lib
-from kvip_b200.synthetic import DecodePipeline, payload_rows
+from decode_harness import DecodePipeline, payload_rows
 
 pytestmark = pytest.mark.gpu
 TOPK = 2048
@@ -36,12 +36,14 @@ def oracle_step(p, before, scores):
     host = p.host_pool.flat.numpy() if p.host_pool is not None else p.source.cpu().numpy().reshape(-1)
     logical_out = np.full((batch * queries, TOPK), -1, np.int32)
     slot_out = np.full((batch * queries, TOPK), -1, np.int32)
-    reads = []
+    reads, posts = [], []
     for b in range(batch):
         owner = int(owners[b])
+        tail = None if p.tail_bounds is None else p.tail_bounds[b].cpu().numpy()
         ref = oracle.resolve_request(topk[b], state["hot_valid"][owner], state["reserved"][b], state["lru_slots"][b],
-                                     history, resident)
+                                     history, resident, tail_bounds=tail, output_stride=p.output_stride, request=b)
         assert ref["error"] == 0
+        posts.append(ref["final_posts"])
         for q in range(queries):
             live = topk[b, q] >= 0
             logical_out[b * queries + q, live] = state["logical"][owner][topk[b, q][live]]
@@ -55,6 +57,7 @@ def oracle_step(p, before, scores):
                              owner * p.output_stride + ref["events_dst"], owner, p.output_stride, resident,
                              p.token_bytes)
         reads.append(ref["total"])
+    state["final_posts"] = np.stack(posts)
     gathered = oracle.gather(state["pool"], slot_out, owners, queries, p.output_stride)
     # LRU feedback: touched slots move to the tail in ascending slot order
     for b in range(batch):
@@ -133,6 +136,8 @@ def test_forward_matches_oracle_over_steps(config, device):
             assert np.array_equal(after["order"][:, :p.resident], state["order"][:, :p.resident])
             assert np.array_equal(p.gather_out.cpu().numpy(), gathered)
             assert np.array_equal(p.rotating.query_counts[:, 4].cpu().numpy(), np.asarray(reads))
+            assert np.array_equal(p.rotating.final_posts.cpu().numpy().view(np.uint32).reshape(p.batch, 4, 32),
+                                  state["final_posts"]), "final posts differ from the restatement"
             # fetched bytes identify the selected logical token of the right owner
             owners = p.workspace.inputs.row_owners.cpu().numpy()
             got = p.gather_out.cpu().numpy()
@@ -146,6 +151,93 @@ def test_forward_matches_oracle_over_steps(config, device):
         assert sum(total_reads[2]) < sum(total_reads[0]), "a repeated query must mostly hit the resident pool"
     finally:
         p.close()
+
+
+def test_forward_with_abc_tail(device):
+    """The fused call with ABC tail bounds bound (reference binding.py:150-164, cache_metadata.h:22-26, 100-105): the
+    last tokens of every request live in a ring of dedicated slots behind the hot ones. Those positions are served
+    from the ring (location resident + p % ring), never fetched and never evicted; everything else behaves as
+    without a tail. Checked against the restatement over three steps, and by the fetched bytes themselves."""
+    ring = 512
+    config = dict(batch=3, queries=2, heads=64, history=12288, resident=4096, len_lo=9000, len_hi=12288,
+                  key_dtype="fp8", weight_dtype="bf16", token_bytes=1152, seed=3)
+    p = DecodePipeline(device, fill_payload=True, tail_slots=ring, **config)
+    try:
+        owners = p.workspace.inputs.row_owners.cpu().numpy()
+        bounds = np.zeros((p.batch, 2), np.int32)
+        for b in range(p.batch):
+            length, owner = int(p.lengths[b]), int(owners[b])
+            bounds[b] = (length - 300 - 40 * b, length)     # the newest 300..380 tokens are uncommitted
+            tail = np.arange(bounds[b, 0], bounds[b, 1])
+            # the owner of the ring wrote these rows when the tokens were generated (update_abc's slot rule)
+            rows = torch.from_numpy(payload_rows(owner, tail, p.token_bytes)).to(device)
+            slots = torch.from_numpy(owner * p.output_stride + p.resident + tail % ring).to(device)
+            p.pool_hbm[slots] = rows
+            # scores of recent tokens are large in practice; here the host pool simply has no valid copy of them
+            p.host_pool.tensor[owner, bounds[b, 0]:bounds[b, 1]] = 0xEE
+        p.tail_bounds.copy_(torch.from_numpy(bounds))
+        in_tail_total = 0
+        for step in range(3):
+            if step:
+                p.new_queries(config["seed"] + 7 * step)
+            before = snapshot(p)
+            p.step()
+            torch.cuda.synchronize()
+            assert int(p.forward.li_status.item()) == 0 and int(p.update.status.abs().sum()) == 0
+            scores = p.workspace.scores.cpu().numpy()
+            state, topk, logical_out, slot_out, gathered, reads = oracle_step(p, before, scores)
+            assert np.array_equal(p.workspace.topk.cpu().numpy(), topk)
+            assert np.array_equal(p.update.slot_output.cpu().numpy().reshape(-1, TOPK), slot_out)
+            assert np.array_equal(p.update.logical_output.cpu().numpy().reshape(-1, TOPK), logical_out)
+            after = snapshot(p)
+            for name in ("keys", "scales", "addresses", "logical", "hot_valid", "pool", "lru_slots", "reserved"):
+                assert np.array_equal(after[name], state[name]), (step, name)
+            assert np.array_equal(p.gather_out.cpu().numpy(), gathered)
+            got = p.gather_out.cpu().numpy()
+            for t in range(p.batch * p.queries):
+                b = t // p.queries
+                positions = topk.reshape(-1, TOPK)[t]
+                live = positions >= 0
+                in_tail = live & (positions >= bounds[b, 0]) & (positions < bounds[b, 1])
+                in_tail_total += int(in_tail.sum())
+                assert (slot_out[t][in_tail] == p.resident + positions[in_tail] % ring).all()
+                assert (slot_out[t][live & ~in_tail] < p.resident).all()
+                want = payload_rows(int(owners[b]), logical_out[t][live], p.token_bytes)
+                assert np.array_equal(got[t][live], want), "tail rows must come from the ring, not from the host pool"
+        assert in_tail_total > 0, "the case must select tail positions"
+    finally:
+        p.close()
+
+
+def test_stage_times_and_option_bits(device):
+    """KVIP_OPTION_DIAGNOSTICS makes the call stamp the GPU timer between its stages (reference: the `times`
+    buffer, streaming.cpp:107-108, 390-465); the reference's scheduling-hint bits are accepted and change nothing;
+    its legacy-layout bit is refused; the outputs do not depend on any of them."""
+    config = dict(batch=2, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=9, host_pool=False, fill_payload=True)
+    plain, timed = DecodePipeline(device, **config), DecodePipeline(device, **config)
+    library = _lib.load_library()
+    assert library.kvip_b200_abi_version() == 2
+    timed.forward.set_options(diagnostics=True)
+    timed.forward._options |= _lib.OPTION_SCHEDULING_HINTS      # parallel finalize + prepare metadata + UBmem overlap
+    timed.forward._options_word[0] = timed.forward._options
+    before = library.kvip_b200_launch_count()
+    timed.step()
+    assert library.kvip_b200_launch_count() - before == 8 + 8   # the eight kernels of a step + eight stamps
+    plain.step()
+    torch.cuda.synchronize()
+    assert torch.equal(plain.update.outputs, timed.update.outputs) and torch.equal(plain.gather_out, timed.gather_out)
+    times = timed.forward.stage_times()
+    assert set(times) == set(_lib.TIME_STAGES) | {"total"}
+    assert all(value >= 0 for value in times.values()) and times["li_score"] > 0 and times["gather"] > 0
+    assert abs(sum(times[name] for name in _lib.TIME_STAGES) - times["total"]) < 1e-6
+    assert 1 < times["total"] < 1e6, "a small step takes microseconds to milliseconds"
+    assert int(plain.forward.times.abs().sum()) == 0, "without the option nothing is stamped"
+    plain.forward._options_word[0] = plain.forward._options | _lib.OPTION_LEGACY_LAYOUT
+    code = plain.forward.function(plain.rotating.bindings.data_ptr(), plain.update.bindings.data_ptr(),
+                                  plain.forward.workspace.data_ptr(), None, plain.forward.shape_pointer, 2)
+    assert code == _lib.BAD_ARGUMENT and "legacy" in _lib.last_error(library)
+    plain.forward._options_word[0] = plain.forward._options
 
 
 def test_forward_is_graph_capturable_and_allocation_free(device):
@@ -358,6 +450,80 @@ def test_full_size_step_properties(device):
     torch.cuda.synchronize()
     assert int(p.rotating.query_counts[:, 4].sum()) == 0, "a repeated query must find every row resident"
     assert torch.equal(torch.sort(p.update.logical_output, dim=-1).values, torch.sort(first_logical, dim=-1).values)
+
+
+def test_full_size_steps_with_evictions_from_the_host_pool(device):
+    """Benchmark context length (131072 keys, FP8, 1152-byte rows) with misses served from the pinned host pool and a
+    resident pool small enough (4096 slots) that rows are evicted and fetched again: independent queries in steps
+    1-3 fill the pool and push the first step's rows out, step 4 repeats the first step's queries. After EVERY step
+    the invariants the reference's harness checks (execution.py:2102-2131, 2183-2198, 2216-2224) must hold: the
+    Index rows stay a joint permutation, every selected token sits in a distinct valid slot whose pool row is that
+    token's host row, the dense gather returns those rows, statuses are zero."""
+    batch, history, resident = 8, 131072, 4096
+    p = DecodePipeline(device, batch=batch, queries=1, heads=64, history=history, resident=resident, len_lo=100000,
+                       len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152, seed=6, host_pool=True,
+                       fill_payload=True)
+    try:
+        keys_before, scales_before = p.storage.keys.clone(), p.storage.scales.clone()
+        identity = torch.arange(history, device=device)
+        owners = p.row_owner_list
+        lengths = torch.from_numpy(p.lengths).to(device)
+        reads = []
+        for step, seed in enumerate((6, 60, 600, 6)):
+            p.new_queries(seed)
+            p.step()
+            torch.cuda.synchronize()
+            assert int(p.forward.li_status.item()) == 0 and int(p.update.status.abs().sum()) == 0
+            assert int(p.rotating.row_status[:, :3].abs().sum()) == 0
+            reads.append(int(p.rotating.query_counts[:, 4].sum()))
+            topk = p.workspace.topk.view(-1, 2048)
+            for row in range(batch):
+                owner, n = owners[row], int(lengths[row])
+                values = p.workspace.scores[row, :n]
+                picked = topk[row].long()
+                assert torch.equal(torch.sort(values[picked], descending=True).values, torch.topk(values, 2048).values)
+                ids = p.storage.logical_ids[owner]
+                assert torch.equal(torch.sort(ids).values, identity), (step, row)
+                assert torch.equal(p.storage.keys[owner], keys_before[owner][ids])
+                assert torch.equal(p.storage.scales[owner], scales_before[owner][ids])
+                assert torch.equal(p.storage.addresses[owner], (ids + owner * history) * p.token_bytes)
+                logical = p.update.logical_output[row, 0].long()
+                slots = p.update.slot_output[row, 0].long()
+                assert int(slots.min()) >= 0 and int(slots.max()) < resident and slots.unique().numel() == 2048
+                assert bool((p.storage.hot_valid[owner][slots] == 1).all())
+                assert torch.equal(ids[slots], logical), "slot p must hold Index row p"
+                expected_rows = p.host_pool.tensor[owner][logical.cpu()]
+                assert torch.equal(p.pool_hbm[owner * p.output_stride + slots].cpu(), expected_rows), (step, row)
+                assert torch.equal(p.gather_out[row].cpu(), expected_rows)
+                # every valid hot slot (not only the selected ones) still holds the row its Index position names
+                valid = torch.nonzero(p.storage.hot_valid[owner]).view(-1)
+                sample = valid[:: max(1, valid.numel() // 256)]
+                assert torch.equal(p.pool_hbm[owner * p.output_stride + sample].cpu(),
+                                   p.host_pool.tensor[owner][ids[sample].cpu()])
+        assert reads[0] == batch * 2048, "an empty pool misses everything"
+        assert reads[2] > 0 and int(p.storage.hot_valid.sum()) <= batch * resident
+        # step 3 took the least recently used slots, i.e. step 1's rows: the repeated query fetches them again
+        assert batch * 1024 < reads[3] <= batch * 2048, "the repeated query must find its rows evicted"
+    finally:
+        p.close()
+
+
+def test_two_devices_in_one_process(device):
+    """Function attributes (the dynamic shared-memory limits) and the SM count are kept per device: a process that
+    drives a second GPU gets the same results there. Skipped on a one-GPU box."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    config = dict(batch=2, queries=2, heads=64, history=8192, resident=4096, len_lo=6000, len_hi=8192, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=13, host_pool=False, fill_payload=True)
+    results = []
+    for index in (0, 1):
+        with torch.cuda.device(index):
+            p = DecodePipeline(torch.device("cuda", index), **config)
+            p.step()
+            torch.cuda.synchronize()
+            assert int(p.forward.li_status.item()) == 0 and int(p.update.status.abs().sum()) == 0
+            results.append((p.update.outputs.cpu(), p.gather_out.cpu()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
 
 
 def test_forward_rejects_mismatched_shape(device):

@@ -75,6 +75,32 @@ def test_stage_entry_points_reject_null_arguments(library):
     assert b"null" in library.kvip_b200_last_error()
 
 
+def test_option_bits_do_not_collide_with_the_reference(library):
+    """The reference's option word (python/kvip/operators/lifetch/streaming.py:133-146) owns 0x80000000 diagnostics,
+    0x40000000 deferred fetch, 0x20000000 legacy layout, 0x10000000 parallel finalize, 0x08000000 prepare metadata,
+    0x04000000 UBmem overlap, bits 16-18 workers and bits 0-15 the prefetch limit. The bits this build adds lie
+    elsewhere; the legacy layout is refused before anything is enqueued (checked here without a device)."""
+    reference_bits = 0xFC000000 | (7 << 16) | 0xFFFF
+    added = (_lib.OPTION_SELECT_ONLY, _lib.OPTION_COMMIT_ONLY, _lib.OPTION_SCORES_READY)
+    assert all(bit & reference_bits == 0 for bit in added) and len({*added}) == 3
+    assert _lib.OPTION_SCHEDULING_HINTS == 0x10000000 | 0x08000000 | 0x04000000
+    assert library.kvip_b200_abi_version() == 2
+    shape = _lib.RuntimeShape.prepare(library, batch=2, history=8192, resident=4096, indexHeads=64, queries=1, tokenBytes=1152)
+    context = _lib.Context(shape=shape)
+    workspace = _lib.Workspace(history=8192, resident=4096, max_events=10240, options=_lib.OPTION_LEGACY_LAYOUT | (2 << 16))
+    bindings = (ctypes.c_uint64 * 16)(*([0] * 14), ctypes.addressof(context), ctypes.addressof(workspace))
+    update = (ctypes.c_int64 * 28)()
+    update[24], update[25] = 8192, 4096
+    code = library.kvip_lifetch_streaming_forward(ctypes.addressof(bindings), ctypes.addressof(update),
+                                                  ctypes.addressof(workspace), None, ctypes.byref(shape), 2)
+    assert code == _lib.BAD_ARGUMENT and b"legacy" in library.kvip_b200_last_error()
+    # with a scheduling hint instead, the call passes the option check and stops at the first unbound operand
+    workspace.options = _lib.OPTION_SCHEDULING_HINTS | (2 << 16)
+    code = library.kvip_lifetch_streaming_forward(ctypes.addressof(bindings), ctypes.addressof(update),
+                                                  ctypes.addressof(workspace), None, ctypes.byref(shape), 2)
+    assert code == _lib.BAD_ARGUMENT and b"unbound" in library.kvip_b200_last_error()
+
+
 def test_product_has_no_cpu_fallback():
     from kvip_b200 import ops
     with pytest.raises(ValueError, match="CUDA"):

@@ -381,6 +381,10 @@ def test_resolver_matches_oracle(spec, device):
         assert np.array_equal(state.change_slots[b].cpu().numpy(), ref["change_slots"])
         assert np.array_equal(state.fetch_sources[b, :n].cpu().numpy(), addresses[b][ref["events_src"]])
         assert np.array_equal(state.fetch_destinations[b, :n].cpu().numpy(), b * resident + ref["events_dst"])
+        posts = state.final_posts.view(case["batch"], 4, 32)[b].cpu().numpy().view(np.uint32)
+        expected_posts = oracle.resolve_request(case["selected"][b], case["hot_valid"][b], case["reserved_hot"][b],
+                                                case["lru_slots"][b], history, resident, request=b)["final_posts"]
+        assert np.array_equal(posts, expected_posts), "final posts (count, first descriptor, error) differ"
         q = case["queries"]
         assert np.array_equal(state.slot_output.view(-1, q, TOPK)[b].cpu().numpy(), ref["locations"])
         assert np.array_equal(state.logical_output.view(-1, q, TOPK)[b].cpu().numpy(),
@@ -407,6 +411,122 @@ def test_resolver_padding_rows_and_range_error(device):
     assert (state.locations[0, 2:].cpu().numpy() == -1).all()
     assert int(state.row_status[1, 0]) == oracle.ERR_TOKEN_RANGE
     assert int(state.query_counts[1, 4]) == 0
+
+
+def test_resolver_abc_tail_matches_oracle(device):
+    """ABC tail (reference cache_metadata.h:22-26, 100-105; prefetch.h:26-44): positions [begin, end) of a request
+    live in the ring of output_stride - resident dedicated slots. They are never hot by position, never misses and
+    never victims; their location is resident + p % ring while the ring holds them, and a tail position beyond
+    the ring is resolved like a cold one. Bit-exact against the restatement, plus the properties themselves."""
+    batch, queries, history, resident, ring = 3, 4, 16384, 4096, 512
+    case = workloads.resolver_case(seed=21, batch=batch, queries=queries, history=history, resident=resident)
+    rng = np.random.default_rng(5)
+    # request 0: tail of 300 cold positions; request 1: a tail that reaches below `resident` and is longer than the
+    # ring; request 2: empty tail. Every request selects some tail positions in every query.
+    bounds = np.array([[9000, 9300], [3900, 4700], [12000, 12000]], dtype=np.int32)
+    for b in range(batch):
+        lo, hi = bounds[b]
+        if hi > lo:
+            for q in range(queries):
+                row = case["selected"][b, q]
+                tail = rng.choice(np.arange(lo, hi), 64, replace=False)
+                fresh = tail[~np.isin(tail, row)]
+                row[rng.choice(TOPK, len(fresh), replace=False)] = fresh
+    logical = np.stack([np.arange(history) for _ in range(batch)]).astype(np.int64)
+    addresses = logical * 1152
+    state = ops.ResolveState(batch, queries, device)
+    dev = {k: torch.from_numpy(v).to(device) for k, v in case.items() if isinstance(v, np.ndarray)}
+    ops.resolve(dev["selected"], dev["hot_valid"], dev["reserved_hot"], dev["lru_slots"], torch.from_numpy(logical).to(device),
+                torch.from_numpy(addresses).to(device), state, history=history, resident=resident,
+                output_stride=resident + ring, tail_bounds=torch.from_numpy(bounds).to(device))
+    torch.cuda.synchronize()
+    for b in range(batch):
+        ref = oracle.resolve_request(case["selected"][b], case["hot_valid"][b], case["reserved_hot"][b],
+                                     case["lru_slots"][b], history, resident, tail_bounds=bounds[b],
+                                     output_stride=resident + ring, request=b)
+        assert ref["error"] == 0 and int(state.row_status[b, 0]) == 0
+        loc = state.locations[b].cpu().numpy()
+        n = ref["total"]
+        assert np.array_equal(loc, ref["locations"])
+        assert np.array_equal(state.events_src[b, :n].cpu().numpy(), ref["events_src"])
+        assert np.array_equal(state.events_dst[b, :n].cpu().numpy(), ref["events_dst"])
+        assert np.array_equal(state.final_posts.view(batch, 4, 32)[b].cpu().numpy().view(np.uint32), ref["final_posts"])
+        sel = case["selected"][b]
+        lo, hi = bounds[b]
+        in_ring = (sel >= lo) & (sel < hi) & (sel - lo < ring)
+        assert np.array_equal(loc[in_ring], resident + sel[in_ring] % ring)
+        assert (loc[~in_ring] < resident).all() and (loc[~in_ring] >= 0).all()
+        events = set(ref["events_src"].tolist())
+        assert not events & set(sel[in_ring].tolist()), "a ring position must not be fetched"
+        assert (ref["events_dst"] < resident).all(), "ring slots are never victims"
+        if b == 1:  # tail positions below `resident` are not hot hits even where hot_valid says so
+            low = in_ring & (sel < resident)
+            assert low.any() and (loc[low] >= resident).all()
+            beyond = (sel >= lo + ring) & (sel < hi)
+            assert beyond.any() and (loc[beyond] < resident).all(), "beyond the ring: resolved like a cold position"
+    with pytest.raises(ValueError):  # fewer than 384 dedicated slots (reference binding.py:163-164)
+        ops.resolve(dev["selected"], dev["hot_valid"], dev["reserved_hot"], dev["lru_slots"], torch.from_numpy(logical).to(device),
+                    torch.from_numpy(addresses).to(device), state, history=history, resident=resident,
+                    output_stride=resident + 256, tail_bounds=torch.from_numpy(bounds).to(device))
+
+
+def test_resolver_rejects_a_source_outside_the_pool(device):
+    """A missing row whose source address lies outside the miss source fails its request in the resolver, before
+    any Index row moves (the reference range-checks the same descriptors, streaming.cpp:399-400): status
+    KVIP_ERR_SOURCE, no descriptors, outputs -1; the other request is untouched."""
+    case = workloads.resolver_case(seed=31, batch=2, queries=2, history=8192, resident=4096)
+    history, resident = 8192, 4096
+    logical = np.stack([np.arange(history) for _ in range(2)]).astype(np.int64)
+    addresses = logical * 1152
+    cold = case["selected"][1][case["selected"][1] >= resident][0]
+    addresses[1, cold] = history * 1152          # one row past the end of the source
+    state = ops.ResolveState(2, 2, device)
+    dev = {k: torch.from_numpy(v).to(device) for k, v in case.items() if isinstance(v, np.ndarray)}
+    ops.resolve(dev["selected"], dev["hot_valid"], dev["reserved_hot"], dev["lru_slots"], torch.from_numpy(logical).to(device),
+                torch.from_numpy(addresses).to(device), state, history=history, resident=resident,
+                source_bytes=history * 1152, token_bytes=1152)
+    torch.cuda.synchronize()
+    for b in range(2):
+        ref = oracle.resolve_request(case["selected"][b], case["hot_valid"][b], case["reserved_hot"][b],
+                                     case["lru_slots"][b], history, resident, addresses=addresses[b],
+                                     source_bytes=history * 1152, token_bytes=1152, request=b)
+        assert int(state.row_status[b, 0]) == ref["error"] == (oracle.ERR_SOURCE if b == 1 else 0)
+        assert int(state.query_counts[b, 4]) == ref["total"]
+        assert np.array_equal(state.final_posts.view(2, 4, 32)[b].cpu().numpy().view(np.uint32), ref["final_posts"])
+    assert (state.slot_output.view(2, 2, TOPK)[1].cpu().numpy() == -1).all()
+    assert np.array_equal(state.locations[0].cpu().numpy(),
+                          oracle.resolve_request(case["selected"][0], case["hot_valid"][0], case["reserved_hot"][0],
+                                                 case["lru_slots"][0], history, resident)["locations"])
+
+
+def test_fetch_bad_descriptor_revokes_residency(device):
+    """A descriptor that fails the fetch's own range check is skipped, and its destination slot must not keep the
+    residency of the row it evicted (the Index row of the new token already sits there): hot_valid of the slot is
+    cleared, row_status[2] is set and the update status gets code 4 (reference CompleteEarlyUpdate,
+    index_cache_update.h:6-20). The other descriptors of the request still land."""
+    batch, resident, token_bytes, rows = 2, 4096, 1152, 32
+    state = ops.ResolveState(batch, 1, device)
+    source = torch.from_numpy(workloads.payload(0, np.arange(256), token_bytes)).to(device)
+    pool = torch.zeros((batch * resident, token_bytes), dtype=torch.uint8, device=device)
+    hot_valid = torch.ones((batch, resident), dtype=torch.int32, device=device)
+    status = torch.zeros(batch, dtype=torch.int32, device=device)
+    tokens = torch.arange(rows, device=device)
+    for b in range(batch):
+        state.fetch_sources[b, :rows] = (tokens + 10 * b) * token_bytes
+        state.fetch_destinations[b, :rows] = (b * resident + 100 + tokens).int()
+        state.query_counts[b, 4] = rows
+    state.fetch_sources[1, 7] = 256 * token_bytes     # one row past the end of the source
+    ops.fetch(source, source.numel(), pool, hot_valid, state, resident=resident, output_stride=resident,
+              token_bytes=token_bytes, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 4] and int(state.row_status[1, 2]) == 1 and int(state.row_status[0, 2]) == 0
+    valid = hot_valid.cpu().numpy()
+    assert valid[1, 107] == 0 and valid[1].sum() == resident - 1 and valid[0].all()
+    got = pool.cpu().numpy()
+    for b in range(batch):
+        for i in range(rows):
+            expected = np.zeros(token_bytes, np.uint8) if (b, i) == (1, 7) else workloads.payload(0, [i + 10 * b], token_bytes)[0]
+            assert np.array_equal(got[b * resident + 100 + i], expected), (b, i)
 
 
 def _index_state(batch, history, resident, seed, bf16=False):

@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle_c
 from kvip_b200 import _lib
 
 pytestmark = pytest.mark.gpu
@@ -58,6 +59,8 @@ def test_static_scratch_topk_matches_the_allocating_entry_point(device):
         assert torch.cuda.mem_get_info(device)[0] == free_before
         assert torch.cuda.memory_stats(device)["allocation.all.allocated"] == count_before
         assert torch.equal(static_out, expected) and torch.equal(static_scores, expected_scores)
+        # and both are the oracle's selection (C restatement of the canonical order)
+        assert np.array_equal(static_out.cpu().numpy(), oracle_c.topk(scores_np, lengths_np, ends.cpu().numpy()))
 
 
 def test_static_scratch_topk_rejects_more_rows_than_it_holds(device):
