@@ -115,6 +115,21 @@ def time_region(torch, stream, fn, steps):
     return start.elapsed_time(stop) / 1e3
 
 
+def time_blocks(torch, stream, fn, steps, first_block_s, *, least=10, most=200, target_s=1.0):
+    """Back-to-back blocks of `steps` calls, each between its own pair of CUDA events. A block of 20 replays lasts a
+    few milliseconds, less than one sample of the clock monitor and short enough for one stray clock step to move
+    it: enough blocks are timed to fill about a second, and the caller reports their median, minimum and maximum."""
+    count = max(least, min(most, int(target_s / max(first_block_s, 1e-6)) + 1))
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(count + 1)]
+    marks[0].record(stream)
+    for block in range(count):
+        for _ in range(steps):
+            fn()
+        marks[block + 1].record(stream)
+    marks[-1].synchronize()
+    return [marks[i].elapsed_time(marks[i + 1]) / 1e3 for i in range(count)]
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -181,13 +196,22 @@ def run_ours(args):
                     graph.replay()
                 stream.synchronize()
 
+        first_block = time_region(torch, stream, graph.replay, args.steps)
         with ClockSampler(local) as clocks:
-            soak(0.7)
+            soak(0.3)
             barrier()
-            elapsed = time_region(torch, stream, graph.replay, args.steps)
+            block_seconds = time_blocks(torch, stream, graph.replay, args.steps, first_block)
             barrier()
-            soak(0.7)
+            soak(0.3)
         steady_reads = int(p.rotating.query_counts[:, 4].sum().item())
+        blocks = torch.tensor(block_seconds, dtype=torch.float64, device=device)
+        if world > 1:   # every block as slow as its slowest rank (all ranks time the same number of blocks)
+            counts = torch.tensor([len(block_seconds)], dtype=torch.int64, device=device)
+            dist.all_reduce(counts, op=dist.ReduceOp.MIN)
+            blocks = blocks[: int(counts.item())].contiguous()
+            dist.all_reduce(blocks, op=dist.ReduceOp.MAX)
+        block_seconds = sorted(blocks.tolist())
+        elapsed = block_seconds[len(block_seconds) // 2]   # the median block of `steps` replays
 
         # ---- per-stage device time (each stage alone, K launches, inputs larger than L2) ------------
         inputs, s, r, ws = p.workspace.inputs, p.storage, p.rotating, p.workspace
@@ -270,10 +294,10 @@ def run_ours(args):
         if world == 1 and not args.no_miss_path:
             miss_path = measure_miss_path(torch, ops, p, stream, args)
 
-    worst = torch.tensor([elapsed, e2e_elapsed, serial_elapsed], dtype=torch.float64, device=device)
+    worst = torch.tensor([e2e_elapsed, serial_elapsed], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed, serial_elapsed = (float(x) for x in worst.tolist())
+    e2e_elapsed, serial_elapsed = (float(x) for x in worst.tolist())
     hbm_peak, peak_kind = peaks()
     key_bytes = 1 if p.key_dtype == "fp8" else 2
     li_bytes = li_algorithmic_bytes(p.lengths, p.queries, p.heads, key_bytes)
@@ -284,12 +308,22 @@ def run_ours(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32",
         "data": "synthetic",
+        "blocks": {"count": len(block_seconds), "steps_per_block": args.steps, "reported": "median block",
+                   "min_ms_per_step": block_seconds[0] / args.steps * 1e3,
+                   "max_ms_per_step": block_seconds[-1] / args.steps * 1e3,
+                   # time x clock: comparable between a box at full clock and one under its power cap
+                   "median_ms_x_sm_mhz": (elapsed / args.steps * 1e3 * clocks.result["sm_mhz"]
+                                          if clocks.result.get("sm_mhz") else None)},
         "config": {"workload": args.workload, "batch_per_gpu": p.batch, "queries_per_request": p.queries,
                    "context": int(p.lengths.max()), "index_heads": p.heads, "topk": 2048,
                    "resident_slots": p.resident, "token_bytes": p.token_bytes, "cuda_graph": True,
                    "partition": "by request, no collective",
                    "l2": "inputs larger than L2 (keys %.0f MB per step)" % (li_bytes / 1e6),
-                   "miss_source": miss_source},
+                   "miss_source": miss_source,
+                   "steady_state": "the captured step is replayed with fixed queries: after warm-up every selected row "
+                                   "is resident, the timed steps fetch nothing from the host pool and 'Fetch' is the "
+                                   "dense gather of 2048 resident rows per query; value_with_misses is the same step "
+                                   "with drifting queries"},
         "e2e": {"value": world * tokens * args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3,
                 "api": "HostDecodeLoop.step: copies of steps i-1 / i+1 overlap the kernels of step i",
@@ -303,7 +337,8 @@ def run_ours(args):
                      # pages, 1.014 x its algorithmic bytes), scaled by the pages one launch of this workload streams
                      "traffic": (int(1.014 * li_bytes) if p.key_dtype == "fp8" and args.workload.startswith("decode_128k")
                                  else None),
-                     "traffic_source": "profiles/li_score_tcgen05__decode_128k_b8.md, scaled by pages per launch",
+                     "traffic_kind": "scaled, not measured on this workload: DRAM bytes of an ncu capture of the "
+                                     "8-request case of the same kernel, times the ratio of key pages per launch",
                      "step_frac": step_bytes / stages["step_graph"] / 1e9 / hbm_peak},
         "stages_us": {k: v * 1e6 for k, v in stages.items()},
         "fetch": {"cold_step_reads": cold_reads, "cold_step_ms": cold_s * 1e3,
@@ -312,6 +347,9 @@ def run_ours(args):
     }
     if miss_path:
         line["miss_path"] = miss_path
+        line["value_with_misses"] = {"value": world * miss_path["tokens_per_s"], "unit": "tokens/s",
+                                     "ms_per_step": miss_path["ms_per_step"], "miss_fraction": miss_path["miss_fraction"],
+                                     "note": "drifting queries, misses read from the pinned host pool inside the step"}
     if rank == 0:
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg, args.cpu_requests)
@@ -368,6 +406,170 @@ def measure_miss_path(torch, ops, p, stream, args):
         out["host_link"] = {"rows": rows * p.batch, "bytes": rows * p.batch * p.token_bytes, "ms": t * 1e3,
                             "gbs": rows * p.batch * p.token_bytes / t / 1e9}
     return out
+
+
+def zipf_selections(rng, length, steps, reuse, exponent=1.1):
+    """`steps` selections of 2048 logical tokens of one request (NumPy, host). Every selection is an ordered list:
+    index = score rank. Selection k keeps `reuse` of selection k-1, sampled without replacement with probability
+    proportional to rank^-exponent (a high-ranked token is likelier to be selected again), and fills up with
+    tokens drawn uniformly from the rest of the context; kept tokens stay in rank order ahead of the new ones."""
+    import numpy as np
+    keep = int(round(2048 * reuse))
+    weights = np.arange(1, 2049, dtype=np.float64) ** -exponent
+    weights /= weights.sum()
+    lists = [rng.choice(length, 2048, replace=False)]
+    for _ in range(steps - 1):
+        previous = lists[-1]
+        kept = previous[np.sort(rng.choice(2048, keep, replace=False, p=weights))]
+        taken = np.zeros(length, dtype=bool)
+        taken[previous] = True                       # new tokens come from outside the previous selection
+        fresh = rng.choice(np.flatnonzero(~taken), 2048 - keep, replace=False)
+        lists.append(np.concatenate((kept, fresh)))
+    return np.stack(lists)
+
+
+def run_zipf(args):
+    """`--workload decode_128k_b32_zipf`: the full decode step WITH misses of the benchmark configurations - batch 32,
+    131072-token context, FP8 Index keys, TopK 2048, a resident pool of 25 % of the context (32768 slots of 1152
+    bytes), misses read from the pinned, mapped host pool, LRU feedback, and one new bf16 Index row per token
+    quantised to FP8; 8 timed steps whose selections reuse the previous step's tokens with Zipf(1.1) rank weights.
+
+    The selection is steered by biasing the scores (no trace of real queries ships with the reference): every step
+    runs the real score kernel over the whole context, then the harness raises the scores of the step's chosen
+    tokens above all others (three small torch ops: inverse of the Index permutation, position lookup, scatter) and
+    the fused call continues from those score rows (KVIP_OPTION_SCORES_READY): TopK, resolver, Index exchange,
+    fetch, gather and LRU feedback are the product path on real state. The whole step is one CUDA graph; the
+    step's token list is copied into a static buffer before each replay. The harness ops are timed alone and
+    reported so that their share can be subtracted."""
+    import numpy as np
+    import torch
+
+    from decode_harness import DecodePipeline
+    from kvip_b200 import _lib, ops
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    stream = torch.cuda.Stream(device)
+    lib = _load_counter()
+    steps, warm = 8, max(args.warmup, 4)
+    cfg = dict(batch=args.batch or 32, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
+               len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152)
+    rng = np.random.default_rng(0)
+    total = warm + 2 * steps   # warm-up, the timed steps, and as many again with stage stamps
+    with torch.cuda.stream(stream):
+        p = DecodePipeline(device, seed=0, gather=True, host_pool=True, **cfg)
+        chosen = np.stack([zipf_selections(rng, int(p.lengths[b]), total, args.reuse) for b in range(p.batch)], axis=1)
+        chosen = torch.from_numpy(chosen).to(device)                 # [total, B, 2048] logical tokens
+        inputs, s, ws = p.workspace.inputs, p.storage, p.workspace
+        owners = inputs.row_owners.long()
+        tokens_now = torch.zeros((p.batch, 2048), dtype=torch.int64, device=device)   # static: read by the graph
+        inverse = torch.zeros((p.batch, p.history), dtype=torch.int64, device=device)
+        positions = torch.zeros((p.batch, 2048), dtype=torch.int64, device=device)
+        arange = torch.arange(p.history, dtype=torch.int64, device=device).expand(p.batch, -1).contiguous()
+        boost = torch.full((p.batch, 2048), 3.0e38, dtype=torch.float32, device=device)
+        keys_view = s.keys.view(torch.float8_e4m3fn).view(-1, 128)
+        qe2d = inputs.query_ends.view(p.batch, p.queries)
+
+        def steer():  # where does each chosen logical token sit now, and lift its score
+            inverse.scatter_(1, s.logical_ids[owners], arange)
+            torch.gather(inverse, 1, tokens_now, out=positions)
+            ws.scores.scatter_(1, positions, boost)
+
+        def step():
+            p.ingest_new_tokens()
+            ops.li_score(inputs.query, keys_view, inputs.weights, inputs.scale, s.scales.view(-1), ws.key_lengths, qe2d,
+                         inputs.block_table, ws.scores, status=p.forward.li_status)
+            steer()
+            p.forward(scores_ready=True)
+
+        def run(index, replay):
+            tokens_now.copy_(chosen[index])
+            replay()
+
+        for i in range(2):     # eager: lazy set-up outside capture
+            run(i, step)
+        stream.synchronize()
+        before = lib.kvip_b200_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        launches_per_step = lib.kvip_b200_launch_count() - before
+        for i in range(2, warm):
+            run(i, graph.replay)
+        stream.synchronize()
+        misses = torch.zeros(steps, dtype=torch.int64, device=device)
+        with ClockSampler(local) as clocks:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for k in range(steps):
+                run(warm + k, graph.replay)
+                misses[k] = p.rotating.query_counts[:, 4].sum()
+            stop.record(stream)
+            stop.synchronize()
+        seconds = start.elapsed_time(stop) / 1e3
+        status = (int(p.update.status.abs().max().item()) | int(p.rotating.row_status[:, 0].abs().max().item())
+                  | int(p.rotating.row_status[:, 2].abs().max().item()) | int(p.forward.li_status.item()))
+        selected = torch.sort(p.update.logical_output.view(p.batch, 2048).long(), dim=1).values
+        verified = bool(torch.equal(selected, torch.sort(chosen[warm + steps - 1], dim=1).values))
+        harness = time_region(torch, stream, steer, 20) / 20
+        # the same chain, eight more steps, with the call's own stage stamps (a profiling pass: eight extra launches)
+        p.forward.set_options(diagnostics=True)
+        stage_sum, link = {}, []
+        for k in range(steps):
+            run(warm + steps + k, step)
+            stream.synchronize()
+            times = p.forward.stage_times()
+            count = int(p.rotating.query_counts[:, 4].sum().item())
+            for name, value in times.items():
+                stage_sum[name] = stage_sum.get(name, 0.0) + value / steps
+            if times["fetch"] > 0:
+                link.append(count * p.token_bytes / (times["fetch"] * 1e-6) / 1e9)
+        p.forward.set_options()
+        # end to end: the step fed from and drained to pinned host memory on one stream
+        T = p.query_tokens()
+        host_q = inputs.query.view(torch.uint8).cpu().pin_memory()
+        host_out = torch.empty((2, T, 1, 2048), dtype=torch.int32).pin_memory()
+        host_tokens = chosen[warm:warm + steps].cpu().pin_memory()
+
+        def e2e_steps():
+            for k in range(steps):
+                inputs.query.view(torch.uint8).copy_(host_q, non_blocking=True)
+                tokens_now.copy_(host_tokens[k], non_blocking=True)
+                graph.replay()
+                host_out.copy_(p.update.outputs, non_blocking=True)
+
+        e2e_seconds = time_region(torch, stream, e2e_steps, 1)
+    miss_list = misses.tolist()
+    per_step = sum(miss_list) / steps
+    hbm_peak, peak_kind = peaks()
+    li_bytes = li_algorithmic_bytes(p.lengths, p.queries, p.heads, 1)
+    print(json.dumps({
+        "metric": METRIC + ", with misses (Zipf reuse)", "value": T * steps / seconds, "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warm, "ms_per_step": seconds / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": p.batch, "context": int(p.lengths.max()), "topk": 2048,
+                   "resident_slots": p.resident, "token_bytes": p.token_bytes, "cuda_graph": True,
+                   "reuse_of_previous_selection": args.reuse, "zipf_exponent": 1.1,
+                   "selection": "scores of the step's chosen tokens raised after the real score pass",
+                   "index_update": "one new bf16 row per token quantised to FP8, every step",
+                   "l2": "inputs larger than L2 (keys %.0f MB per step)" % (li_bytes / 1e6),
+                   "miss_source": "pinned mapped host pool"},
+        "misses_per_step": per_step, "misses_by_step": miss_list, "miss_fraction": per_step / (T * 2048),
+        "miss_bytes_per_step": per_step * p.token_bytes, "status": status, "selection_verified": verified,
+        "harness_us_per_step": harness * 1e6,
+        "stages_us": stage_sum,
+        "host_link": {"gbs_inside_the_step": (sum(link) / len(link)) if link else None,
+                      "how": "missing bytes of the step / device time of its fetch stage (stage stamps), mean of 8 steps"},
+        "e2e": {"value": T * steps / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": host_q.numel() + 2048 * 8 * p.batch,
+                "d2h_bytes_per_step": host_out.numel() * 4, "ms_per_step": e2e_seconds / steps * 1e3},
+        "gpu_launches": launches_per_step * steps,
+        "roofline": {"kernel": "fetch_rows", "bound": "host link", "achieved": (sum(link) / len(link)) if link else None,
+                     "peak": None, "unit": "GB/s", "frac": None, "traffic": None,
+                     "note": "the step is bound by the host link; its HBM-bound part is reported by decode_128k_b64"},
+        "clocks": clocks.result,
+    }), flush=True)
+    p.close()
 
 
 def cpu_step(cfg, requests, seed=0, budget_s=1e9):
@@ -448,6 +650,45 @@ def run_reference(args):
     }), flush=True)
 
 
+def measure_fp8_peak(torch, device, local):
+    """Dense FP8 (e4m3 x e4m3 -> bf16) tensor throughput of this GPU, measured the way the bf16 figure of
+    MEASURED_PEAKS.json was: torch._scaled_mm (cuBLASLt) on 8192^3, best of 10 as the burst figure and a
+    four-second back-to-back loop as the sustained one, with the SM clock sampled during the loop. Only a
+    denominator for the roofline of the prefill workload: nothing of the product path calls it."""
+    n = 8192
+    a = (torch.randn((n, n), device=device) * 0.5).to(torch.float8_e4m3fn)
+    b = (torch.randn((n, n), device=device) * 0.5).to(torch.float8_e4m3fn).t()    # column-major operand
+    one = torch.ones((), dtype=torch.float32, device=device)
+    out = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+    run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=out)  # noqa: E731
+    flops = 2.0 * n ** 3
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize(device)
+    best = float("inf")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(10):
+        start.record()
+        run()
+        stop.record()
+        stop.synchronize()
+        best = min(best, start.elapsed_time(stop) / 1e3)
+    with ClockSampler(local) as sampler:
+        begin, count = time.perf_counter(), 0
+        start.record()
+        while time.perf_counter() - begin < 4.0:
+            for _ in range(50):
+                run()
+            count += 50
+            torch.cuda.synchronize(device)
+        stop.record()
+        stop.synchronize()
+        sustained = start.elapsed_time(stop) / 1e3 / count
+    return {"fp8_tflops": flops / best / 1e12, "fp8_tflops_sustained": flops / sustained / 1e12,
+            "how": "torch._scaled_mm e4m3 x e4m3 -> bf16, 8192^3: best of 10 (burst), 4 s back to back (sustained)",
+            "clocks_under_load": sampler.result}
+
+
 def run_prefill(args):
     """`--workload prefill_16k_128k`: LI score + TopK of one request's 16384-token query chunk against its causal
     131072-token context (FP8), the dense-contraction stress of the benchmark configs. The reference packs at
@@ -512,8 +753,11 @@ def run_prefill(args):
             e2e_elapsed = time_region(torch, stream, e2e_step, steps)
         clocks = sampler.result
     flops = 2.0 * heads * 128 * float(ends.to(torch.float64).sum().item())
-    peak_path = ROOT / "MEASURED_PEAKS.json"
-    bf16_peak = float(json.loads(peak_path.read_text())["bf16_tflops"]) if peak_path.exists() else 1590.0
+    del scores, picked
+    torch.cuda.empty_cache()
+    fp8 = measure_fp8_peak(torch, device, device.index or 0)
+    # a launch lasts milliseconds and a chunk tens of them: the sustained figure is the fair denominator
+    fp8_peak = fp8["fp8_tflops_sustained"]
     achieved = flops / (li_elapsed / steps) / 1e12
     print(json.dumps({
         "metric": "LI+TopK query tokens/s, chunked prefill 16384 x 131072 causal", "value": chunk * steps / elapsed,
@@ -525,9 +769,10 @@ def run_prefill(args):
         "e2e": {"value": chunk * steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": host_query.numel(),
                 "d2h_bytes_per_step": host_picked.numel() * 4, "ms_per_step": e2e_elapsed / steps * 1e3},
         "gpu_launches": launches,
-        "roofline": {"kernel": "li_score_tcgen05", "bound": "tensor", "achieved": achieved, "peak": 2 * bf16_peak,
-                     "unit": "TFLOP/s", "frac": achieved / (2 * bf16_peak),
-                     "peak_kind": "2 x the measured bf16 burst figure (no FP8 figure was measured on this pool)",
+        "roofline": {"kernel": "li_score_tcgen05", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
+                     "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+                     "peak_kind": "of measured: dense FP8 GEMM throughput measured in this run (sustained figure)",
+                     "peak_measurement": fp8,
                      "flops_per_chunk": flops, "ms_li_per_chunk": li_elapsed / steps * 1e3, "traffic": None},
         "clocks": clocks,
     }), flush=True)
@@ -542,7 +787,7 @@ def run_seqshard(args):
     import torch.distributed as dist
 
     from kvip_b200 import ops
-    from kvip_b200.sharding import gather_candidates, shard_bounds
+    from kvip_b200.sharding import ShardedTopk, shard_bounds
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -570,9 +815,8 @@ def run_seqshard(args):
     table = torch.arange(keys_here // 128, dtype=torch.int32, device=device).view(1, -1)
     scores = torch.zeros((1, keys_here), dtype=torch.float32, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
-    cand_scores = torch.zeros((1, 2048), dtype=torch.float32, device=device)
-    cand_index = torch.empty((1, 2048), dtype=torch.int32, device=device)
-    merged = torch.empty((1, 2048), dtype=torch.int32, device=device)
+    sharded = ShardedTopk(1, device)
+    merged = sharded.merged
     host_merged = torch.empty((1, 2048), dtype=torch.int32).pin_memory()
     host_query = query.view(torch.uint8).cpu().pin_memory()
     lib = _load_counter()
@@ -580,9 +824,28 @@ def run_seqshard(args):
 
     def step():
         ops.li_score(query, keys, weights, query_scale, key_scale, lengths, ends, table, scores, status=status)
-        ops.topk(scores, lengths, ends, cand_index, out_scores=cand_scores, base_index=begin)
-        all_scores, all_index = gather_candidates(cand_scores, cand_index)
-        ops.topk_merge(all_scores, all_index, merged)
+        sharded(scores, lengths, ends, begin)   # local TopK -> one all-gather -> merge in place
+
+    def phases(rounds=50):
+        """Device time of the four phases of the eager step, from CUDA events between them (mean of `rounds`)."""
+        import torch.distributed as dist
+        names = ("shard_li_score", "local_topk", "all_gather", "merge")
+        total = dict.fromkeys(names, 0.0)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        for _ in range(rounds):
+            marks[0].record(stream)
+            ops.li_score(query, keys, weights, query_scale, key_scale, lengths, ends, table, scores, status=status)
+            marks[1].record(stream)
+            ops.topk(scores, lengths, ends, sharded.local_index, out_scores=sharded.local_scores, base_index=begin)
+            marks[2].record(stream)
+            dist.all_gather_into_tensor(sharded.gathered, sharded.send)
+            marks[3].record(stream)
+            ops.topk_merge_gathered(sharded.gathered, sharded.merged)
+            marks[4].record(stream)
+            marks[4].synchronize()
+            for i, name in enumerate(names):
+                total[name] += marks[i].elapsed_time(marks[i + 1]) * 1e3 / rounds
+        return total
 
     def e2e_step():
         query.view(torch.uint8).copy_(host_query, non_blocking=True)
@@ -638,9 +901,13 @@ def run_seqshard(args):
         replay()
         stream.synchronize()
         verified = verified and bool(torch.equal(expected, merged))
-    worst = torch.tensor([elapsed, e2e_elapsed, 0.0 if verified else 1.0], dtype=torch.float64, device=device)
+        phase_us = phases()
+        barrier()
+    worst = torch.tensor([elapsed, e2e_elapsed, 0.0 if verified else 1.0] + [phase_us[k] for k in sorted(phase_us)],
+                         dtype=torch.float64, device=device)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed, failed = (float(x) for x in worst.tolist())
+    elapsed, e2e_elapsed, failed, *slowest = (float(x) for x in worst.tolist())
+    phase_us = dict(zip(sorted(phase_us), slowest))
     if rank == 0:
         print(json.dumps({
             "metric": "LI+TopK query tokens/s, one 1,048,576-token request sharded along the sequence",
@@ -654,6 +921,8 @@ def run_seqshard(args):
             "e2e": {"value": args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": host_query.numel(),
                     "d2h_bytes_per_step": host_merged.numel() * 4, "ms_per_step": e2e_elapsed / args.steps * 1e3},
             "gpu_launches": launches, "verified_against_unsharded_topk": failed == 0.0,
+            "phases_us": dict(phase_us, note="eager launches, CUDA events between the phases, slowest rank of each; the "
+                                             "events keep the launches from overlapping, so the sum exceeds the step"),
             "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": None, "peak": peaks()[0],
                          "unit": "GB/s", "frac": None, "traffic": None,
                          "note": "latency-bound step: about 7 key pages per CTA; see ms_per_step"},
@@ -815,7 +1084,10 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch"], default="decode_128k_b64")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch",
+                                                       "decode_128k_b32_zipf"], default="decode_128k_b64")
+    parser.add_argument("--reuse", type=float, default=0.75,
+                        help="decode_128k_b32_zipf: share of a selection kept from the previous step")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")
     parser.add_argument("--device-source", action="store_true", help="serve misses from HBM instead of the host pool")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -836,6 +1108,8 @@ def main():
         run_lidu(args)
     elif args.workload == "miss_path_prefetch":
         run_miss_prefetch(args)
+    elif args.workload == "decode_128k_b32_zipf":
+        run_zipf(args)
     else:
         run_ours(args)
 

@@ -161,10 +161,14 @@ uint32_t kvip_b200_topk_static(const KvipTopkArgs* args, void* stream);
  * global top-2048 under the same total order. New on B200 (no reference counterpart;
  * precedent: the on-chip sequence split, common/lifetch/sequence_schedule.h:9-37). */
 typedef struct KvipMergeArgs {
-  const float* cand_scores;   /* [rows, shards*2048] */
-  const int32_t* cand_index;  /* [rows, shards*2048], -1 = empty */
+  const float* cand_scores;   /* [rows, shards*2048], or any layout the two strides describe */
+  const int32_t* cand_index;  /* same layout, -1 = empty */
   int32_t* topk;              /* [rows, 2048] */
   uint32_t rows, shards;
+  uint32_t shard_stride;      /* elements between the candidate lists of two shards of one row; 0 = 2048 */
+  uint32_t row_stride;        /* elements between two rows of one shard; 0 = shards * 2048. The buffer an all-gather of
+                                 per-rank [2, rows, 2048] (scores, indices) blocks fills is read in place with
+                                 shard_stride = 2 * rows * 2048 and row_stride = 2048. */
 } KvipMergeArgs;
 uint32_t kvip_b200_topk_merge(const KvipMergeArgs* args, void* stream);
 
@@ -263,6 +267,8 @@ typedef struct KvipResolveArgs {
   uint32_t reserved1;
   uint64_t source_bytes;        /* size of the miss source; 0 = addresses are not checked here */
   KvipFinalPost* final_posts;   /* [batch, 4] out, or NULL */
+  uint32_t* miss_mask;          /* [batch*queries, 64] out or NULL: bit k of a row = entry k of that TopK row was a miss
+                                   (its slot is filled by this round's fetch); lets the gather run in two phases */
 } KvipResolveArgs;
 uint32_t kvip_b200_resolve(const KvipResolveArgs* args, void* stream);
 
@@ -287,8 +293,15 @@ typedef struct KvipFetchArgs {
   int32_t* status;                 /* [batch] Index-update status or NULL: a descriptor that fails the range check
                                       ORs 4 into its request's word (index_cache_update.h:6-20) and the destination
                                       slot loses residency, so the next step cannot read a stale row as a hit */
+  uint32_t defer_publication;      /* 1 = copy only; hot_valid = 1 is left to kvip_b200_publish_residency */
+  uint32_t reserved0;
 } KvipFetchArgs;
 uint32_t kvip_b200_fetch(const KvipFetchArgs* args, void* stream);
+/* hot_valid[owner, slot] = 1 for every descriptor the fetch accepted (same argument struct, same checks). Split from
+ * the copy for callers that run the fetch beside the Index exchange: the exchange revokes the residency of
+ * positions it frees, and a slot freed there and refilled by this round's fetch must end up valid, so the
+ * publication has to come after both (PublishQueryCompletion, streaming.cpp:300-328, has the same order). */
+uint32_t kvip_b200_publish_residency(const KvipFetchArgs* args, void* stream);
 
 /* Dense gather of the selected rows: out[t, k, :] = pool[owner*outputStride + slot[t,k], :],
  * zero rows where slot < 0. (The north-star "fetch" output; the reference hands slot
@@ -299,6 +312,10 @@ typedef struct KvipGatherArgs {
   const int32_t* row_owners;   /* [batch] or NULL */
   uint8_t* out;                /* [rows, 2048, tokenBytes] */
   uint32_t rows, queries, outputStride, tokenBytes;
+  const uint32_t* miss_mask;   /* [rows, 64] from the resolver, or NULL */
+  uint32_t phase;              /* with miss_mask: 0 = every entry, 1 = only entries that were hits (independent of this
+                                  round's fetch), 2 = only entries that were misses */
+  uint32_t reserved0;
 } KvipGatherArgs;
 uint32_t kvip_b200_gather(const KvipGatherArgs* args, void* stream);
 
@@ -519,6 +536,7 @@ typedef struct KvipContext {          /* reference: rotating::Context, include/c
   uint64_t query_counts, pool, source_base, source_bytes;
   KvipRuntimeShape shape;
   uint64_t final_posts;          /* KvipFinalPost [batch, 4] or 0 */
+  uint64_t miss_mask;            /* uint32 [batch*queries, 64] or 0: needed for the overlapped commit phase */
 } KvipContext;
 
 typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_types.h:17-22 */
@@ -537,7 +555,15 @@ typedef struct KvipWorkspace {        /* reference: pipeline_ab::Args, pipeline_
   uint64_t staging;             /* uint8 [batch, staged_capacity, tokenBytes] */
   uint64_t staged_hits;         /* int32 [batch] or 0: incremented per missing row served from the staging area */
   uint32_t staged_capacity, reserved2;
-  uint8_t reserved[24];
+  /* Overlapped commit phase (all three set, and KvipContext.miss_mask bound; 0 = everything on `stream`): the
+     service outputs, the Index exchange and the gather of the entries that were hits are enqueued on `side_stream`
+     while the fetch of the missing rows occupies `stream`; residency is published and the missed entries are
+     gathered after both have finished. The call records `fork_event` on `stream`, makes the side stream wait for
+     it, and makes `stream` wait for `join_event`, so the caller sees one ordered step (and one CUDA graph).
+     No counterpart in the reference, whose forward enqueues on one stream. */
+  uint64_t side_stream;         /* cudaStream_t */
+  uint64_t fork_event;          /* cudaEvent_t */
+  uint64_t join_event;          /* cudaEvent_t */
 } KvipWorkspace;
 
 uint32_t kvip_lifetch_streaming_forward(void* bindings, void* update, void* workspace,

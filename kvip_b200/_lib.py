@@ -62,7 +62,8 @@ ColdArgs = _struct("ColdArgs", ("scores", "key_lengths", "query_ends", "prefix_t
                                 "bitmap", "counts"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "resident", "bitmap_words", "reserved0")])
 
-MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"), [("rows", u32), ("shards", u32)])
+MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"),
+                    [("rows", u32), ("shards", u32), ("shard_stride", u32), ("row_stride", u32)])
 
 ResolveArgs = _struct("ResolveArgs", (
     "topk", "row_owners", "hot_valid", "reserved_hot", "lru_slots", "tail_bounds", "logical_ids", "addresses",

@@ -80,12 +80,15 @@ __device__ __forceinline__ void bitonic_sort(uint64_t* data, uint32_t n) {
 __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a, uint32_t padded) {
   extern __shared__ uint64_t composite[];
   const uint32_t row = blockIdx.x, n = a.shards * kTop;
-  const float* cs = a.cand_scores + static_cast<uint64_t>(row) * n;
-  const int32_t* ci = a.cand_index + static_cast<uint64_t>(row) * n;
+  const uint64_t shard_stride = a.shard_stride ? a.shard_stride : kTop;
+  const uint64_t row_offset = static_cast<uint64_t>(row) * (a.row_stride ? a.row_stride : n);
   for (uint32_t i = threadIdx.x; i < padded; i += kThreads) {
     uint64_t c = ~0ull;
-    if (i < n && ci[i] >= 0)
-      c = (static_cast<uint64_t>(~sortable_key(cs[i])) << 32) | static_cast<uint32_t>(ci[i]);
+    if (i < n) {
+      const uint64_t at = row_offset + (i / kTop) * shard_stride + (i % kTop);
+      const int32_t index = a.cand_index[at];
+      if (index >= 0) c = (static_cast<uint64_t>(~sortable_key(a.cand_scores[at])) << 32) | static_cast<uint32_t>(index);
+    }
     composite[i] = c;
   }
   __syncthreads();

@@ -435,8 +435,14 @@ class LIFetch:
                 self._lru_done.record(self._side)
             stream.wait_event(self._lru_done)
 
-    def __call__(self):
-        if self.prefetch is None:
+    def __call__(self, scores_ready=False):
+        """The whole step. `scores_ready=True`: the score rows were written by the caller (an `ops.li_score` launch of
+        its own, or a test that supplies scores): the call starts at TopK."""
+        if scores_ready:
+            if self.prefetch is not None:
+                raise ValueError("prefetch windows issue the score pass themselves")
+            self._enqueue(_lib.OPTION_SCORES_READY)
+        elif self.prefetch is None:
             self._enqueue(0)
         else:
             self.select()

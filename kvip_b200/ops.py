@@ -136,6 +136,22 @@ def topk_merge(cand_scores, cand_index, out=None):
     return out
 
 
+def topk_merge_gathered(gathered, out=None):
+    """Global top-2048 straight from the all-gather buffer: `gathered` int32 [shards, 2, rows, 2048], block r = rank
+    r's (score bits, indices). No repacking between the collective and the merge."""
+    device = gathered.device
+    _require(gathered, "gathered", torch.int32, device)
+    shards, two, rows, width = gathered.shape
+    if two != 2 or width != TOPK:
+        raise ValueError("gathered candidates must be int32 [shards, 2, rows, 2048]")
+    if out is None:
+        out = torch.empty((rows, TOPK), dtype=torch.int32, device=device)
+    args = _lib.MergeArgs(cand_scores=gathered.data_ptr(), cand_index=gathered[0, 1].data_ptr(), topk=_ptr(out),
+                          rows=rows, shards=shards, shard_stride=2 * rows * TOPK, row_stride=TOPK)
+    _lib.check(_lib.load_library().kvip_b200_topk_merge(ctypes.byref(args), _stream(device)), "topk_merge")
+    return out
+
+
 class ResolveState:
     """Per-launch resolver scratch and outputs (shapes of operators/lifetch/workspace.py:9-32)."""
 

@@ -49,6 +49,29 @@ def gather_candidates(local_scores, local_index, group=None):
     return scores, index
 
 
+class ShardedTopk:
+    """Preallocated buffers of the sequence-sharded TopK of `rows` score rows: the local TopK writes its scores and
+    global indices straight into this rank's send block, ONE all-gather fills [world, 2, rows, 2048], and the merge
+    kernel reads that buffer in place. Per step: local TopK, all-gather, merge - three launches, no repacking."""
+
+    def __init__(self, rows, device, group=None):
+        import torch.distributed as dist
+
+        self.group, self.world = group, dist.get_world_size(group)
+        self.send = torch.zeros((2, rows, TOPK), dtype=torch.int32, device=device)
+        self.gathered = torch.zeros((self.world, 2, rows, TOPK), dtype=torch.int32, device=device)
+        self.merged = torch.empty((rows, TOPK), dtype=torch.int32, device=device)
+        self.local_scores, self.local_index = self.send[0].view(torch.float32), self.send[1]
+
+    def __call__(self, scores, lengths, ends, base_index):
+        import torch.distributed as dist
+
+        from . import ops
+        ops.topk(scores, lengths, ends, self.local_index, out_scores=self.local_scores, base_index=base_index)
+        dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
+        return ops.topk_merge_gathered(self.gathered, self.merged)
+
+
 def sequence_sharded_topk(local_scores, local_length, base_index, *, queries=1, group=None, local_topk=None,
                           merge=None):
     """Global TopK-2048 of a request whose score rows are sharded along the sequence.

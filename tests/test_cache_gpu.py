@@ -379,6 +379,60 @@ def test_lidu_reference_known_answers(device):
     assert outs["counts"].cpu().tolist() == [0, 0, 0]
 
 
+def _reference_lidu_all_hit_inputs(shift):
+    """The inputs of the reference's tests/operators/lidu/test_lidu.py:17-49, unmodified: identity token->slot map over
+    4096 slots, victim candidates 0..2047 (NativeMtp.preferred, execution.py:1392), `bitmap[:, :64] = -1` (the 2048
+    candidate slots marked), four query rows selecting tokens shift..shift+2047, second request = graph padding."""
+    batch, history, hot = 2, 4096, 4096
+    bitmap = np.zeros((batch, 4176), np.int32)
+    bitmap[:, :64] = -1
+    return dict(
+        topk=np.tile((np.arange(TOPK, dtype=np.int32) + shift), (8, 1)).reshape(8, 1, TOPK), ends=np.array([4, 8], np.int32),
+        pools=np.array([0, batch], np.int32), t2s=np.tile(np.arange(history, dtype=np.int32), (batch, 1)),
+        s2t=np.tile(np.arange(hot, dtype=np.int32), (batch, 1)), cursors=np.zeros(batch, np.int32),
+        cache_tokens=np.array([hot, 0], np.int32), candidate_lens=np.array([history, 0], np.int32),
+        miss_slots=np.tile(np.arange(TOPK, dtype=np.int32), (batch, 1)), bitmap=bitmap,
+        block_table=np.arange(batch * hot // 128, dtype=np.int32).reshape(batch, -1),
+        logical=np.array([history, 1], np.int32)), history
+
+
+@pytest.mark.xfail(strict=True, reason=(
+    "The reference's own known answer for these inputs is counts == [0, 0, 0] (test_lidu.py:38). The kernel source it "
+    "ships cannot produce it: ClassifyTopkSimt (a5_lidu_fused_batch_get_prepare_mtp.cpp:205-217) makes a mapped slot "
+    "a hit only when its bit in the membership words is CLEAR, and LoadMissSlotMembership (:1331-1353) loads "
+    "miss_slot_bitmap verbatim, so tokens 0..2047, which sit in the marked slots 0..2047, are misses. This build "
+    "follows the kernel source; see test_lidu_marked_victim_slots_are_misses for what that rule gives."))
+def test_lidu_reference_known_answer_with_the_reference_bitmap(device):
+    state, history = _reference_lidu_all_hit_inputs(shift=0)
+    _, outs, _, _ = _run_lidu(state, device, layer_id=0, num_layers=1, max_num_reqs=2, qcap=history // 128)
+    assert outs["counts"].cpu().tolist() == [0, 0, 0]
+
+
+def test_lidu_marked_victim_slots_are_misses(device):
+    """On the serving path `miss_slots` / `miss_slot_bitmap` are the LRU's 2048 oldest slots and their bitmap
+    (execution.py:1576-1584 seed_native_bitmap, 1839-1850, 3453-3456): slots this very call may overwrite. A selected
+    token that lives in one of them is therefore re-resolved like a miss (the kernel's rule, :205-217), exactly as
+    the fused resolver refuses a hot hit on a position with `reserved_hot >= 0` (resolver_staged_dma2.h:14-16).
+    With the reference test's unmodified inputs that rule gives: shift 0 -> all 2048 tokens are misses and take the
+    candidate slots again; shift 256 / 512 -> the tokens below 2048 are misses, the rest hits. The oracle
+    restatement says the same, and the reference's harness invariants (NativeMtp.verify, execution.py:1478-1506:
+    every selected token maps to a slot in range, exported slot sets equal the map) hold."""
+    for shift in (0, 256, 512):
+        state, history = _reference_lidu_all_hit_inputs(shift)
+        dev, outs, cpu, ref = _run_lidu(state, device, layer_id=0, num_layers=1, max_num_reqs=2, qcap=history // 128)
+        _compare_lidu(dev, outs, cpu, ref)
+        counts = outs["counts"].cpu().tolist()
+        assert counts == [TOPK - shift, 0, TOPK - shift], (shift, counts)
+        t2s = dev["t2s"].cpu().numpy()
+        tokens = np.arange(TOPK) + shift
+        slots = t2s[0, tokens]
+        assert slots.min() >= 0 and slots.max() < 4096 and len(set(slots.tolist())) == TOPK
+        exported = outs["dest"].cpu().numpy().reshape(8, TOPK)[:4]
+        for q in range(4):
+            assert np.array_equal(np.sort(exported[q]), np.sort(slots))
+        assert np.array_equal(dev["s2t"].cpu().numpy()[0, slots], tokens)
+
+
 def test_lidu_row_errors_and_argument_checks(device):
     state = _lidu_state(device, 3, [2, 2, 2], source=20000, hot=4096, seed=9)
     state["topk"][2, 0, 7] = 20000          # token outside candidate_len -> row 1 fails (-103 -> count -1)
