@@ -428,39 +428,17 @@ def zipf_selections(rng, length, steps, reuse, exponent=1.1):
     return np.stack(lists)
 
 
-def run_zipf(args):
-    """`--workload decode_128k_b32_zipf`: the full decode step WITH misses of the benchmark configurations - batch 32,
-    131072-token context, FP8 Index keys, TopK 2048, a resident pool of 25 % of the context (32768 slots of 1152
-    bytes), misses read from the pinned, mapped host pool, LRU feedback, and one new bf16 Index row per token
-    quantised to FP8; 8 timed steps whose selections reuse the previous step's tokens with Zipf(1.1) rank weights.
-
-    The selection is steered by biasing the scores (no trace of real queries ships with the reference): every step
-    runs the real score kernel over the whole context, then the harness raises the scores of the step's chosen
-    tokens above all others (three small torch ops: inverse of the Index permutation, position lookup, scatter) and
-    the fused call continues from those score rows (KVIP_OPTION_SCORES_READY): TopK, resolver, Index exchange,
-    fetch, gather and LRU feedback are the product path on real state. The whole step is one CUDA graph; the
-    step's token list is copied into a static buffer before each replay. The harness ops are timed alone and
-    reported so that their share can be subtracted."""
-    import numpy as np
-    import torch
-
+def zipf_variant(torch, device, stream, cfg, chosen_host, steps, warm, overlap):
+    """One pipeline of the Zipf-reuse workload (commit phase serial or overlapped): timed steps, a second pass with
+    stage stamps, an end-to-end pass. Returns the measurements as a dict."""
     from decode_harness import DecodePipeline
-    from kvip_b200 import _lib, ops
+    from kvip_b200 import ops
 
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
-    stream = torch.cuda.Stream(device)
     lib = _load_counter()
-    steps, warm = 8, max(args.warmup, 4)
-    cfg = dict(batch=args.batch or 32, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
-               len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152)
-    rng = np.random.default_rng(0)
-    total = warm + 2 * steps   # warm-up, the timed steps, and as many again with stage stamps
+    local = device.index or 0
     with torch.cuda.stream(stream):
-        p = DecodePipeline(device, seed=0, gather=True, host_pool=True, **cfg)
-        chosen = np.stack([zipf_selections(rng, int(p.lengths[b]), total, args.reuse) for b in range(p.batch)], axis=1)
-        chosen = torch.from_numpy(chosen).to(device)                 # [total, B, 2048] logical tokens
+        p = DecodePipeline(device, seed=0, gather=True, host_pool=True, overlap_fetch=overlap, **cfg)
+        chosen = torch.from_numpy(chosen_host).to(device)                 # [total, B, 2048] logical tokens
         inputs, s, ws = p.workspace.inputs, p.storage, p.workspace
         owners = inputs.row_owners.long()
         tokens_now = torch.zeros((p.batch, 2048), dtype=torch.int64, device=device)   # static: read by the graph
@@ -513,18 +491,21 @@ def run_zipf(args):
         selected = torch.sort(p.update.logical_output.view(p.batch, 2048).long(), dim=1).values
         verified = bool(torch.equal(selected, torch.sort(chosen[warm + steps - 1], dim=1).values))
         harness = time_region(torch, stream, steer, 20) / 20
-        # the same chain, eight more steps, with the call's own stage stamps (a profiling pass: eight extra launches)
+        # the same chain, as many steps again, with the call's own stage stamps (a profiling pass: extra launches)
         p.forward.set_options(diagnostics=True)
         stage_sum, link = {}, []
         for k in range(steps):
             run(warm + steps + k, step)
             stream.synchronize()
-            times = p.forward.stage_times()
+            stamps = p.forward.times[:8].cpu().tolist()
             count = int(p.rotating.query_counts[:, 4].sum().item())
-            for name, value in times.items():
+            # serial: the fetch starts when the exchange has finished; overlapped: when the resolver has
+            fetch_us = (stamps[6] - (stamps[3] if overlap else stamps[5])) / 1e3
+            for name, value in (("li_to_resolve", (stamps[3] - stamps[0]) / 1e3), ("fetch", fetch_us),
+                                ("resolve_to_end", (stamps[7] - stamps[3]) / 1e3), ("total", (stamps[7] - stamps[0]) / 1e3)):
                 stage_sum[name] = stage_sum.get(name, 0.0) + value / steps
-            if times["fetch"] > 0:
-                link.append(count * p.token_bytes / (times["fetch"] * 1e-6) / 1e9)
+            if fetch_us > 0:
+                link.append(count * p.token_bytes / (fetch_us * 1e-6) / 1e9)
         p.forward.set_options()
         # end to end: the step fed from and drained to pinned host memory on one stream
         T = p.query_tokens()
@@ -541,35 +522,78 @@ def run_zipf(args):
 
         e2e_seconds = time_region(torch, stream, e2e_steps, 1)
     miss_list = misses.tolist()
-    per_step = sum(miss_list) / steps
-    hbm_peak, peak_kind = peaks()
-    li_bytes = li_algorithmic_bytes(p.lengths, p.queries, p.heads, 1)
+    result = dict(seconds=seconds, e2e_seconds=e2e_seconds, misses=miss_list, status=status, verified=verified,
+                  harness_us=harness * 1e6, stages_us=stage_sum, link_gbs=(sum(link) / len(link)) if link else None,
+                  launches_per_step=launches_per_step, clocks=clocks.result, tokens=T, lengths=p.lengths.copy(),
+                  h2d=host_q.numel() + 2048 * 8 * p.batch, d2h=host_out.numel() * 4)
+    p.close()
+    del p, graph
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_zipf(args):
+    """`--workload decode_128k_b32_zipf`: the full decode step WITH misses of the benchmark configurations - batch 32,
+    131072-token context, FP8 Index keys, TopK 2048, a resident pool of 25 % of the context (32768 slots of 1152
+    bytes), misses read from the pinned, mapped host pool, LRU feedback, and one new bf16 Index row per token
+    quantised to FP8; 8 timed steps whose selections reuse the previous step's tokens with Zipf(1.1) rank weights.
+
+    The selection is steered by biasing the scores (no trace of real queries ships with the reference): every step
+    runs the real score kernel over the whole context, then the harness raises the scores of the step's chosen
+    tokens above all others (three small torch ops: inverse of the Index permutation, position lookup, scatter) and
+    the fused call continues from those score rows (KVIP_OPTION_SCORES_READY): TopK, resolver, Index exchange,
+    fetch, gather and LRU feedback are the product path on real state. The whole step is one CUDA graph; the
+    step's token list is copied into a static buffer before each replay. The harness ops are timed alone and
+    reported so that their share can be subtracted. Measured twice, on the same selections: with the commit phase
+    on one stream, and with `LIFetch(overlap_fetch=True)`; `value` is the overlapped variant."""
+    import numpy as np
+    import torch
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    stream = torch.cuda.Stream(device)
+    steps, warm = 8, max(args.warmup, 4)
+    cfg = dict(batch=args.batch or 32, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
+               len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152)
+    rng = np.random.default_rng(0)
+    total = warm + 2 * steps   # warm-up, the timed steps, and as many again with stage stamps
+    chosen = np.stack([zipf_selections(rng, cfg["len_hi"], total, args.reuse) for _ in range(cfg["batch"])], axis=1)
+    serial = zipf_variant(torch, device, stream, cfg, chosen, steps, warm, overlap=False)
+    best = zipf_variant(torch, device, stream, cfg, chosen, steps, warm, overlap=True)
+    T, seconds = best["tokens"], best["seconds"]
+    per_step = sum(best["misses"]) / steps
+    li_bytes = li_algorithmic_bytes(best["lengths"], cfg["queries"], cfg["heads"], 1)
     print(json.dumps({
         "metric": METRIC + ", with misses (Zipf reuse)", "value": T * steps / seconds, "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "warmup": warm, "ms_per_step": seconds / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": p.batch, "context": int(p.lengths.max()), "topk": 2048,
-                   "resident_slots": p.resident, "token_bytes": p.token_bytes, "cuda_graph": True,
+        "config": {"workload": args.workload, "batch_per_gpu": cfg["batch"], "context": cfg["len_hi"], "topk": 2048,
+                   "resident_slots": cfg["resident"], "token_bytes": cfg["token_bytes"], "cuda_graph": True,
                    "reuse_of_previous_selection": args.reuse, "zipf_exponent": 1.1,
                    "selection": "scores of the step's chosen tokens raised after the real score pass",
                    "index_update": "one new bf16 row per token quantised to FP8, every step",
+                   "commit_phase": "overlapped: outputs, exchange and the gather of hit entries beside the fetch",
                    "l2": "inputs larger than L2 (keys %.0f MB per step)" % (li_bytes / 1e6),
                    "miss_source": "pinned mapped host pool"},
-        "misses_per_step": per_step, "misses_by_step": miss_list, "miss_fraction": per_step / (T * 2048),
-        "miss_bytes_per_step": per_step * p.token_bytes, "status": status, "selection_verified": verified,
-        "harness_us_per_step": harness * 1e6,
-        "stages_us": stage_sum,
-        "host_link": {"gbs_inside_the_step": (sum(link) / len(link)) if link else None,
-                      "how": "missing bytes of the step / device time of its fetch stage (stage stamps), mean of 8 steps"},
-        "e2e": {"value": T * steps / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": host_q.numel() + 2048 * 8 * p.batch,
-                "d2h_bytes_per_step": host_out.numel() * 4, "ms_per_step": e2e_seconds / steps * 1e3},
-        "gpu_launches": launches_per_step * steps,
-        "roofline": {"kernel": "fetch_rows", "bound": "host link", "achieved": (sum(link) / len(link)) if link else None,
-                     "peak": None, "unit": "GB/s", "frac": None, "traffic": None,
+        "misses_per_step": per_step, "misses_by_step": best["misses"], "miss_fraction": per_step / (T * 2048),
+        "miss_bytes_per_step": per_step * cfg["token_bytes"], "status": best["status"] | serial["status"],
+        "selection_verified": best["verified"] and serial["verified"],
+        "same_misses_in_both_variants": best["misses"] == serial["misses"],
+        "harness_us_per_step": best["harness_us"], "stages_us": best["stages_us"],
+        "serial_commit_phase": {"ms_per_step": serial["seconds"] / steps * 1e3, "tokens_per_s": T * steps / serial["seconds"],
+                                "stages_us": serial["stages_us"], "host_link_gbs_inside_the_step": serial["link_gbs"]},
+        "host_link": {"gbs_inside_the_step": best["link_gbs"],
+                      "how": "missing bytes of a step / device time of its fetch stage (the call's stage stamps), mean "
+                             "over the steps of the stamped pass"},
+        "e2e": {"value": T * steps / best["e2e_seconds"], "unit": "tokens/s", "h2d_bytes_per_step": best["h2d"],
+                "d2h_bytes_per_step": best["d2h"], "ms_per_step": best["e2e_seconds"] / steps * 1e3},
+        "gpu_launches": best["launches_per_step"] * steps,
+        "roofline": {"kernel": "fetch_rows", "bound": "host link", "achieved": best["link_gbs"], "peak": None,
+                     "unit": "GB/s", "frac": None, "traffic": None,
                      "note": "the step is bound by the host link; its HBM-bound part is reported by decode_128k_b64"},
-        "clocks": clocks.result,
+        "clocks": best["clocks"],
     }), flush=True)
-    p.close()
 
 
 def cpu_step(cfg, requests, seed=0, budget_s=1e9):

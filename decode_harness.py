@@ -73,7 +73,7 @@ class DecodePipeline:
                  weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
                  score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0,
                  overlap_lru=True, prefetch_limit=0, prefetch_windows=3, prefetch_ctas=0,
-                 prefetch_last_window=False, tail_slots=0, head_sum=_lib.HEAD_SUM_AUTO):
+                 prefetch_last_window=False, tail_slots=0, head_sum=_lib.HEAD_SUM_AUTO, overlap_fetch=False):
         self.device = device = torch.device(device)
         self.batch, self.queries, self.heads, self.history, self.resident = batch, queries, heads, history, resident
         self.token_bytes, self.key_dtype = token_bytes, key_dtype
@@ -158,7 +158,7 @@ class DecodePipeline:
         self.overlap_lru = overlap_lru
         self.forward = LIFetch(self.rotating, self.update, lru=self.lru if overlap_lru else None,
                                prefetch_limit=prefetch_limit, prefetch_windows=prefetch_windows, prefetch_ctas=prefetch_ctas,
-                               prefetch_last_window=prefetch_last_window)
+                               prefetch_last_window=prefetch_last_window, overlap_fetch=overlap_fetch)
 
     def new_queries(self, seed):
         """Fresh projected queries / head weights for all rows, packed through QueryInputs.pack."""

@@ -71,15 +71,16 @@ ResolveArgs = _struct("ResolveArgs", (
     "fetch_sources", "fetch_destinations", "logical_output", "slot_output", "unpack_indices", "output_valid",
     "query_ends", "row_status"), [(n, u32) for n in (
         "batch", "queries", "history", "resident", "address_stride", "outputStride", "tokenBytes", "reserved1")] + [
-            ("source_bytes", u64), ("final_posts", vp)])
+            ("source_bytes", u64), ("final_posts", vp), ("miss_mask", vp)])
 
 FetchArgs = _struct("FetchArgs", (
     "source_base", "fetch_sources", "fetch_destinations", "query_counts", "row_owners", "row_status", "pool",
     "hot_valid"), [("source_bytes", u64)] + [(n, u32) for n in ("batch", "resident", "outputStride", "tokenBytes")] + [
-        ("status", vp)])
+        ("status", vp), ("defer_publication", u32), ("reserved0", u32)])
 
 GatherArgs = _struct("GatherArgs", ("pool", "slots", "row_owners", "out"),
-                     [(n, u32) for n in ("rows", "queries", "outputStride", "tokenBytes")])
+                     [(n, u32) for n in ("rows", "queries", "outputStride", "tokenBytes")] + [
+                         ("miss_mask", vp), ("phase", u32), ("reserved0", u32)])
 
 ExchangeArgs = _struct("ExchangeArgs", (
     "keys", "scales", "addresses", "logical_ids", "hot_valid", "events_src", "events_dst", "query_counts",
@@ -136,7 +137,7 @@ class Context(ctypes.Structure):
         "locations", "lru_slots", "reserved_hot", "changes", "change_slots", "change_count", "query_ends",
         "fetch_sources", "fetch_destinations", "hot_valid", "row_owners", "token_addresses", "address_stride",
         "output_stride", "tail_bounds", "row_status", "query_counts", "pool", "source_base", "source_bytes")] + [
-            ("shape", RuntimeShape), ("final_posts", u64)]
+            ("shape", RuntimeShape), ("final_posts", u64), ("miss_mask", u64)]
 
 
 class Workspace(ctypes.Structure):
@@ -148,7 +149,7 @@ class Workspace(ctypes.Structure):
             (n, u64) for n in ("query_bitmaps", "query_errors", "update_bindings", "dense_shadow", "packed_fetch",
                                "gather_out", "topk_scores", "li_status", "topk_histogram", "topk_split",
                                "slots_ready_event", "staged_sources", "staged_rows", "staging", "staged_hits")] + [
-            ("staged_capacity", u32), ("reserved2", u32), ("reserved", ctypes.c_uint8 * 24)]
+            ("staged_capacity", u32), ("reserved2", u32)] + [(n, u64) for n in ("side_stream", "fork_event", "join_event")]
 
 
 _STAGES = {
@@ -156,7 +157,7 @@ _STAGES = {
     "kvip_b200_topk_static": TopkArgs,
     "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs,
     "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
-    "kvip_b200_gather": GatherArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
+    "kvip_b200_gather": GatherArgs, "kvip_b200_publish_residency": FetchArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
     "kvip_b200_ingest_spans": IngestSpanArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs, "kvip_b200_publish_pages": PagesArgs,
     "kvip_b200_window_bounds": WindowArgs, "kvip_b200_resident_threshold": ThresholdArgs,

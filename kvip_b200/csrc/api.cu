@@ -16,6 +16,7 @@ uint32_t launch_exchange(const KvipExchangeArgs& a, cudaStream_t stream);
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream);
 uint32_t launch_fetch_staged(const KvipFetchArgs& a, const KvipWorkspace& ws, cudaStream_t stream);
 uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream);
+uint32_t launch_publish_residency(const KvipFetchArgs& a, cudaStream_t stream);
 
 namespace {
 std::atomic<uint32_t> g_launches{0};
@@ -232,6 +233,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   rs.tokenBytes = s.tokenBytes;
   rs.source_bytes = (ws->options & KVIP_OPTION_DEFERRED_FETCH) ? 0 : ctx->source_bytes;  // descriptors only: the caller fetches
   rs.final_posts = ptr<KvipFinalPost>(ctx->final_posts);
+  rs.miss_mask = ptr<uint32_t>(ctx->miss_mask);
   KVIP_REQUIRE(rs.hot_valid && rs.reserved_hot && rs.lru_slots && rs.logical_ids && rs.addresses && rs.locations &&
                    rs.changes && rs.change_slots && rs.change_count && rs.events_src && rs.events_dst && rs.query_counts &&
                    rs.fetch_sources && rs.fetch_destinations && rs.row_status, "forward: a resolver operand is unbound");
@@ -240,10 +242,33 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   if (select_phase && (rc = launch_resolve_requests(rs, stream))) return rc;
   if (select_phase && (rc = stamp(KVIP_TIME_RESOLVE, false))) return rc;
   if (!commit_phase) return 0;
-  if ((rc = launch_publish_outputs(rs, stream))) return rc;
-  if ((rc = stamp(KVIP_TIME_OUTPUTS, false))) return rc;
+
+  // ---- commit phase: service outputs, Index exchange, fetch, gather ----------------------------------------
+  // Serial (default): all on `stream`, in that order. Overlapped (side stream, two events and the miss mask bound):
+  //     stream      : fork ................ fetch (copies only) ...... join -> publish residency -> gather(misses)
+  //     side stream :      outputs -> exchange -> gather(hits) -> join
+  // The fetch of a step with misses is bound by the host link and leaves HBM idle; the exchange and the gather of
+  // the entries that were hits touch neither the victim slots nor the fetch descriptors, so they run beside it.
+  // Residency is published after BOTH the exchange (which revokes freed positions) and the fetch have finished.
+  const bool fetch_runs = !(ws->options & KVIP_OPTION_DEFERRED_FETCH);
+  const bool overlapped = fetch_runs && ws->side_stream && ws->fork_event && ws->join_event && ctx->miss_mask && !ws->staging;
+  cudaStream_t side = overlapped ? reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(ws->side_stream)) : stream;
+  cudaEvent_t fork_event = reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->fork_event));
+  cudaEvent_t join_event = reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->join_event));
+  auto stamp_on = [&](cudaStream_t where, uint32_t index, bool skipped) -> uint32_t {
+    if (!times) return 0;
+    stage_stamp<<<1, 1, 0, where>>>(times, index, skipped && index ? 1u : 0u);
+    count_launch();
+    return check_launch("stage_stamp");
+  };
+  if (overlapped) {
+    if (cudaEventRecord(fork_event, stream) != cudaSuccess || cudaStreamWaitEvent(side, fork_event, 0) != cudaSuccess)
+      return check_launch("forward: forking the side stream");
+  }
+  if ((rc = launch_publish_outputs(rs, side))) return rc;
+  if ((rc = stamp_on(side, KVIP_TIME_OUTPUTS, false))) return rc;
   if (ws->slots_ready_event &&
-      cudaEventRecord(reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->slots_ready_event)), stream) != cudaSuccess)
+      cudaEventRecord(reinterpret_cast<cudaEvent_t>(static_cast<uintptr_t>(ws->slots_ready_event)), side) != cudaSuccess)
     return check_launch("forward: recording the slots-ready event");
 
   KvipExchangeArgs ex{};
@@ -255,31 +280,43 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   ex.batch = s.batch; ex.queries = s.queries; ex.history = s.history; ex.resident = s.resident;
   ex.address_stride = static_cast<uint32_t>(upd[7]); ex.key_row_bytes = s.keyDtype == KVIP_KEY_BF16 ? 256u : 128u;
   KVIP_REQUIRE(ex.keys && ex.scales && ex.addresses && ex.hot_valid && ex.shadow && ex.status, "forward: an update operand is unbound");
-  if ((rc = launch_exchange(ex, stream))) return rc;
-  if ((rc = stamp(KVIP_TIME_EXCHANGE, false))) return rc;
+  if ((rc = launch_exchange(ex, side))) return rc;
+  if ((rc = stamp_on(side, KVIP_TIME_EXCHANGE, false))) return rc;
 
-  if (!(ws->options & KVIP_OPTION_DEFERRED_FETCH)) {  // deferred fetch: descriptors only
-    KvipFetchArgs ft{};
-    ft.source_base = ptr<const uint8_t>(ctx->source_base); ft.fetch_sources = rs.fetch_sources;
-    ft.fetch_destinations = rs.fetch_destinations; ft.query_counts = rs.query_counts; ft.row_owners = rs.row_owners;
-    ft.row_status = rs.row_status; ft.pool = ptr<uint8_t>(ctx->pool); ft.hot_valid = ex.hot_valid;
-    ft.source_bytes = ctx->source_bytes; ft.batch = s.batch; ft.resident = s.resident; ft.outputStride = s.outputStride;
-    ft.tokenBytes = s.tokenBytes; ft.status = ex.status;
-    KVIP_REQUIRE(ft.source_base && ft.pool, "forward: the KV pools are unbound");
+  if (!fetch_runs) {  // deferred fetch: descriptors only
+    if ((rc = stamp(KVIP_TIME_FETCH, true))) return rc;
+    return stamp(KVIP_TIME_GATHER, true);
+  }
+  KvipFetchArgs ft{};
+  ft.source_base = ptr<const uint8_t>(ctx->source_base); ft.fetch_sources = rs.fetch_sources;
+  ft.fetch_destinations = rs.fetch_destinations; ft.query_counts = rs.query_counts; ft.row_owners = rs.row_owners;
+  ft.row_status = rs.row_status; ft.pool = ptr<uint8_t>(ctx->pool); ft.hot_valid = ex.hot_valid;
+  ft.source_bytes = ctx->source_bytes; ft.batch = s.batch; ft.resident = s.resident; ft.outputStride = s.outputStride;
+  ft.tokenBytes = s.tokenBytes; ft.status = ex.status; ft.defer_publication = overlapped ? 1u : 0u;
+  KVIP_REQUIRE(ft.source_base && ft.pool, "forward: the KV pools are unbound");
+  KvipGatherArgs ga{};
+  const bool gathers = s.gatherRows && ws->gather_out;
+  ga.pool = ft.pool; ga.slots = rs.locations; ga.row_owners = rs.row_owners; ga.out = ptr<uint8_t>(ws->gather_out);
+  ga.rows = s.batch * s.queries; ga.queries = s.queries; ga.outputStride = s.outputStride; ga.tokenBytes = s.tokenBytes;
+  if (!overlapped) {
     if ((rc = ws->staging ? launch_fetch_staged(ft, *ws, stream) : launch_fetch(ft, stream))) return rc;
     if ((rc = stamp(KVIP_TIME_FETCH, false))) return rc;
-    if (s.gatherRows && ws->gather_out) {
-      KvipGatherArgs ga{};
-      ga.pool = ft.pool; ga.slots = rs.locations; ga.row_owners = rs.row_owners; ga.out = ptr<uint8_t>(ws->gather_out);
-      ga.rows = s.batch * s.queries; ga.queries = s.queries; ga.outputStride = s.outputStride; ga.tokenBytes = s.tokenBytes;
-      if ((rc = launch_gather(ga, stream))) return rc;
-      if ((rc = stamp(KVIP_TIME_GATHER, false))) return rc;
-    } else if ((rc = stamp(KVIP_TIME_GATHER, true))) {
-      return rc;
-    }
-  } else {
-    if ((rc = stamp(KVIP_TIME_FETCH, true))) return rc;
-    if ((rc = stamp(KVIP_TIME_GATHER, true))) return rc;
+    if (gathers && (rc = launch_gather(ga, stream))) return rc;
+    return stamp(KVIP_TIME_GATHER, !gathers);
   }
-  return 0;
+  ga.miss_mask = rs.miss_mask;
+  if (gathers) {
+    ga.phase = 1u;   // entries that were hits: beside the fetch
+    if ((rc = launch_gather(ga, side))) return rc;
+  }
+  if (cudaEventRecord(join_event, side) != cudaSuccess) return check_launch("forward: recording the join event");
+  if ((rc = launch_fetch(ft, stream))) return rc;
+  if ((rc = stamp(KVIP_TIME_FETCH, false))) return rc;
+  if (cudaStreamWaitEvent(stream, join_event, 0) != cudaSuccess) return check_launch("forward: joining the side stream");
+  if ((rc = launch_publish_residency(ft, stream))) return rc;
+  if (gathers) {
+    ga.phase = 2u;   // entries the fetch has just filled
+    if ((rc = launch_gather(ga, stream))) return rc;
+  }
+  return stamp(KVIP_TIME_GATHER, !gathers);
 }

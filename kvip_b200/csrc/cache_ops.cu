@@ -28,6 +28,26 @@ __device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, 
   for (uint32_t p = lane + 96u; p < pieces; p += 32u) d[p] = __ldcs(s + p);
 }
 
+__device__ __forceinline__ bool descriptor_ok(const KvipFetchArgs& a, int64_t source, int32_t dest, uint32_t slot) {
+  return source >= 0 && static_cast<uint64_t>(source) + a.tokenBytes <= a.source_bytes && (source & 15) == 0 &&
+         dest >= 0 && slot < a.outputStride;
+}
+
+// hot_valid = 1 for every accepted descriptor; the second half of a fetch that ran with defer_publication.
+__global__ void __launch_bounds__(256) publish_residency(const KvipFetchArgs a) {
+  const uint32_t b = blockIdx.y;
+  if (a.row_status[b * 32u] != 0) return;
+  const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
+  const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < count; i += gridDim.x * 256u) {
+    const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
+    const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
+    const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
+    if (descriptor_ok(a, source, dest, slot) && slot < a.resident)
+      a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
+  }
+}
+
 __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs a) {
   const uint32_t b = blockIdx.y, lane = threadIdx.x & 31u;
   if (a.row_status[b * 32u] != 0) return;
@@ -38,8 +58,7 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs 
     const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
     const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
     const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
-    const bool ok = source >= 0 && static_cast<uint64_t>(source) + a.tokenBytes <= a.source_bytes &&
-                    (source & 15) == 0 && dest >= 0 && slot < a.outputStride;
+    const bool ok = descriptor_ok(a, source, dest, slot);
     if (!ok) {
       // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
       // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
@@ -53,7 +72,8 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs 
       continue;
     }
     copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
-    if (lane == 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
+    if (lane == 0 && slot < a.resident && !a.defer_publication)
+      a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
   }
 }
 
@@ -68,11 +88,20 @@ __global__ void __launch_bounds__(256) gather_rows(const KvipGatherArgs a) {
   const uint32_t k0 = (blockIdx.x * 8u + (threadIdx.x >> 5)) * kGatherPerWarp;
   const uint32_t b = row / a.queries;
   const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+  // two-phase gather: `wanted` has a bit per entry of this warp that belongs to the phase (hits first, beside the
+  // fetch; the entries the fetch fills afterwards)
+  uint32_t wanted = (1u << kGatherPerWarp) - 1u;
+  if (a.miss_mask && a.phase) {
+    const uint32_t missed = (a.miss_mask[static_cast<uint64_t>(row) * (kTop / 32u) + (k0 >> 5)] >> (k0 & 31u)) & wanted;
+    wanted = a.phase == 2u ? missed : (~missed & wanted);
+    if (!wanted) return;   // warp-uniform
+  }
   const int32_t my_slot = lane < kGatherPerWarp ? a.slots[static_cast<uint64_t>(row) * kTop + k0 + lane] : -1;
   const uint32_t pieces = a.tokenBytes >> 4;
   uint8_t* dst0 = a.out + (static_cast<uint64_t>(row) * kTop + k0) * a.tokenBytes;
   if (pieces > 96u) {  // rows beyond 1536 bytes: one entry after the other
     for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
+      if (!((wanted >> e) & 1u)) continue;
       const int32_t slot = __shfl_sync(0xffffffffu, my_slot, e);
       uint4* d = reinterpret_cast<uint4*>(dst0 + static_cast<uint64_t>(e) * a.tokenBytes);
       if (slot < 0 || static_cast<uint32_t>(slot) >= a.outputStride) {
@@ -89,7 +118,7 @@ __global__ void __launch_bounds__(256) gather_rows(const KvipGatherArgs a) {
 #pragma unroll
   for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
     const int32_t slot = __shfl_sync(0xffffffffu, my_slot, e);
-    const bool live = slot >= 0 && static_cast<uint32_t>(slot) < a.outputStride;
+    const bool live = slot >= 0 && static_cast<uint32_t>(slot) < a.outputStride && ((wanted >> e) & 1u);
     const uint4* s = reinterpret_cast<const uint4*>(
         a.pool + (static_cast<uint64_t>(owner) * a.outputStride + (live ? static_cast<uint32_t>(slot) : 0u)) * a.tokenBytes);
 #pragma unroll
@@ -98,6 +127,7 @@ __global__ void __launch_bounds__(256) gather_rows(const KvipGatherArgs a) {
   }
 #pragma unroll
   for (uint32_t e = 0; e < kGatherPerWarp; ++e) {
+    if (!((wanted >> e) & 1u)) continue;
     uint4* d = reinterpret_cast<uint4*>(dst0 + static_cast<uint64_t>(e) * a.tokenBytes);
 #pragma unroll
     for (uint32_t k = 0; k < 3; ++k)
@@ -340,6 +370,13 @@ uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream) {
   return check_launch("fetch_rows");
 }
 
+uint32_t launch_publish_residency(const KvipFetchArgs& a, cudaStream_t stream) {
+  dim3 grid(4, a.batch);
+  publish_residency<<<grid, 256, 0, stream>>>(a);
+  count_launch();
+  return check_launch("publish_residency");
+}
+
 uint32_t launch_gather(const KvipGatherArgs& a, cudaStream_t stream) {
   dim3 grid(kTop / (8u * kGatherPerWarp), a.rows);
   gather_rows<<<grid, 256, 0, stream>>>(a);
@@ -359,12 +396,20 @@ extern "C" uint32_t kvip_b200_fetch(const KvipFetchArgs* a, void* stream) {
   return kvip::launch_fetch(*a, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" uint32_t kvip_b200_publish_residency(const KvipFetchArgs* a, void* stream) {
+  KVIP_REQUIRE(a && a->fetch_sources && a->fetch_destinations && a->query_counts && a->row_status && a->hot_valid,
+               "publish_residency: null pointer");
+  KVIP_REQUIRE(a->batch >= 1 && a->outputStride >= a->resident, "publish_residency: geometry");
+  return kvip::launch_publish_residency(*a, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" uint32_t kvip_b200_gather(const KvipGatherArgs* a, void* stream) {
   KVIP_REQUIRE(a && a->pool && a->slots && a->out, "gather: null pointer");
   KVIP_REQUIRE(a->tokenBytes >= 16 && a->tokenBytes % 16 == 0, "gather: token bytes must be a multiple of 16");
   KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->pool) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->out) & 15u) == 0,
                "gather: pool and output must be 16-byte aligned");
   KVIP_REQUIRE(a->rows >= 1 && a->queries >= 1 && a->rows % a->queries == 0, "gather: rows must be batch*queries");
+  KVIP_REQUIRE(a->phase <= 2u && (a->phase == 0u || a->miss_mask), "gather: phases 1 and 2 need the miss mask");
   return kvip::launch_gather(*a, static_cast<cudaStream_t>(stream));
 }
 

@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
     change_slots[i] = i < kLruSlots ? lru[i] : -1;
   }
   if (tid < 8) ctl[tid] = 0;
+  if (a.miss_mask)
+    for (uint32_t i = tid; i < Q * (kTop / 32u); i += kThreads) a.miss_mask[static_cast<uint64_t>(b) * Q * (kTop / 32u) + i] = 0;
   __syncthreads();
 
   // ---- 1. classification of all queries ------------------------------------------------
@@ -122,6 +124,15 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
       where[q][j] = slot;
       if (q < Q) loc[q * kTop + tid * 2u + j] = slot;
     }
+  if (a.miss_mask) {
+    // bit k of a row: entry k is filled by this round's fetch. Entries 2*tid and 2*tid+1 are adjacent bits of one word.
+#pragma unroll
+    for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q) {
+      const uint32_t bits = (q < Q && token[q][0] >= 0 && where[q][0] == kMissing ? 1u : 0u) |
+                            (q < Q && token[q][1] >= 0 && where[q][1] == kMissing ? 2u : 0u);
+      if (bits) atomicOr(a.miss_mask + (static_cast<uint64_t>(b) * Q + q) * (kTop / 32u) + (tid >> 4), bits << ((tid & 15u) * 2u));
+    }
+  }
   __syncthreads();
 
   // ---- 2. queries in order ---------------------------------------------------------------

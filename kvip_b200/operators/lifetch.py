@@ -216,6 +216,8 @@ class CudaBinding:
         self.reserved_hot.fill_(-1)
         # one 128-byte record per (request, query): count, first descriptor, error (include/kvip_b200.h: KvipFinalPost)
         self.final_posts = torch.zeros((batch * self.final_workers, 32), dtype=torch.int32, device=self.device)
+        # one bit per TopK entry: filled by this round's fetch (lets the gather run in two phases around the fetch)
+        self.miss_mask = torch.zeros((batch * queries, TOPK // 32), dtype=torch.int32, device=self.device)
         self.mapping = self.final_status = self.prefetch_status = None
         self.output, self.query_ends, self.hot_valid, self.row_owners = output, query_ends, hot_valid, row_owners
         self.token_addresses, self.tail_bounds, self.gather_output = token_addresses, tail_bounds, gather_output
@@ -261,7 +263,7 @@ class CudaBinding:
             tail_bounds=0 if tail_bounds is None else tail_bounds.data_ptr(),
             row_status=self.row_status.data_ptr(), query_counts=self.query_counts.data_ptr(),
             pool=output.data_ptr(), source_base=source_base, source_bytes=source_bytes, shape=self.runtime_shape,
-            final_posts=self.final_posts.data_ptr())
+            final_posts=self.final_posts.data_ptr(), miss_mask=self.miss_mask.data_ptr())
         self.context = _host_blob(torch, bytes(context))
         self.arguments = tuple(arguments) + (self.context,)
         self.bindings = None  # completed by LIFetch (needs the workspace record)
@@ -342,7 +344,7 @@ class LIFetch:
     inputs and writes no output row, `commit()` reads no query input."""
 
     def __init__(self, rotating, update, *, q_workers=2, lru=None, prefetch_limit=None, prefetch_windows=3, prefetch_ctas=0,
-                 prefetch_last_window=False):
+                 prefetch_last_window=False, overlap_fetch=False):
         if rotating.device != update.device:
             raise ValueError("Fetch and Index update must use the same device")
         if update.bindings.numel() != 28:
@@ -356,15 +358,22 @@ class LIFetch:
         self.shape_pointer = ctypes.byref(shape)
         self.q_workers, self.prefetch_limit = q_workers, 0
         self.lru = lru
-        self._slots_ready = self._lru_done = self._side = None
-        if lru is not None:
-            if lru.device != rotating.device or lru.rows_count != self.batch:
-                raise ValueError("the SlotLRU must have one row per request on the cache device")
-            current = torch.cuda.current_stream(rotating.device)
+        self._slots_ready = self._lru_done = self._side = self._fork = self._join = None
+        self.overlap_fetch = bool(overlap_fetch)
+        current = torch.cuda.current_stream(rotating.device)
+        if lru is not None and (lru.device != rotating.device or lru.rows_count != self.batch):
+            raise ValueError("the SlotLRU must have one row per request on the cache device")
+        if lru is not None or overlap_fetch:
             self._side = torch.cuda.Stream(rotating.device)
             self._slots_ready, self._lru_done = torch.cuda.Event(), torch.cuda.Event()
             self._slots_ready.record(current)   # an event has no handle before its first record
             self._lru_done.record(current)
+        if overlap_fetch:
+            # the commit phase forks here: outputs, Index exchange and the gather of the hit entries run on the side
+            # stream beside the fetch of the missing rows (include/kvip_b200.h: KvipWorkspace.side_stream)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+            self._fork.record(current)
+            self._join.record(current)
         library = rotating.library
         self.resolver_cores, flag_count = int(library.kvip_streaming_resolver_cores()), int(library.kvip_streaming_flag_count())
         if self.resolver_cores != 3 or flag_count != 16:
@@ -398,7 +407,10 @@ class LIFetch:
             query_errors=0, update_bindings=update.bindings.data_ptr(), dense_shadow=self.dense_shadow.data_ptr(),
             packed_fetch=0, gather_out=0 if rotating.gather_output is None else rotating.gather_output.data_ptr(),
             topk_scores=0, li_status=self.li_status.data_ptr(), topk_histogram=0, topk_split=0,
-            slots_ready_event=0 if self._slots_ready is None else int(self._slots_ready.cuda_event))
+            slots_ready_event=0 if self._slots_ready is None or lru is None else int(self._slots_ready.cuda_event),
+            side_stream=int(self._side.cuda_stream) if overlap_fetch else 0,
+            fork_event=int(self._fork.cuda_event) if overlap_fetch else 0,
+            join_event=int(self._join.cuda_event) if overlap_fetch else 0)
         self.workspace = _host_blob(torch, bytes(workspace))
         words = [x.data_ptr() for x in rotating.arguments] + [self.workspace.data_ptr()]
         rotating.bindings = torch.from_numpy(np.asarray(words, dtype="<u8").view("<i8").copy())
@@ -428,7 +440,8 @@ class LIFetch:
         if result:
             raise RuntimeError(f"streaming LIFetch launch failed: {result} ({_lib.last_error(self.rotating.library)})")
         if self.lru is not None and not phase & _lib.OPTION_SELECT_ONLY:
-            # fork: LRU feedback beside fetch + gather; join before the caller's next work on this stream
+            # fork: LRU feedback beside fetch + gather; join before the caller's next work on this stream. (With
+            # overlap_fetch the side stream already carries the output rows: the wait is then a no-op.)
             self._side.wait_event(self._slots_ready)
             with self.torch.cuda.stream(self._side):
                 self.lru.commit(self.update.slot_output.view(self.batch, -1))

@@ -299,6 +299,54 @@ def test_two_phase_call_and_serial_lru_equal_the_fused_call(device):
         assert int(fused.update.status.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("host_pool", [False, True])
+def test_overlapped_commit_phase_equals_the_serial_one(host_pool, device):
+    """`LIFetch(overlap_fetch=True)`: outputs, Index exchange and the gather of the hit entries run on a side stream
+    beside the fetch of the missing rows; residency is published and the missed entries are gathered after both.
+    Every observable result must equal the serial call's over steps with misses, evictions and repeats - eagerly
+    and replayed from one CUDA graph (the fork and the join are part of the capture)."""
+    config = dict(batch=3, queries=2, heads=64, history=12288, resident=4096, len_lo=9000, len_hi=12288, key_dtype="fp8",
+                  weight_dtype="bf16", token_bytes=1152, seed=21, host_pool=host_pool, fill_payload=True)
+    serial = DecodePipeline(device, **config)
+    overlapped = DecodePipeline(device, overlap_fetch=True, **config)
+    stream = torch.cuda.Stream(device)
+    try:
+        with torch.cuda.stream(stream):
+            graph = None
+            for step, seed in enumerate((21, 22, 23, 21, 24, 22)):
+                for p in (serial, overlapped):
+                    p.new_queries(seed)
+                serial.step()
+                if graph is None:
+                    overlapped.step()
+                else:
+                    graph.replay()
+                stream.synchronize()
+                for name in ("outputs",):
+                    assert torch.equal(getattr(serial.update, name), getattr(overlapped.update, name)), (step, name)
+                assert torch.equal(serial.gather_out, overlapped.gather_out), step
+                assert torch.equal(serial.pool_hbm, overlapped.pool_hbm), step
+                assert torch.equal(serial.storage.hot_valid, overlapped.storage.hot_valid), step
+                assert torch.equal(serial.storage.logical_ids, overlapped.storage.logical_ids), step
+                assert torch.equal(serial.storage.keys, overlapped.storage.keys), step
+                assert torch.equal(serial.lru.order, overlapped.lru.order), step
+                assert torch.equal(serial.rotating.query_counts, overlapped.rotating.query_counts), step
+                assert int(overlapped.update.status.abs().sum()) == 0
+                if step == 0:
+                    assert int(serial.rotating.query_counts[:, 4].sum()) > 0, "the case must have misses"
+                    # the miss mask marks exactly the entries whose slot this step's fetch filled
+                    mask = overlapped.rotating.miss_mask.cpu().numpy().view(np.uint32)
+                    bits = ((mask[:, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(mask.shape[0], TOPK)
+                    assert bits.sum() == 3 * 2 * TOPK, "an empty pool misses every entry"
+                if step == 1:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):   # recorded, not run: the states stay equal
+                        overlapped.step()
+    finally:
+        serial.close()
+        overlapped.close()
+
+
 def _host_inputs(p):
     inputs = p.workspace.inputs
     pin = lambda t: t.cpu().pin_memory()  # noqa: E731
