@@ -11,8 +11,12 @@ namespace {
 // warp issues three fully coalesced 512-byte requests (the last one 128 bytes). The source is
 // read through the device alias of pinned, mapped host memory; each request crosses the host
 // link once and lands in the resident HBM slot.
+// The descriptors of all requests form one flat list that the warps of a SMALL grid deal out round-robin: the
+// host link, not the GPU, sets the pace (about 50 GB/s), 512 warps keep several hundred KB in flight, and a grid
+// that leaves most SMs untouched lets the Index exchange (whose 1024-thread CTAs need an SM to themselves) and the
+// gather of the hit entries run beside the fetch.
 constexpr uint32_t kFetchThreads = 256;
-constexpr uint32_t kFetchBlocksPerRequest = 16;
+constexpr uint32_t kFetchBlocks = 64;
 
 __device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, uint32_t bytes, uint32_t lane) {
   const uint32_t pieces = bytes >> 4;
@@ -49,31 +53,35 @@ __global__ void __launch_bounds__(256) publish_residency(const KvipFetchArgs a) 
 }
 
 __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs a) {
-  const uint32_t b = blockIdx.y, lane = threadIdx.x & 31u;
-  if (a.row_status[b * 32u] != 0) return;
-  const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
-  const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+  const uint32_t lane = threadIdx.x & 31u;
   const uint32_t warps = gridDim.x * (kFetchThreads / 32u);
-  for (uint32_t i = blockIdx.x * (kFetchThreads / 32u) + (threadIdx.x >> 5); i < count; i += warps) {
-    const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
-    const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
-    const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
-    const bool ok = descriptor_ok(a, source, dest, slot);
-    if (!ok) {
-      // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
-      // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
-      // it is revoked, and the request's update status gets the reference's code for a failed publication
-      // (CompleteEarlyUpdate, index_cache_update.h:6-20).
-      if (lane == 0) {
-        atomicOr(a.row_status + b * 32u + 2, 1);
-        if (a.status) atomicOr(a.status + b, 4);
-        if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
+  const uint32_t me = blockIdx.x * (kFetchThreads / 32u) + (threadIdx.x >> 5);
+  uint32_t offset = 0;   // descriptors of the earlier requests, modulo the number of warps
+  for (uint32_t b = 0; b < a.batch; ++b) {
+    if (a.row_status[b * 32u] != 0) continue;   // a failed request moves nothing
+    const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
+    const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
+    for (uint32_t i = (me + warps - offset) % warps; i < count; i += warps) {
+      const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
+      const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
+      const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
+      if (!descriptor_ok(a, source, dest, slot)) {
+        // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
+        // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
+        // it is revoked, and the request's update status gets the reference's code for a failed publication
+        // (CompleteEarlyUpdate, index_cache_update.h:6-20).
+        if (lane == 0) {
+          atomicOr(a.row_status + b * 32u + 2, 1);
+          if (a.status) atomicOr(a.status + b, 4);
+          if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
+        }
+        continue;
       }
-      continue;
+      copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
+      if (lane == 0 && slot < a.resident && !a.defer_publication)
+        a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
     }
-    copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
-    if (lane == 0 && slot < a.resident && !a.defer_publication)
-      a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
+    offset = (offset + count) % warps;
   }
 }
 
@@ -364,8 +372,7 @@ __global__ void __launch_bounds__(128) publish_pages(const KvipPagesArgs a) {
 }  // namespace
 
 uint32_t launch_fetch(const KvipFetchArgs& a, cudaStream_t stream) {
-  dim3 grid(kFetchBlocksPerRequest, a.batch);
-  fetch_rows<<<grid, kFetchThreads, 0, stream>>>(a);
+  fetch_rows<<<kFetchBlocks, kFetchThreads, 0, stream>>>(a);
   count_launch();
   return check_launch("fetch_rows");
 }
