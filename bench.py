@@ -149,14 +149,14 @@ def run_ours(args):
     lib = _lib.load_library()
     miss_source = "device tensor" if args.device_source else "pinned mapped host pool"
     try:
-        p = DecodePipeline(device, seed=rank, gather=True, host_pool=not args.device_source, **cfg)
+        p = DecodePipeline(device, seed=rank, gather=True, host_pool=not args.device_source, head_sum=args.head_sum, **cfg)
     except (RuntimeError, MemoryError) as failure:
         # the host pool of one rank is owners x history x token_bytes (9.7 GB at the headline): when the box cannot
         # pin that much for every rank, the miss rows come from a device tensor instead, and the line says so
         if args.device_source:
             raise
         torch.cuda.empty_cache()
-        p = DecodePipeline(device, seed=rank, gather=True, host_pool=False, **cfg)
+        p = DecodePipeline(device, seed=rank, gather=True, host_pool=False, head_sum=args.head_sum, **cfg)
         miss_source = f"device tensor (host pool unavailable: {str(failure)[:80]})"
     stream = torch.cuda.Stream(device)
     tokens = p.query_tokens()
@@ -221,7 +221,7 @@ def run_ours(args):
         li = lambda: ops.li_score(inputs.query, keys_view.view(-1, 128), inputs.weights,  # noqa: E731
                                   inputs.scale if p.key_dtype == "fp8" else None,
                                   s.scales.view(-1) if p.key_dtype == "fp8" else None, ws.key_lengths, qe2d,
-                                  inputs.block_table, ws.scores, status=p.forward.li_status)
+                                  inputs.block_table, ws.scores, status=p.forward.li_status, head_sum=args.head_sum)
         tk = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048))  # noqa: E731
         ga = lambda: ops.gather(p.pool_hbm, p.update.slot_output.view(-1, 2048), p.gather_out,  # noqa: E731
                                 queries=p.queries, output_stride=p.output_stride, token_bytes=p.token_bytes,
@@ -751,7 +751,7 @@ def run_prefill(args):
     def li(part):
         lo, hi = part * rows, (part + 1) * rows
         ops.li_score(query[lo:hi], keys, weights[lo:hi], query_scale[lo:hi], key_scale, key_lengths,
-                     ends[lo // 4:hi // 4], table, scores, status=status)
+                     ends[lo // 4:hi // 4], table, scores, status=status, head_sum=args.head_sum)
 
     def step(li_only=False):
         for part in range(chunk // rows):
@@ -1113,6 +1113,8 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch",
                                                        "decode_128k_b32_zipf"], default="decode_128k_b64")
+    parser.add_argument("--head-sum", type=int, default=0, choices=(0, 1, 2),
+                        help="how the score kernel reads accumulators back: 0 = automatic, 1 = rows, 2 = quads")
     parser.add_argument("--reuse", type=float, default=0.75,
                         help="decode_128k_b32_zipf: share of a selection kept from the previous step")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")

@@ -61,11 +61,13 @@ extern "C" {
 enum { KVIP_KEY_FP8_E4M3 = 0, KVIP_KEY_BF16 = 1 };
 enum { KVIP_WEIGHT_BF16 = 0, KVIP_WEIGHT_FP32 = 1 };
 enum { KVIP_SCORE_FP32 = 0, KVIP_SCORE_BF16_AWAY = 1 };
-/* The weighted sum over index heads: on the CUDA cores in fp32 (the reference's arithmetic,
- * indexer_score.h:59-140), or on the tensor core as a second, small MMA over bf16-rounded operands (wide query
- * tiles only; fp32 score mode only). AUTO picks the tensor core when a key page meets 128 or more
- * (query, head) columns, where the register reduction and not HBM sets the pace. */
-enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_REGISTERS = 1, KVIP_HEAD_SUM_TENSOR = 2 };
+/* How the tcgen05 kernel reads an accumulator back for the weighted sum over index heads (fp32 arithmetic either
+ * way; the order of the additions differs, inside every tolerance stated for this kernel). ROWS: a thread owns a
+ * token row and walks the columns; the head weights are warp-uniform shared-memory reads. QUADS: a thread owns two
+ * adjacent columns of every eight for four rows (the MMA fragment layout) and a quarter of the weights; four lanes
+ * add their partial sums with shuffles. AUTO: QUADS when a key page meets 128 or more (query, head) columns, where
+ * the weight reads of ROWS and not HBM set the pace; ROWS otherwise. */
+enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_ROWS = 1, KVIP_HEAD_SUM_QUADS = 2 };
 
 /* Geometry bound before graph capture. Same size (80 bytes, 20 x u32) and the same
  * leading fields as rotating::RuntimeShape (include/runtime_shape.h:5-27); the fields
@@ -118,7 +120,7 @@ typedef struct KvipLiArgs {
                                  KVIP_ERR_PIPELINE in *status; 0 in production */
   uint32_t wait_kilocycles;   /* limit of every barrier wait inside the kernel, in units of 1024 SM clock cycles;
                                  0 = the default of about one second */
-  uint32_t head_sum;          /* KVIP_HEAD_SUM_*: where the weighted sum over heads is computed */
+  uint32_t head_sum;          /* KVIP_HEAD_SUM_*: how accumulators are read back for the sum over heads */
 } KvipLiArgs;
 uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
 /* CUDA-core restatement of the same formula with the oracle's accumulation order;

@@ -21,13 +21,14 @@
 //     accumulators, and the number of units reduced at once divides the number of accumulators, so
 //     every use of one stage or accumulator is waited for by the same thread, in order: a
 //     parity wait by a thread that runs a whole phase ahead of the barrier would pass at once;
-//   * wide query tiles (128 or more (query, head) columns per key page) leave the register reduction, not HBM,
-//     in charge of the pace: every head weight is a warp-uniform shared-memory read. For them the weighted sum
-//     over heads runs on the tensor core as well (fp32 score mode): the epilogue writes ReLU(acc) back to tensor
-//     memory as packed bf16 (in place, over the accumulator's own columns), an issuer multiplies that tile - the
-//     A operand, read from tensor memory - with a [columns x 16] matrix of the request's head weights in shared
-//     memory (two columns per query slot: the bf16 head and tail of the fp32 weight), and the epilogue reads the
-//     two sums per query slot back, adds them and applies the key scale. What is rounded is ReLU(acc), to bf16;
+//   * two ways to read an accumulator back for the reduction over heads. ROWS: a thread owns one token row and
+//     walks its columns (tcgen05.ld 32x32b); every head weight is then the same for all lanes of a warp and
+//     comes from shared memory, one 16-byte broadcast load per four columns. At 64 columns per key page that
+//     hides under the HBM time of the page; at 128 or more it is what sets the pace (a 16-byte load by 32 lanes
+//     costs four shared-memory wavefronts whatever the addresses). QUADS: tcgen05.ld 16x256b hands a thread two
+//     adjacent columns out of every eight, for four token rows; a lane then needs only a quarter of the head
+//     weights (16 of 64), which it loads once per query slot, and the four lanes that share a row add their
+//     partial sums with two shuffles. Same arithmetic in fp32, a quarter of the shared-memory traffic;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
 //     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
 //     is released and the kernel returns.
@@ -48,13 +49,6 @@ constexpr uint32_t kMaxBatch = 1024;
 constexpr uint32_t kMaxN = 256;            // query slots * heads
 constexpr uint32_t kAtomBytes = 128 * 128; // one 128-row x 128-byte swizzle atom
 constexpr uint32_t kDefaultWaitKilocycles = 2000000u;  // about one second of SM clock
-// tensor-core head sum: units of 128 accumulator columns; packed bf16 ReLU(acc) in columns [0, 64) of the unit, the
-// [128 x 16] result of the second MMA in columns [64, 80); one 16-row weight matrix (4 KiB, two swizzle atoms) per
-// accumulator in shared memory
-constexpr uint32_t kSumColumn = 64;
-constexpr uint32_t kSumN = 16;
-constexpr uint32_t kWmatBytes = kSumN * 128u * 2u;
-constexpr uint32_t kTensorAcc = 4;
 
 template <bool kBf16> struct LiCfg {
   static constexpr uint32_t kAtoms = kBf16 ? 2 : 1;           // 128-byte K slices per row
@@ -64,7 +58,6 @@ template <bool kBf16> struct LiCfg {
   // everything but the key stages, for `n` = query slots x heads accumulator columns
   static constexpr uint32_t fixed_bytes(uint32_t n) {
     return 1024 /*alignment slack*/ + 1024 /*barriers*/ + n * 128 * kAtoms /*query tile*/ +
-           (n >= 128 ? kTensorAcc * kWmatBytes : 0) /*weight matrices of the tensor-core head sum*/ +
            4 * kEpilogueGroups * n * 4 /*W per epilogue warp*/ + (kMaxBatch + 1) * 4 /*tile prefix*/ +
            kMaxBatch /*active queries*/ + 64;
   }
@@ -166,40 +159,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+// 16 lanes x 64 columns of fp32 in the fragment layout of an MMA accumulator: with g = lane / 4 and t = lane % 4,
+// registers 4k .. 4k+3 hold (row g, columns 8k + 2t and 8k + 2t + 1) and (row g + 8, the same two columns).
+__device__ __forceinline__ void tmem_ld_16x256_x8(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_16x256_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
-      : "memory");
-}
-// 32 lanes x 16 columns: thread i of the warp writes row (lane base + i).
-__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-// {ReLU(hi), ReLU(lo)} rounded to nearest-even bf16, packed: `lo` lands in the lower half (the even K index)
-__device__ __forceinline__ uint32_t relu_bf16x2(uint32_t lo, uint32_t hi) {
-  uint32_t packed;
-  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
-  return packed;
-}
-// D[tmem] (+)= A[tmem, bf16, one row per lane] x B[smem descriptor, bf16]
-__device__ __forceinline__ void tcgen05_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                                   uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
@@ -238,9 +219,8 @@ __device__ __forceinline__ float load_weight(const KvipLiArgs& a, uint32_t index
   return w;
 }
 
-// kTensorSum: the instantiation for wide query tiles (128 or more columns, fp32 scores) whose weighted sum over heads
-// runs on the tensor core; the other instantiation carries none of that code.
-template <bool kBf16, bool kTensorSum>
+// kQuads: the epilogue reads accumulators in the 16x256b fragment layout (see the header comment).
+template <bool kBf16, bool kQuads>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap query_map,
                  const __grid_constant__ KvipLiArgs a, const uint32_t S) {
@@ -257,22 +237,15 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t n_max = a.queries * a.heads;  // accumulator columns / query-tile rows of this launch
   const uint32_t q_atom_bytes = n_max * 128u;  // one 128-byte K slice of the query tile
   const uint32_t q_smem = key_smem + S * Cfg::kTileBytes;
-  // tensor-core head sum: where it applies, and its weight matrices right behind the query tile (1024-byte aligned)
-  constexpr bool tensor_sum = kTensorSum;
-  const uint32_t wmat_bytes = n_max >= 128u ? kTensorAcc * kWmatBytes : 0u;
-  const uint32_t wmat_offset = 1024u + S * Cfg::kTileBytes + q_atom_bytes * Cfg::kAtoms;
-  const uint32_t wmat_smem = base + wmat_offset;
-  float* w_smem = reinterpret_cast<float*>(smem + wmat_offset + wmat_bytes);
+  float* w_smem = reinterpret_cast<float*>(smem + 1024u + S * Cfg::kTileBytes + q_atom_bytes * Cfg::kAtoms);
   uint32_t* prefix = reinterpret_cast<uint32_t*>(w_smem + 4 * kEpilogueGroups * n_max);
   uint8_t* active_q = reinterpret_cast<uint8_t*>(prefix + kMaxBatch + 1);
   // barrier map: [0,S) full, [S,2S) empty, 2S q_full, 2S+1 q_empty, then kMaxAcc tmem_full and kMaxAcc
   // tmem_empty; then the tmem base word and the abort flag.
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
-  // (for the tensor-core head sum: kMaxAcc p_ready - the packed tile is written - and kMaxAcc sum_full)
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 + 4 * kMaxAcc);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 2 + 2 * kMaxAcc);
   const uint32_t kQFull = 2 * S, kQEmpty = 2 * S + 1, kAccFull = 2 * S + 2, kAccEmpty = 2 * S + 2 + kMaxAcc;
-  const uint32_t kPReady = kAccEmpty + kMaxAcc, kSumFull = kPReady + kMaxAcc;
   volatile uint32_t* abort_flag = tmem_slot + 1;
   const WaitControl waits{abort_flag, static_cast<long long>(a.wait_kilocycles ? a.wait_kilocycles : kDefaultWaitKilocycles) << 10};
 
@@ -322,10 +295,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   if (threadIdx.x == 64) {
     for (uint32_t i = 0; i < S; ++i) { mbar_init(bar(i), 1); mbar_init(bar(S + i), 1); }
     mbar_init(bar(kQFull), 1); mbar_init(bar(kQEmpty), issuers);
-    for (uint32_t i = 0; i < kMaxAcc; ++i) {
-      mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128u);
-      mbar_init(bar(kPReady + i), 128u); mbar_init(bar(kSumFull + i), 1);
-    }
+    for (uint32_t i = 0; i < kMaxAcc; ++i) { mbar_init(bar(kAccFull + i), 1); mbar_init(bar(kAccEmpty + i), 128u); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -419,42 +389,13 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       uint32_t stage = w, phase = 0;                           // w < issuers <= S
       uint32_t acc = w * halves, acc_phase = 0;                // first unit of tile w; w * halves < acc_count
       bool alive = true;
-      // Tensor-core head sum: a unit whose first MMA has been issued is owed a second one (packed ReLU tile x
-      // weight matrix) once the epilogue has written the packed tile. It is issued before this thread next waits
-      // for anything else, at the latest before the unit's accumulator is reused.
-      uint32_t owed = 0, ready_phase = 0;                      // bit per accumulator
-      uint64_t owed_steps = 0;                                 // byte per accumulator: K steps of its second MMA
-      auto second_mma = [&]() -> bool {
-        while (owed) {
-          const uint32_t i = static_cast<uint32_t>(__ffs(owed)) - 1u;
-          if (!mbar_wait(bar(kPReady + i), (ready_phase >> i) & 1u, waits)) return false;
-          ready_phase ^= 1u << i;
-          owed &= owed - 1u;
-          tcgen05_fence_after();
-          const uint32_t unit = tmem_base + i * acc_stride;
-          const uint32_t idesc2 = (1u << 4) | (1u << 7) | (1u << 10) | ((kSumN >> 3) << 17) | ((128u >> 4) << 24);
-          const uint32_t steps = static_cast<uint32_t>(owed_steps >> (8u * i)) & 0xffu;   // columns / 16
-          for (uint32_t s = 0; s < steps; ++s) {
-            const uint64_t db = umma_desc(wmat_smem + i * kWmatBytes + (s >> 2) * (kWmatBytes / 2u)) + 2u * (s & 3u);
-            tcgen05_mma_a_tmem(unit + kSumColumn, unit + s * 8u, db, idesc2, s != 0u);
-          }
-          tcgen05_commit(bar(kSumFull + i));
-        }
-        return true;
-      };
       while (alive) {
         const uint32_t request_end = min(prefix[request + 1], tile_end);
-        if constexpr (tensor_sum) {
-          if (!second_mma()) break;   // before waiting for the next request's query tile
-        }
         if (!mbar_wait(bar(kQFull), seq & 1u, waits)) break;
         const uint32_t n = active_q[request] * H;              // live accumulator columns of this request
         const uint32_t fmt = kBf16 ? 1u : 0u;  // kind::f16: BF16 = 1; kind::f8f6f4: E4M3 = 0
         bool issued = false;
         for (; t < request_end; t += issuers) {
-          if constexpr (tensor_sum) {
-            if (!second_mma()) { alive = false; break; }
-          }
           if (!mbar_wait(bar(stage), phase, waits)) { alive = false; break; }
           for (uint32_t h = 0; h < halves; ++h) {
             if (!mbar_wait(bar(kAccEmpty + acc + h), acc_phase ^ 1u, waits)) { alive = false; break; }
@@ -476,10 +417,6 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
                 tcgen05_mma<kBf16>(d_tmem, da + 2u * k, db + 2u * k, idesc, (atom | k) != 0u);
             }
             tcgen05_commit(bar(kAccFull + acc + h));   // accumulator ready for the epilogue
-            if constexpr (tensor_sum) {
-              owed |= 1u << (acc + h);
-              owed_steps = (owed_steps & ~(0xffull << (8u * (acc + h)))) | (static_cast<uint64_t>(columns / 16u) << (8u * (acc + h)));
-            }
           }
           if (!alive) break;
           tcgen05_commit(bar(S + stage));              // key stage free once these MMAs retire
@@ -496,9 +433,6 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         do { ++request; } while (prefix[request + 1] == prefix[request]);  // next request that has tiles
         ++seq;
       }
-      if constexpr (tensor_sum) {
-        if (alive) second_mma();   // the units of this thread's last tile
-      }
     }
   } else {
     // ================= epilogue: groups of 4 warps, one token row per thread =================
@@ -506,7 +440,9 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     // far longer than the time the next key page needs to arrive, so several units are reduced concurrently.
     const uint32_t group = (warp - kFirstEpilogueWarp) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
-    const uint32_t row = quad * 32u + lane;       // token row inside the page
+    // the token row (inside the page) whose score this thread scales and stores. ROWS: the row it reduced. QUADS: the
+    // four lanes of a group reduce rows g, g + 8, g + 16, g + 24 of the quadrant together; lane t of them keeps row g + 8t
+    const uint32_t row = quad * 32u + (kQuads ? (lane >> 2) + 8u * (lane & 3u) : lane);
     float* w_warp = w_smem + (warp - kFirstEpilogueWarp) * n_max;  // private copy: no cross-warp barrier needed
     TileCursor cur(prefix, a.batch), ahead(prefix, a.batch);
     uint32_t live_mask = 0;
@@ -531,8 +467,6 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     float kscale = scale_of(tile_of(first), page_next);
     page_next = page_of(tile_of(first + G));
     uint32_t acc = group % acc_count, acc_phase = 0;   // G divides acc_count: a group meets the same accumulators
-    uint32_t sum_phase = 0;                            // bit per accumulator: parity of its next sum_full wait
-    int32_t matrix_of = -1;                            // (request, half) whose weights this group's matrix holds
     for (uint32_t u = first; u < units_here; u += G) {
       const uint32_t t = tile_begin + u / halves, h = u % halves;
       const uint32_t b = cur.seek(t);
@@ -541,8 +475,15 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       page_next = page_of(tile_of(u + 2 * G));
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
-        if constexpr (!tensor_sum)
+        if constexpr (kQuads) {
+          // lane t of a group needs heads 8k + 2t and 8k + 2t + 1: stored as H / 4 consecutive floats per (slot, t)
+          for (uint32_t i = lane; i < nq * H; i += 32u) {
+            const uint32_t q = i / H, head = i % H;
+            w_warp[q * H + ((head >> 1) & 3u) * (H / 4u) + (head >> 3) * 2u + (head & 1u)] = load_weight(a, b * Q * H + i);
+          }
+        } else {
           for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
+        }
         live_mask = 0;
         for (uint32_t q = 0; q < nq; ++q) live_mask |= (a.query_ends[b * Q + q] > 0 ? 1u : 0u) << q;
         __syncwarp();
@@ -554,61 +495,62 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
       const uint32_t q_first = h * unit_queries, q_last = min(nq, q_first + unit_queries);
-      if constexpr (tensor_sum) { if (q_first < q_last) {
-        // ---- weighted sum over heads on the tensor core -------------------------------------------------
-        // 1. this unit's weight matrix, when the (request, half) changed: row 2j = bf16 head of query slot j's
-        //    weights over its own columns (zero elsewhere), row 2j + 1 = the bf16 tail; K-major, 128-byte swizzle.
-        //    The matrix of this accumulator is free: the group waited for its last second MMA before it got here.
-        const int32_t wanted_matrix = static_cast<int32_t>(b * 2u + h);
-        if (matrix_of != wanted_matrix) {
-          uint8_t* matrix = smem + wmat_offset + acc * kWmatBytes;
-          for (uint32_t chunk = row; chunk < kWmatBytes / 16u; chunk += 128u) {   // 16-byte chunks: 8 columns of a row
-            const uint32_t atom = chunk >> 7, r = (chunk & 127u) >> 3, j = chunk & 7u;
-            const uint32_t column = atom * 64u + j * 8u, slot = column / H, q = q_first + slot;
-            uint32_t packed[4] = {0u, 0u, 0u, 0u};
-            if ((r >> 1) == slot && q < q_last) {
+      if constexpr (kQuads) {
+        const uint32_t t4 = lane & 3u;
+        for (uint32_t q = q_first; q < q_last; ++q) {
+          // this lane's quarter of the slot's head weights (16 of 64, or 8 of 32)
+          float w[16];
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + t4 * (H / 4u));
 #pragma unroll
-              for (uint32_t e = 0; e < 8u; ++e) {
-                const float weight = load_weight(a, (b * Q + q) * H + (column % H) + e);
-                __nv_bfloat16 part = __float2bfloat16_rn(weight);
-                if (r & 1u) part = __float2bfloat16_rn(weight - __bfloat162float(part));
-                packed[e >> 1] |= static_cast<uint32_t>(__bfloat16_as_ushort(part)) << (16u * (e & 1u));
+          for (uint32_t j = 0; j < 4; ++j) {
+            const float4 x = j * 4u < H / 4u ? w4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[4 * j] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
+          }
+          float sums[4];
+#pragma unroll
+          for (uint32_t half = 0; half < 2; ++half) {   // rows g, g + 8 of lanes 0-15, then of lanes 16-31 of the quadrant
+            float even0 = 0.f, odd0 = 0.f, even1 = 0.f, odd1 = 0.f;
+            const uint32_t at = taddr + ((half * 16u) << 16) + (q - q_first) * H;
+            if (H == 64u) {
+              uint32_t v[32];
+              tmem_ld_16x256_x8(at, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (uint32_t k = 0; k < 8; ++k) {
+                even0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 0]), 0.f), w[2 * k], even0);
+                odd0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 1]), 0.f), w[2 * k + 1], odd0);
+                even1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 2]), 0.f), w[2 * k], even1);
+                odd1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 3]), 0.f), w[2 * k + 1], odd1);
+              }
+            } else {
+              uint32_t v[16];
+              tmem_ld_16x256_x4(at, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (uint32_t k = 0; k < 4; ++k) {
+                even0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 0]), 0.f), w[2 * k], even0);
+                odd0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 1]), 0.f), w[2 * k + 1], odd0);
+                even1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 2]), 0.f), w[2 * k], even1);
+                odd1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 3]), 0.f), w[2 * k + 1], odd1);
               }
             }
-            *reinterpret_cast<uint4*>(matrix + atom * (kWmatBytes / 2u) + (r >> 3) * 1024u + (r & 7u) * 128u +
-                                      ((j ^ (r & 7u)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            sums[2 * half] = even0 + odd0;
+            sums[2 * half + 1] = even1 + odd1;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
-          matrix_of = wanted_matrix;
-        }
-        // 2. ReLU(acc) -> packed bf16, in place: columns [c, c + 32) are read before [c / 2, c / 2 + 16) are written
-        const uint32_t columns = (q_last - q_first) * H;
-        for (uint32_t c = 0; c < columns; c += 32u) {
-          uint32_t v[32], packed[16];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
+          // the four lanes of a group hold the four quarters of every row's sum
 #pragma unroll
-          for (uint32_t i = 0; i < 16u; ++i) packed[i] = relu_bf16x2(v[2u * i], v[2u * i + 1u]);
-          tmem_st_32x16(taddr + (c >> 1), packed);
+          for (uint32_t r = 0; r < 4; ++r) {
+            sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], 1);
+            sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], 2);
+          }
+          if ((live_mask >> q) & 1u) {
+            // sums[r] is row g + 8r: lane t keeps r = t
+            float score = (t4 == 0u ? sums[0] : (t4 == 1u ? sums[1] : (t4 == 2u ? sums[2] : sums[3]))) * kscale;
+            if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
+            a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
+          }
         }
-        tmem_st_wait();
-        tcgen05_fence_before();
-        mbar_arrive(bar(kPReady + acc));
-        // 3. the sums: columns [64, 64 + 16) of the unit, two per query slot
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(kSumFull + acc), (sum_phase >> acc) & 1u, waits))) break;
-        sum_phase ^= 1u << acc;
-        tcgen05_fence_after();
-        uint32_t sums[16];
-        tmem_ld_32x16(taddr + kSumColumn, sums);
-        tmem_ld_wait();
-#pragma unroll
-        for (uint32_t slot = 0; slot < 4u; ++slot) {
-          const uint32_t q = q_first + slot;
-          if (q < q_last && ((live_mask >> q) & 1u))
-            a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] =
-                (__uint_as_float(sums[2u * slot]) + __uint_as_float(sums[2u * slot + 1u])) * kscale;
-        }
-      } } else
+      } else
       for (uint32_t q = q_first; q < q_last; ++q) {
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
         // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
@@ -747,13 +689,11 @@ uint32_t validate(const KvipLiArgs* a) {
                "li_score: unknown dtype or score mode");
   KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->keys) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->query) & 15u) == 0,
                "li_score: keys and query must be 16-byte aligned");
-  KVIP_REQUIRE(a->head_sum <= KVIP_HEAD_SUM_TENSOR, "li_score: unknown head-sum mode");
-  KVIP_REQUIRE(a->head_sum != KVIP_HEAD_SUM_TENSOR || (a->queries * a->heads >= 128u && a->scoreMode == KVIP_SCORE_FP32),
-               "li_score: the tensor-core head sum needs 128 or more (query, head) columns and fp32 scores");
+  KVIP_REQUIRE(a->head_sum <= KVIP_HEAD_SUM_QUADS, "li_score: unknown head-sum mode");
   return 0;
 }
 
-template <bool kBf16, bool kTensorSum>
+template <bool kBf16, bool kQuads>
 uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   using Cfg = LiCfg<kBf16>;
   CUtensorMap key_map, query_map;
@@ -762,8 +702,8 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
     set_error("li_score: cuTensorMapEncodeTiled failed");
     return KVIP_BAD_ARGUMENT;
   }
-  if (uint32_t bad = raise_dynamic_smem(kTensorSum ? (kBf16 ? kSlotLiBf16Sum : kSlotLiFp8Sum) : (kBf16 ? kSlotLiBf16 : kSlotLiFp8),
-                                        reinterpret_cast<const void*>(li_score_tcgen05<kBf16, kTensorSum>),
+  if (uint32_t bad = raise_dynamic_smem(kQuads ? (kBf16 ? kSlotLiBf16Sum : kSlotLiFp8Sum) : (kBf16 ? kSlotLiBf16 : kSlotLiFp8),
+                                        reinterpret_cast<const void*>(li_score_tcgen05<kBf16, kQuads>),
                                         static_cast<int>(Cfg::kSmemLimit), "li_score attribute"))
     return bad;
   const uint32_t n_max = a.queries * a.heads;
@@ -772,7 +712,7 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   const uint32_t smem_bytes = Cfg::fixed_bytes(n_max) + stages * Cfg::kTileBytes;
   uint32_t ctas = a.ctas;
   if (!ctas) ctas = device_sm_count();
-  li_score_tcgen05<kBf16, kTensorSum><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
+  li_score_tcgen05<kBf16, kQuads><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
   count_launch();
   return check_launch("li_score_tcgen05");
 }
@@ -780,12 +720,10 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
 }  // namespace
 
 uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream) {
-  // the weighted sum over heads goes to the tensor core where the register reduction would set the pace
-  const bool wide = a.queries * a.heads >= 128u && a.scoreMode == KVIP_SCORE_FP32;
-  const bool tensor_sum = wide && a.head_sum != KVIP_HEAD_SUM_REGISTERS;
-  if (a.keyDtype == KVIP_KEY_BF16)
-    return tensor_sum ? launch_tcgen05<true, true>(a, stream) : launch_tcgen05<true, false>(a, stream);
-  return tensor_sum ? launch_tcgen05<false, true>(a, stream) : launch_tcgen05<false, false>(a, stream);
+  // wide query tiles are reduced in the fragment layout, where the head weights cost a quarter of the shared-memory reads
+  const bool quads = a.head_sum == KVIP_HEAD_SUM_QUADS || (a.head_sum == KVIP_HEAD_SUM_AUTO && a.queries * a.heads >= 128u);
+  if (a.keyDtype == KVIP_KEY_BF16) return quads ? launch_tcgen05<true, true>(a, stream) : launch_tcgen05<true, false>(a, stream);
+  return quads ? launch_tcgen05<false, true>(a, stream) : launch_tcgen05<false, false>(a, stream);
 }
 
 uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream) {

@@ -59,15 +59,20 @@ __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
 }
 
 // ---- merge of shard candidates -----------------------------------------------------------
-// Bitonic sort of (key descending, index ascending) composites in shared memory, cut at
-// 2048, then a second sort that restores the canonical output order.
-__device__ __forceinline__ void bitonic_sort(uint64_t* data, uint32_t n) {
+// One CTA per row. The candidates (shards x 2048 (score, index) pairs, at most 16384) are loaded into shared
+// memory once; the 2048th largest key is found by radix select over them (three passes over shared memory), ties
+// at that key are settled towards the lower index by a second radix select over the tied indices, the 2048
+// winners are compacted and only they are sorted (by "is a tie", then index): the canonical order. Sorting all
+// candidates instead cost 105 block-wide compare-exchange rounds over 16384 entries; this takes 66 over 2048.
+constexpr uint32_t kMergeMax = 8u * kTop;
+
+__device__ __forceinline__ void bitonic_sort(uint32_t* data, uint32_t n) {   // ascending; n a power of two
   for (uint32_t k = 2; k <= n; k <<= 1) {
     for (uint32_t j = k >> 1; j > 0; j >>= 1) {
       for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         const uint32_t partner = i ^ j;
         if (partner > i) {
-          const uint64_t x = data[i], y = data[partner];
+          const uint32_t x = data[i], y = data[partner];
           const bool ascending = (i & k) == 0;
           if ((x > y) == ascending) { data[i] = y; data[partner] = x; }
         }
@@ -77,37 +82,111 @@ __device__ __forceinline__ void bitonic_sort(uint64_t* data, uint32_t n) {
   }
 }
 
-__global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a, uint32_t padded) {
-  extern __shared__ uint64_t composite[];
-  const uint32_t row = blockIdx.x, n = a.shards * kTop;
+// The `want`-th largest of the values value(i), i < n with member(i) (12 + 12 + 8 bit radix select, all threads of
+// the block call). Returns the value; *take = how many entries EQUAL to it belong to the `want` largest.
+template <typename Value, typename Member>
+__device__ uint32_t kth_largest(uint32_t n, uint32_t want, Value value, Member member, uint32_t* hist, uint32_t* scan_scratch,
+                                uint32_t* found, uint32_t* take) {
+  const uint32_t tid = threadIdx.x;
+  uint32_t prefix = 0, prefix_mask = 0, remaining = want;
+#pragma unroll 1
+  for (uint32_t pass = 0; pass < 3; ++pass) {
+    const uint32_t bits = pass == 2 ? 8u : 12u;
+    const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
+    const uint32_t bins = 1u << bits;
+    for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
+    if (tid == 0) { found[0] = 0; found[1] = 0; }
+    __syncthreads();
+    for (uint32_t r = 0; r * kThreads < n; ++r) {   // block-uniform trip count: hist_add votes per warp
+      const uint32_t i = r * kThreads + tid;
+      const bool in = i < n && member(i);
+      const uint32_t v = in ? value(i) : 0u;
+      hist_add(hist, in && (v & prefix_mask) == prefix, (v >> shift) & (bins - 1u));
+    }
+    __syncthreads();
+    const uint32_t per = bins / kThreads ? bins / kThreads : 1u;  // 4, 4, then 1 (256 bins)
+    const uint32_t groups = bins / per;
+    const uint32_t group = groups - 1u - tid;  // valid when tid < groups: the highest bins first
+    uint32_t local = 0;
+    if (tid < groups)
+      for (uint32_t j = 0; j < per; ++j) local += hist[group * per + j];
+    uint32_t above = block_exclusive_scan(local, scan_scratch, nullptr);
+    if (tid < groups) {
+      for (int32_t j = static_cast<int32_t>(per) - 1; j >= 0; --j) {
+        const uint32_t count = hist[group * per + static_cast<uint32_t>(j)];
+        if (above < remaining && above + count >= remaining) {
+          found[0] = group * per + static_cast<uint32_t>(j);
+          found[1] = remaining - above;
+        }
+        above += count;
+      }
+    }
+    __syncthreads();
+    prefix |= found[0] << shift;
+    prefix_mask |= (bins - 1u) << shift;
+    remaining = found[1];
+    __syncthreads();
+  }
+  *take = remaining;
+  return prefix;
+}
+
+__global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
+  extern __shared__ uint32_t merge_smem[];   // [n] keys, [n] indices, [2048] winners
+  __shared__ uint32_t hist[4096];
+  __shared__ uint32_t scan_scratch[33];
+  __shared__ uint32_t found[2];
+  const uint32_t row = blockIdx.x, tid = threadIdx.x, n = a.shards * kTop;
+  uint32_t* keys = merge_smem;
+  int32_t* index = reinterpret_cast<int32_t*>(merge_smem + n);
+  uint32_t* winners = merge_smem + 2u * n;
   const uint64_t shard_stride = a.shard_stride ? a.shard_stride : kTop;
   const uint64_t row_offset = static_cast<uint64_t>(row) * (a.row_stride ? a.row_stride : n);
-  for (uint32_t i = threadIdx.x; i < padded; i += kThreads) {
-    uint64_t c = ~0ull;
-    if (i < n) {
-      const uint64_t at = row_offset + (i / kTop) * shard_stride + (i % kTop);
-      const int32_t index = a.cand_index[at];
-      if (index >= 0) c = (static_cast<uint64_t>(~sortable_key(a.cand_scores[at])) << 32) | static_cast<uint32_t>(index);
-    }
-    composite[i] = c;
+  uint32_t mine = 0;
+  for (uint32_t i = tid; i < n; i += kThreads) {
+    const uint64_t at = row_offset + (i / kTop) * shard_stride + (i % kTop);
+    const int32_t candidate = a.cand_index[at];
+    index[i] = candidate;
+    keys[i] = candidate >= 0 ? sortable_key(a.cand_scores[at]) : 0u;
+    mine += candidate >= 0 ? 1u : 0u;
   }
-  __syncthreads();
-  bitonic_sort(composite, padded);
-  // canonical order: keys above the cut by ascending index, then the cut key by ascending index
-  const uint32_t cut_key = static_cast<uint32_t>(composite[kTop - 1] >> 32);
-  __syncthreads();
-  for (uint32_t i = threadIdx.x; i < kTop; i += kThreads) {
-    const uint64_t c = composite[i];
-    if (c != ~0ull) {
-      const uint64_t tie = static_cast<uint32_t>(c >> 32) == cut_key ? 1ull : 0ull;
-      composite[i] = (tie << 32) | (c & 0xffffffffull);
-    }
+  uint32_t valid;
+  block_exclusive_scan(mine, scan_scratch, &valid);   // also the barrier after the loads
+  // the cut: key of the 2048th largest candidate, how many candidates tied at it are taken, and below which index
+  uint32_t cut_key = 0, ties_taken = 0, tie_index_limit = 0xffffffffu;   // defaults: every valid candidate wins
+  if (valid > kTop) {   // block-uniform
+    cut_key = kth_largest(n, kTop, [&](uint32_t i) { return keys[i]; }, [&](uint32_t i) { return index[i] >= 0; }, hist,
+                          scan_scratch, found, &ties_taken);
+    // lower index first among the tied: the ties_taken smallest indices = the ties_taken largest of ~index
+    uint32_t unused;
+    const uint32_t inverted = kth_largest(n, ties_taken, [&](uint32_t i) { return ~static_cast<uint32_t>(index[i]); },
+                                          [&](uint32_t i) { return index[i] >= 0 && keys[i] == cut_key; }, hist,
+                                          scan_scratch, found, &unused);
+    tie_index_limit = ~inverted;   // indices are distinct: exactly ties_taken tied candidates lie at or below it
   }
+  // winners, compacted in any order, as (is a tie, index); then sorted: keys above the cut by ascending index, the
+  // tied ones after them by ascending index
+  for (uint32_t i = tid; i < kTop; i += kThreads) winners[i] = 0xffffffffu;
   __syncthreads();
-  bitonic_sort(composite, kTop);
+  auto classify = [&](uint32_t i, bool* tie) -> bool {
+    if (i >= n || index[i] < 0) return false;
+    *tie = valid > kTop && keys[i] == cut_key;
+    return valid <= kTop || keys[i] > cut_key || (*tie && static_cast<uint32_t>(index[i]) <= tie_index_limit);
+  };
+  uint32_t won = 0;
+  bool tie = false;
+  for (uint32_t i = tid; i < n; i += kThreads) won += classify(i, &tie) ? 1u : 0u;
+  uint32_t at = block_exclusive_scan(won, scan_scratch, nullptr);
+  for (uint32_t i = tid; i < n; i += kThreads)
+    if (classify(i, &tie)) {
+      if (at < kTop) winners[at] = (tie ? 0x80000000u : 0u) | static_cast<uint32_t>(index[i]);
+      ++at;
+    }
+  __syncthreads();
+  bitonic_sort(winners, kTop);
   int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
-  for (uint32_t i = threadIdx.x; i < kTop; i += kThreads)
-    out[i] = composite[i] == ~0ull ? -1 : static_cast<int32_t>(composite[i] & 0xffffffffull);
+  for (uint32_t i = tid; i < kTop; i += kThreads)
+    out[i] = winners[i] == 0xffffffffu ? -1 : static_cast<int32_t>(winners[i] & 0x7fffffffu);
 }
 
 }  // namespace
@@ -189,13 +268,11 @@ extern "C" uint32_t kvip_b200_topk_static(const KvipTopkArgs* a, void* stream) {
 extern "C" uint32_t kvip_b200_topk_merge(const KvipMergeArgs* a, void* stream) {
   KVIP_REQUIRE(a && a->cand_scores && a->cand_index && a->topk, "topk_merge: null pointer");
   KVIP_REQUIRE(a->rows >= 1 && a->shards >= 1 && a->shards <= 8, "topk_merge: 1..8 shards");
-  uint32_t padded = 2048;
-  while (padded < a->shards * KVIP_TOPK) padded <<= 1;
-  const size_t smem = static_cast<size_t>(padded) * sizeof(uint64_t);
+  const size_t smem = (2u * a->shards + 1u) * KVIP_TOPK * sizeof(uint32_t);   // keys, indices, winners
   if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotTopkMerge, reinterpret_cast<const void*>(kvip::topk_merge),
-                                              16384 * 8, "topk_merge attribute"))
+                                              (2 * 8 + 1) * 2048 * 4, "topk_merge attribute"))
     return bad;
-  kvip::topk_merge<<<a->rows, kvip::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a, padded);
+  kvip::topk_merge<<<a->rows, kvip::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
   kvip::count_launch();
   return kvip::check_launch("topk_merge");
 }
