@@ -38,6 +38,8 @@ WORKLOADS = {
                            key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
     "decode_128k_b8": dict(batch=8, queries=1, heads=64, history=131072, resident=32768, len_lo=131072,
                            len_hi=131072, key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
+    "decode_64k_b16_mtp2": dict(batch=16, queries=2, heads=64, history=65536, resident=8192, len_lo=65536, len_hi=65536,
+                                key_dtype="fp8", weight_dtype="bf16", token_bytes=1152),
 }
 METRIC = "LI+TopK+Fetch query tokens/s at 128k ctx"
 
@@ -200,10 +202,22 @@ def run_ours(args):
         with ClockSampler(local) as clocks:
             soak(0.3)
             barrier()
-            block_seconds = time_blocks(torch, stream, graph.replay, args.steps, first_block)
+            block_seconds = time_blocks(torch, stream, graph.replay, args.steps, first_block,
+                                        **(dict(least=1, most=1) if args.quick else {}))
             barrier()
             soak(0.3)
         steady_reads = int(p.rotating.query_counts[:, 4].sum().item())
+        if args.quick:   # profiler captures: the warm-up and the timed replays only
+            median = sorted(block_seconds)[len(block_seconds) // 2]
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "value": world * tokens * args.steps / median, "unit": "tokens/s",
+                                  "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                                  "ms_per_step": median / args.steps * 1e3, "config": {"workload": args.workload, "quick": True},
+                                  "gpu_launches": launches_per_step * args.steps, "cold_step_reads": cold_reads}), flush=True)
+            p.close()
+            if world > 1:
+                dist.destroy_process_group()
+            return
         blocks = torch.tensor(block_seconds, dtype=torch.float64, device=device)
         if world > 1:   # every block as slow as its slowest rank (all ranks time the same number of blocks)
             counts = torch.tensor([len(block_seconds)], dtype=torch.int64, device=device)
@@ -1113,8 +1127,10 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch",
                                                        "decode_128k_b32_zipf"], default="decode_128k_b64")
-    parser.add_argument("--head-sum", type=int, default=0, choices=(0, 1, 2),
-                        help="how the score kernel reads accumulators back: 0 = automatic, 1 = rows, 2 = quads")
+    parser.add_argument("--quick", action="store_true",
+                        help="warm-up and timed replays only (for profiler captures): no stage timings, no end-to-end leg")
+    parser.add_argument("--head-sum", type=int, default=0, choices=(0, 1, 2, 3),
+                        help="how the score kernel reads accumulators back: 0 = automatic, 1 = rows, 2 = quads, 3 = rows, loads ahead")
     parser.add_argument("--reuse", type=float, default=0.75,
                         help="decode_128k_b32_zipf: share of a selection kept from the previous step")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")

@@ -67,7 +67,7 @@ enum { KVIP_SCORE_FP32 = 0, KVIP_SCORE_BF16_AWAY = 1 };
  * adjacent columns of every eight for four rows (the MMA fragment layout) and a quarter of the weights; four lanes
  * add their partial sums with shuffles. AUTO: QUADS when a key page meets 128 or more (query, head) columns, where
  * the weight reads of ROWS and not HBM set the pace; ROWS otherwise. */
-enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_ROWS = 1, KVIP_HEAD_SUM_QUADS = 2 };
+enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_ROWS = 1, KVIP_HEAD_SUM_QUADS = 2, KVIP_HEAD_SUM_ROWS_AHEAD = 3 };
 
 /* Geometry bound before graph capture. Same size (80 bytes, 20 x u32) and the same
  * leading fields as rotating::RuntimeShape (include/runtime_shape.h:5-27); the fields

@@ -21,7 +21,7 @@ BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
 WEIGHT_BF16, WEIGHT_FP32 = 0, 1
 SCORE_FP32, SCORE_BF16_AWAY = 0, 1
-HEAD_SUM_AUTO, HEAD_SUM_ROWS, HEAD_SUM_QUADS = 0, 1, 2
+HEAD_SUM_AUTO, HEAD_SUM_ROWS, HEAD_SUM_QUADS, HEAD_SUM_ROWS_AHEAD = 0, 1, 2, 3
 
 
 def _struct(name, pointer_fields, scalar_fields):

@@ -93,7 +93,7 @@ extern "C" uint32_t kvip_prepare_shape(KvipRuntimeShape* s) {
   KVIP_REQUIRE(s->history >= s->resident && s->history <= (1u << 21), "prepare_shape: history must be in resident..2^21");
   KVIP_REQUIRE(s->tokenBytes >= 16 && s->tokenBytes % 16 == 0, "prepare_shape: token bytes must be a multiple of 16");
   KVIP_REQUIRE(s->keyDtype <= KVIP_KEY_BF16 && s->weightDtype <= KVIP_WEIGHT_FP32 && s->scoreMode <= KVIP_SCORE_BF16_AWAY &&
-                   s->liVariant <= 1 && s->headSum <= KVIP_HEAD_SUM_QUADS, "prepare_shape: unknown dtype, score mode, LI variant or head-sum mode");
+                   s->liVariant <= 1 && s->headSum <= KVIP_HEAD_SUM_ROWS_AHEAD, "prepare_shape: unknown dtype, score mode, LI variant or head-sum mode");
   s->pagesPerRequest = s->history / 128;
   s->scoreStride = s->history;
   s->finalWorkers = 4;

@@ -53,35 +53,52 @@ __global__ void __launch_bounds__(256) publish_residency(const KvipFetchArgs a) 
 }
 
 __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs a) {
-  const uint32_t lane = threadIdx.x & 31u;
+  // first descriptor of every request in the flat list (a failed request contributes none): all counts are loaded
+  // at once, so the prologue costs one memory round trip whatever the batch
+  __shared__ uint32_t first[1025];
+  __shared__ uint32_t scan[33];
+  const uint32_t tid = threadIdx.x, lane = tid & 31u;
+  constexpr uint32_t kPer = 1024u / kFetchThreads;   // batch <= 1024
+  uint32_t mine[kPer], sum = 0;
+#pragma unroll
+  for (uint32_t j = 0; j < kPer; ++j) {
+    const uint32_t b = tid * kPer + j;
+    mine[j] = b < a.batch && a.row_status[b * 32u] == 0 ? static_cast<uint32_t>(max(a.query_counts[b * 8u + 4], 0)) : 0u;
+    sum += mine[j];
+  }
+  uint32_t total;
+  uint32_t before = block_exclusive_scan(sum, scan, &total);
+#pragma unroll
+  for (uint32_t j = 0; j < kPer; ++j) {
+    first[tid * kPer + j] = before;
+    before += mine[j];
+  }
+  if (tid == kFetchThreads - 1u) first[1024] = total;
+  __syncthreads();
   const uint32_t warps = gridDim.x * (kFetchThreads / 32u);
-  const uint32_t me = blockIdx.x * (kFetchThreads / 32u) + (threadIdx.x >> 5);
-  uint32_t offset = 0;   // descriptors of the earlier requests, modulo the number of warps
-  for (uint32_t b = 0; b < a.batch; ++b) {
-    if (a.row_status[b * 32u] != 0) continue;   // a failed request moves nothing
-    const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
+  uint32_t b = 0;
+  for (uint32_t item = blockIdx.x * (kFetchThreads / 32u) + (tid >> 5); item < total; item += warps) {
+    while (first[b + 1] <= item) ++b;   // items ascend: the request index only moves forward (first[1024] = total ends it)
+    const uint32_t i = item - first[b];
     const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
-    for (uint32_t i = (me + warps - offset) % warps; i < count; i += warps) {
-      const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
-      const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
-      const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
-      if (!descriptor_ok(a, source, dest, slot)) {
-        // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
-        // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
-        // it is revoked, and the request's update status gets the reference's code for a failed publication
-        // (CompleteEarlyUpdate, index_cache_update.h:6-20).
-        if (lane == 0) {
-          atomicOr(a.row_status + b * 32u + 2, 1);
-          if (a.status) atomicOr(a.status + b, 4);
-          if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
-        }
-        continue;
+    const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
+    const int32_t dest = a.fetch_destinations[static_cast<uint64_t>(b) * kSlots + i];
+    const uint32_t slot = static_cast<uint32_t>(dest) - owner * a.outputStride;
+    if (!descriptor_ok(a, source, dest, slot)) {
+      // Record and skip the access (streaming.cpp:399-400 does the same range check). The Index row of the new
+      // token already sits at this destination, so the slot must not keep the residency of the row it evicted:
+      // it is revoked, and the request's update status gets the reference's code for a failed publication
+      // (CompleteEarlyUpdate, index_cache_update.h:6-20).
+      if (lane == 0) {
+        atomicOr(a.row_status + b * 32u + 2, 1);
+        if (a.status) atomicOr(a.status + b, 4);
+        if (dest >= 0 && slot < a.resident) a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 0;
       }
-      copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
-      if (lane == 0 && slot < a.resident && !a.defer_publication)
-        a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
+      continue;
     }
-    offset = (offset + count) % warps;
+    copy_row_warp(a.pool + static_cast<uint64_t>(dest) * a.tokenBytes, a.source_base + source, a.tokenBytes, lane);
+    if (lane == 0 && slot < a.resident && !a.defer_publication)
+      a.hot_valid[static_cast<uint64_t>(owner) * a.resident + slot] = 1;
   }
 }
 
@@ -399,7 +416,7 @@ extern "C" uint32_t kvip_b200_fetch(const KvipFetchArgs* a, void* stream) {
   KVIP_REQUIRE(a->tokenBytes >= 16 && a->tokenBytes % 16 == 0, "fetch: token bytes must be a multiple of 16");
   KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->pool) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->source_base) & 15u) == 0,
                "fetch: pool and source base must be 16-byte aligned");
-  KVIP_REQUIRE(a->batch >= 1 && a->outputStride >= a->resident, "fetch: geometry");
+  KVIP_REQUIRE(a->batch >= 1 && a->batch <= 1024 && a->outputStride >= a->resident, "fetch: geometry (batch 1..1024)");
   return kvip::launch_fetch(*a, static_cast<cudaStream_t>(stream));
 }
 

@@ -174,6 +174,15 @@ __device__ __forceinline__ void tmem_ld_16x256_x8(uint32_t taddr, uint32_t (&r)[
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_16x256_x4(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
@@ -219,13 +228,16 @@ __device__ __forceinline__ float load_weight(const KvipLiArgs& a, uint32_t index
   return w;
 }
 
-// kQuads: the epilogue reads accumulators in the 16x256b fragment layout (see the header comment).
-template <bool kBf16, bool kQuads>
+// kEpilogue: how accumulators are read back (see the header comment): kRows, kQuads, or kRowsAhead = kRows with the
+// tensor-memory load of the next 16 columns in flight while the current 16 are reduced.
+constexpr int kRows = 0, kQuadsLayout = 1, kRowsAhead = 2;
+template <bool kBf16, int kEpilogue>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap query_map,
                  const __grid_constant__ KvipLiArgs a, const uint32_t S) {
   using Cfg = LiCfg<kBf16>;
   extern __shared__ uint8_t smem_raw[];
+  constexpr bool kQuads = kEpilogue == kQuadsLayout;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -550,6 +562,41 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
             a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
           }
         }
+      } else if constexpr (kEpilogue == kRowsAhead) {
+        // the unit's columns in pieces of 16, two register buffers: while one piece is reduced the load of the next
+        // is in flight, so a warp does not sit out a tensor-memory round trip per piece
+        const uint32_t pieces = (q_last - q_first) * H / 16u;   // H is 32 or 64: a piece never straddles two query slots
+        uint32_t even[16], odd[16];   // two named buffers: indexed statically, they stay in registers
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        auto reduce = [&](const uint32_t(&v)[16], uint32_t piece) {
+          const uint32_t column = piece * 16u, q = q_first + column / H;
+          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q_first * H + column);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            const float4 w = w4[j];
+            s0 = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, s0);
+            s1 = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, s1);
+            s2 = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, s2);
+            s3 = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, s3);
+          }
+          if ((column + 16u) % H == 0u) {   // the slot's last piece
+            if ((live_mask >> q) & 1u) {
+              float score = ((s0 + s2) + (s1 + s3)) * kscale;
+              if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
+              a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
+            }
+            s0 = s1 = s2 = s3 = 0.f;
+          }
+        };
+        tmem_ld_32x16(taddr, even);
+        for (uint32_t piece = 0; piece < pieces; piece += 2u) {   // `pieces` is even: a slot is 32 or 64 columns
+          tmem_ld_wait();
+          tmem_ld_32x16(taddr + (piece + 1u) * 16u, odd);
+          reduce(even, piece);
+          tmem_ld_wait();
+          if (piece + 2u < pieces) tmem_ld_32x16(taddr + (piece + 2u) * 16u, even);
+          reduce(odd, piece + 1u);
+        }
       } else
       for (uint32_t q = q_first; q < q_last; ++q) {
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
@@ -689,11 +736,11 @@ uint32_t validate(const KvipLiArgs* a) {
                "li_score: unknown dtype or score mode");
   KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->keys) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->query) & 15u) == 0,
                "li_score: keys and query must be 16-byte aligned");
-  KVIP_REQUIRE(a->head_sum <= KVIP_HEAD_SUM_QUADS, "li_score: unknown head-sum mode");
+  KVIP_REQUIRE(a->head_sum <= KVIP_HEAD_SUM_ROWS_AHEAD, "li_score: unknown head-sum mode");
   return 0;
 }
 
-template <bool kBf16, bool kQuads>
+template <bool kBf16, int kEpilogue>
 uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   using Cfg = LiCfg<kBf16>;
   CUtensorMap key_map, query_map;
@@ -702,8 +749,8 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
     set_error("li_score: cuTensorMapEncodeTiled failed");
     return KVIP_BAD_ARGUMENT;
   }
-  if (uint32_t bad = raise_dynamic_smem(kQuads ? (kBf16 ? kSlotLiBf16Sum : kSlotLiFp8Sum) : (kBf16 ? kSlotLiBf16 : kSlotLiFp8),
-                                        reinterpret_cast<const void*>(li_score_tcgen05<kBf16, kQuads>),
+  constexpr KernelSlot slot = static_cast<KernelSlot>(kSlotLi + 2 * kEpilogue + (kBf16 ? 1 : 0));
+  if (uint32_t bad = raise_dynamic_smem(slot, reinterpret_cast<const void*>(li_score_tcgen05<kBf16, kEpilogue>),
                                         static_cast<int>(Cfg::kSmemLimit), "li_score attribute"))
     return bad;
   const uint32_t n_max = a.queries * a.heads;
@@ -712,7 +759,7 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   const uint32_t smem_bytes = Cfg::fixed_bytes(n_max) + stages * Cfg::kTileBytes;
   uint32_t ctas = a.ctas;
   if (!ctas) ctas = device_sm_count();
-  li_score_tcgen05<kBf16, kQuads><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
+  li_score_tcgen05<kBf16, kEpilogue><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
   count_launch();
   return check_launch("li_score_tcgen05");
 }
@@ -720,10 +767,17 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
 }  // namespace
 
 uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream) {
-  // wide query tiles are reduced in the fragment layout, where the head weights cost a quarter of the shared-memory reads
-  const bool quads = a.head_sum == KVIP_HEAD_SUM_QUADS || (a.head_sum == KVIP_HEAD_SUM_AUTO && a.queries * a.heads >= 128u);
-  if (a.keyDtype == KVIP_KEY_BF16) return quads ? launch_tcgen05<true, true>(a, stream) : launch_tcgen05<true, false>(a, stream);
-  return quads ? launch_tcgen05<false, true>(a, stream) : launch_tcgen05<false, false>(a, stream);
+  const bool wide = a.queries * a.heads >= 128u;
+  const uint32_t mode = a.head_sum != KVIP_HEAD_SUM_AUTO ? a.head_sum : (wide ? KVIP_HEAD_SUM_ROWS_AHEAD : KVIP_HEAD_SUM_ROWS);
+  const bool bf16 = a.keyDtype == KVIP_KEY_BF16;
+  switch (mode) {
+    case KVIP_HEAD_SUM_QUADS:
+      return bf16 ? launch_tcgen05<true, kQuadsLayout>(a, stream) : launch_tcgen05<false, kQuadsLayout>(a, stream);
+    case KVIP_HEAD_SUM_ROWS_AHEAD:
+      return bf16 ? launch_tcgen05<true, kRowsAhead>(a, stream) : launch_tcgen05<false, kRowsAhead>(a, stream);
+    default:
+      return bf16 ? launch_tcgen05<true, kRows>(a, stream) : launch_tcgen05<false, kRows>(a, stream);
+  }
 }
 
 uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream) {

@@ -164,26 +164,30 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
                                           scan_scratch, found, &unused);
     tie_index_limit = ~inverted;   // indices are distinct: exactly ties_taken tied candidates lie at or below it
   }
-  // winners, compacted in any order, as (is a tie, index); then sorted: keys above the cut by ascending index, the
-  // tied ones after them by ascending index
+  // winners, compacted in input order (a thread owns a contiguous run of candidates), as (is a tie, index). With a
+  // cut they are then sorted: keys above the cut by ascending index, the tied ones after them by ascending index.
+  // Without a cut (at most 2048 valid candidates) the input order IS the canonical one and is kept: the shards are in
+  // position order and each shard's list is canonical for its slice - ascending positions for a slice of at most
+  // 2048 keys, the whole answer when one shard alone contributes.
   for (uint32_t i = tid; i < kTop; i += kThreads) winners[i] = 0xffffffffu;
   __syncthreads();
   auto classify = [&](uint32_t i, bool* tie) -> bool {
-    if (i >= n || index[i] < 0) return false;
+    if (index[i] < 0) return false;
     *tie = valid > kTop && keys[i] == cut_key;
     return valid <= kTop || keys[i] > cut_key || (*tie && static_cast<uint32_t>(index[i]) <= tie_index_limit);
   };
+  const uint32_t per = n / kThreads;   // n is a multiple of 2048
   uint32_t won = 0;
   bool tie = false;
-  for (uint32_t i = tid; i < n; i += kThreads) won += classify(i, &tie) ? 1u : 0u;
+  for (uint32_t i = tid * per; i < (tid + 1u) * per; ++i) won += classify(i, &tie) ? 1u : 0u;
   uint32_t at = block_exclusive_scan(won, scan_scratch, nullptr);
-  for (uint32_t i = tid; i < n; i += kThreads)
+  for (uint32_t i = tid * per; i < (tid + 1u) * per; ++i)
     if (classify(i, &tie)) {
       if (at < kTop) winners[at] = (tie ? 0x80000000u : 0u) | static_cast<uint32_t>(index[i]);
       ++at;
     }
   __syncthreads();
-  bitonic_sort(winners, kTop);
+  if (valid > kTop) bitonic_sort(winners, kTop);   // block-uniform
   int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
   for (uint32_t i = tid; i < kTop; i += kThreads)
     out[i] = winners[i] == 0xffffffffu ? -1 : static_cast<int32_t>(winners[i] & 0x7fffffffu);

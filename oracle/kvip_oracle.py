@@ -196,11 +196,17 @@ def cold_predicate(scores, key_lengths, query_ends, resident):
 
 
 def topk_merge(cand_scores, cand_index):
-    """Global top-2048 of sharded candidates under (score desc, index asc), canonical order."""
+    """Global top-2048 of sharded candidates under (score desc, index asc), canonical order. With at most 2048
+    valid candidates nothing is cut and the input order is kept: the shards are in position order and every
+    shard's list is canonical for its slice (ascending positions for a slice of at most 2048 keys; the whole answer
+    when a single shard contributes), which is what the TopK of the unsharded row gives."""
     rows = cand_scores.shape[0]
     out = np.full((rows, TOPK), -1, dtype=np.int32)
     for r in range(rows):
         live = np.flatnonzero(cand_index[r] >= 0)
+        if len(live) <= TOPK:
+            out[r, : len(live)] = cand_index[r, live]
+            continue
         keys = sortable_key(cand_scores[r, live]).astype(np.int64)
         index = cand_index[r, live].astype(np.int64)
         order = np.lexsort((index, -keys))[:TOPK]

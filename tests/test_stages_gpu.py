@@ -54,12 +54,12 @@ def test_li_simt_matches_c_oracle_bit_exact(spec, device):
     assert np.array_equal(got[mask].view(np.uint32), expected[mask].view(np.uint32))
 
 
-HEAD_SUMS = [_lib.HEAD_SUM_ROWS, _lib.HEAD_SUM_QUADS]
+HEAD_SUMS = [_lib.HEAD_SUM_ROWS, _lib.HEAD_SUM_QUADS, _lib.HEAD_SUM_ROWS_AHEAD]
 
 
 @pytest.mark.parametrize("spec", LI_CASES, ids=lambda s: f"seed{s['seed']}")
 @pytest.mark.parametrize("score_mode", [0, 1])
-@pytest.mark.parametrize("head_sum", HEAD_SUMS, ids=["rows", "quads"])
+@pytest.mark.parametrize("head_sum", HEAD_SUMS, ids=["rows", "quads", "rows_ahead"])
 def test_li_tcgen05_within_tolerance(spec, score_mode, head_sum, device):
     """Against the NumPy golden formula, for both ways the epilogue reads an accumulator back (one token row per
     thread; the MMA fragment layout with a quarter of the head weights per lane)."""
@@ -333,6 +333,21 @@ def test_topk_merge_equals_unsharded(device):
     got = ops.topk_merge_gathered(torch.from_numpy(gathered).to(device))
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy(), expected)
+    # one shard alone: its list is the answer and comes back unchanged (ties at the cut stay behind the rest)
+    single = oracle_c.topk(whole[:, :per].copy(), np.full(2, per, np.int32), np.full(2, per, np.int32))
+    got = ops.topk_merge(torch.from_numpy(np.take_along_axis(whole, single, 1)).to(device), torch.from_numpy(single).to(device))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), single)
+    # a context shorter than 2048 keys spread over three shards: ascending positions, then -1
+    short_index = np.full((1, 3 * TOPK), -1, np.int32)
+    short_index[0, :700] = np.arange(700)
+    short_index[0, TOPK:TOPK + 650] = 700 + np.arange(650)
+    short_index[0, 2 * TOPK:2 * TOPK + 3] = 1350 + np.arange(3)
+    short_scores = rng.standard_normal((1, 3 * TOPK)).astype(np.float32)
+    got = ops.topk_merge(torch.from_numpy(short_scores).to(device), torch.from_numpy(short_index).to(device))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy()[0], np.concatenate((np.arange(1353), np.full(TOPK - 1353, -1))).astype(np.int32))
+    assert np.array_equal(oracle.topk_merge(short_scores, short_index)[0], got.cpu().numpy()[0])
 
 
 RESOLVER_CASES = [
