@@ -151,14 +151,14 @@ def run_ours(args):
     lib = _lib.load_library()
     miss_source = "device tensor" if args.device_source else "pinned mapped host pool"
     try:
-        p = DecodePipeline(device, seed=rank, gather=True, host_pool=not args.device_source, head_sum=args.head_sum, **cfg)
+        p = DecodePipeline(device, seed=rank, gather=True, host_pool=not args.device_source, **cfg)
     except (RuntimeError, MemoryError) as failure:
         # the host pool of one rank is owners x history x token_bytes (9.7 GB at the headline): when the box cannot
         # pin that much for every rank, the miss rows come from a device tensor instead, and the line says so
         if args.device_source:
             raise
         torch.cuda.empty_cache()
-        p = DecodePipeline(device, seed=rank, gather=True, host_pool=False, head_sum=args.head_sum, **cfg)
+        p = DecodePipeline(device, seed=rank, gather=True, host_pool=False, **cfg)
         miss_source = f"device tensor (host pool unavailable: {str(failure)[:80]})"
     stream = torch.cuda.Stream(device)
     tokens = p.query_tokens()
@@ -235,7 +235,7 @@ def run_ours(args):
         li = lambda: ops.li_score(inputs.query, keys_view.view(-1, 128), inputs.weights,  # noqa: E731
                                   inputs.scale if p.key_dtype == "fp8" else None,
                                   s.scales.view(-1) if p.key_dtype == "fp8" else None, ws.key_lengths, qe2d,
-                                  inputs.block_table, ws.scores, status=p.forward.li_status, head_sum=args.head_sum)
+                                  inputs.block_table, ws.scores, status=p.forward.li_status)
         tk = lambda: ops.topk(ws.scores, ws.key_lengths, inputs.query_ends, ws.topk.view(-1, 2048))  # noqa: E731
         ga = lambda: ops.gather(p.pool_hbm, p.update.slot_output.view(-1, 2048), p.gather_out,  # noqa: E731
                                 queries=p.queries, output_stride=p.output_stride, token_bytes=p.token_bytes,
@@ -377,28 +377,41 @@ def measure_miss_path(torch, ops, p, stream, args):
     """Steps whose selections drift (AR(1) queries), so that part of every selection misses the resident pool
     and is fetched from the pinned host pool, with the Index update of one new bf16 row per token in the
     step; plus the host link alone (the fetch kernel over synthetic descriptors)."""
+    from kvip_b200 import LIFetch
+
     steps, warm = 8, 4
-    p.make_query_bank(steps + warm, correlation=0.95)
-    for i in range(warm):
-        p.load_queries(i)
-        p.step(ingest=True)
-    stream.synchronize()
-    misses, start, stop = [], torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    counts = torch.zeros(steps, dtype=torch.int64, device=p.device)
-    start.record(stream)
-    for i in range(steps):
-        p.load_queries(warm + i)
-        p.step(ingest=True)
-        counts[i] = p.rotating.query_counts[:, 4].sum()
-    stop.record(stream)
-    stop.synchronize()
-    seconds = start.elapsed_time(stop) / 1e3
-    misses = counts.tolist()
+    p.make_query_bank(2 * (steps + warm), correlation=0.95)
+
+    def drifting(first):
+        for i in range(warm):
+            p.load_queries(first + i)
+            p.step(ingest=True)
+        stream.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        counts = torch.zeros(steps, dtype=torch.int64, device=p.device)
+        start.record(stream)
+        for i in range(steps):
+            p.load_queries(first + warm + i)
+            p.step(ingest=True)
+            counts[i] = p.rotating.query_counts[:, 4].sum()
+        stop.record(stream)
+        stop.synchronize()
+        return start.elapsed_time(stop) / 1e3, counts.tolist()
+
+    serial_seconds, serial_misses = drifting(0)
+    # the same pipeline with the commit phase overlapped: a second call object over the same state (the first one is
+    # not used again: the bindings now name the new object's workspace record)
+    p.forward = LIFetch(p.rotating, p.update, lru=p.lru, overlap_fetch=True)
+    seconds, misses = drifting(steps + warm)
     status = int(p.update.status.max().item()) | int(p.rotating.row_status[:, 2].max().item())
     out = {"steps": steps, "ms_per_step": seconds / steps * 1e3, "tokens_per_s": p.query_tokens() * steps / seconds,
            "misses_per_step": sum(misses) / steps, "miss_fraction": sum(misses) / steps / (p.query_tokens() * 2048),
            "miss_bytes_per_step": sum(misses) / steps * p.token_bytes, "status": status,
-           "query_drift": "AR(1), rho = 0.95, new bf16 k_I row per token quantised to FP8"}
+           "commit_phase": "overlapped (LIFetch(overlap_fetch=True)): outputs, Index exchange and the gather of hit "
+                           "entries on a side stream beside the fetch",
+           "serial_commit_phase": {"ms_per_step": serial_seconds / steps * 1e3,
+                                   "misses_per_step": sum(serial_misses) / steps},
+           "query_drift": "AR(1), rho = 0.95, new bf16 k_I row per token quantised to FP8; eager launches"}
     if p.host_pool is not None:
         # host link alone: 16384 rows per request from distinct host rows into the resident slots
         rows = min(8192, p.resident)
@@ -765,7 +778,7 @@ def run_prefill(args):
     def li(part):
         lo, hi = part * rows, (part + 1) * rows
         ops.li_score(query[lo:hi], keys, weights[lo:hi], query_scale[lo:hi], key_scale, key_lengths,
-                     ends[lo // 4:hi // 4], table, scores, status=status, head_sum=args.head_sum)
+                     ends[lo // 4:hi // 4], table, scores, status=status)
 
     def step(li_only=False):
         for part in range(chunk // rows):
@@ -1129,8 +1142,6 @@ def main():
                                                        "decode_128k_b32_zipf"], default="decode_128k_b64")
     parser.add_argument("--quick", action="store_true",
                         help="warm-up and timed replays only (for profiler captures): no stage timings, no end-to-end leg")
-    parser.add_argument("--head-sum", type=int, default=0, choices=(0, 1, 2, 3),
-                        help="how the score kernel reads accumulators back: 0 = automatic, 1 = rows, 2 = quads, 3 = rows, loads ahead")
     parser.add_argument("--reuse", type=float, default=0.75,
                         help="decode_128k_b32_zipf: share of a selection kept from the previous step")
     parser.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload")

@@ -73,7 +73,7 @@ class DecodePipeline:
                  weight_dtype="bf16", token_bytes=1152, seed=0, gather=True, host_pool=True, fill_payload=False,
                  score_mode=_lib.SCORE_FP32, li_variant=0, owners=None, permute_owners=True, sm_count=0,
                  overlap_lru=True, prefetch_limit=0, prefetch_windows=3, prefetch_ctas=0,
-                 prefetch_last_window=False, tail_slots=0, head_sum=_lib.HEAD_SUM_AUTO, overlap_fetch=False):
+                 prefetch_last_window=False, tail_slots=0, overlap_fetch=False):
         self.device = device = torch.device(device)
         self.batch, self.queries, self.heads, self.history, self.resident = batch, queries, heads, history, resident
         self.token_bytes, self.key_dtype = token_bytes, key_dtype
@@ -147,7 +147,7 @@ class DecodePipeline:
             token_addresses=self.storage.addresses, row_owners=inputs.row_owners, scratch=self.workspace.scratch,
             token_bytes=token_bytes, queries=queries, score_mode=score_mode, gather_output=self.gather_out,
             li_variant=li_variant, source=source, sm_count=sm_count, tail_bounds=self.tail_bounds,
-            output_stride=self.output_stride, head_sum=head_sum)
+            output_stride=self.output_stride)
         self.update = IndexUpdate(
             torch, keys=self.storage.keys, scales=self.storage.scales, addresses=self.storage.addresses,
             logical_ids=self.storage.logical_ids, row_owners=inputs.row_owners, rotating=self.rotating,

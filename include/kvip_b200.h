@@ -61,13 +61,6 @@ extern "C" {
 enum { KVIP_KEY_FP8_E4M3 = 0, KVIP_KEY_BF16 = 1 };
 enum { KVIP_WEIGHT_BF16 = 0, KVIP_WEIGHT_FP32 = 1 };
 enum { KVIP_SCORE_FP32 = 0, KVIP_SCORE_BF16_AWAY = 1 };
-/* How the tcgen05 kernel reads an accumulator back for the weighted sum over index heads (fp32 arithmetic either
- * way; the order of the additions differs, inside every tolerance stated for this kernel). ROWS: a thread owns a
- * token row and walks the columns; the head weights are warp-uniform shared-memory reads. QUADS: a thread owns two
- * adjacent columns of every eight for four rows (the MMA fragment layout) and a quarter of the weights; four lanes
- * add their partial sums with shuffles. AUTO: QUADS when a key page meets 128 or more (query, head) columns, where
- * the weight reads of ROWS and not HBM set the pace; ROWS otherwise. */
-enum { KVIP_HEAD_SUM_AUTO = 0, KVIP_HEAD_SUM_ROWS = 1, KVIP_HEAD_SUM_QUADS = 2, KVIP_HEAD_SUM_ROWS_AHEAD = 3 };
 
 /* Geometry bound before graph capture. Same size (80 bytes, 20 x u32) and the same
  * leading fields as rotating::RuntimeShape (include/runtime_shape.h:5-27); the fields
@@ -91,7 +84,7 @@ typedef struct KvipRuntimeShape {
   uint32_t keyRows;        /* rows of the paged key tensor = owners * history */
   uint32_t gatherRows;     /* 1 = also write the dense [T,2048,tokenBytes] gather */
   uint32_t liVariant;      /* 0 = tcgen05 kernel, 1 = CUDA-core cross-check kernel */
-  uint32_t headSum;        /* KVIP_HEAD_SUM_* for the tcgen05 kernel */
+  uint32_t reserved0;
   uint32_t reserved1;
 } KvipRuntimeShape;
 
@@ -120,7 +113,7 @@ typedef struct KvipLiArgs {
                                  KVIP_ERR_PIPELINE in *status; 0 in production */
   uint32_t wait_kilocycles;   /* limit of every barrier wait inside the kernel, in units of 1024 SM clock cycles;
                                  0 = the default of about one second */
-  uint32_t head_sum;          /* KVIP_HEAD_SUM_*: how accumulators are read back for the sum over heads */
+  uint32_t reserved0;
 } KvipLiArgs;
 uint32_t kvip_b200_li_score(const KvipLiArgs* args, void* stream);
 /* CUDA-core restatement of the same formula with the oracle's accumulation order;

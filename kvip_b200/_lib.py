@@ -21,7 +21,6 @@ BAD_ARGUMENT = 100000
 KEY_FP8, KEY_BF16 = 0, 1
 WEIGHT_BF16, WEIGHT_FP32 = 0, 1
 SCORE_FP32, SCORE_BF16_AWAY = 0, 1
-HEAD_SUM_AUTO, HEAD_SUM_ROWS, HEAD_SUM_QUADS, HEAD_SUM_ROWS_AHEAD = 0, 1, 2, 3
 
 
 def _struct(name, pointer_fields, scalar_fields):
@@ -35,7 +34,7 @@ class RuntimeShape(ctypes.Structure):
     _fields_ = [(name, u32) for name in (
         "batch", "history", "resident", "indexHeads", "smCount", "queries", "keyDtype", "weightDtype",
         "scoreMode", "pagesPerRequest", "finalWorkers", "scoreStride", "outputStride", "owners",
-        "tokenBytes", "keyRows", "gatherRows", "liVariant", "headSum", "reserved1")]
+        "tokenBytes", "keyRows", "gatherRows", "liVariant", "reserved0", "reserved1")]
 
     @classmethod
     def prepare(cls, library, **fields):
@@ -49,7 +48,7 @@ LiArgs = _struct("LiArgs", (
     "query", "keys", "weights", "query_scale", "key_scale", "key_lengths", "query_ends", "block_table",
     "scores", "status"), [(n, u32) for n in (
         "batch", "queries", "heads", "pagesPerRequest", "keyRows", "scoreStride", "keyDtype", "weightDtype",
-        "scoreMode", "ctas", "stages", "withhold_tile", "wait_kilocycles", "head_sum")])
+        "scoreMode", "ctas", "stages", "withhold_tile", "wait_kilocycles", "reserved0")])
 
 TopkArgs = _struct("TopkArgs", ("scores", "key_lengths", "query_ends", "topk", "topk_scores", "histogram"),
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "base_index")] + [("split_scratch", vp)])

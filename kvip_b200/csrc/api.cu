@@ -93,7 +93,7 @@ extern "C" uint32_t kvip_prepare_shape(KvipRuntimeShape* s) {
   KVIP_REQUIRE(s->history >= s->resident && s->history <= (1u << 21), "prepare_shape: history must be in resident..2^21");
   KVIP_REQUIRE(s->tokenBytes >= 16 && s->tokenBytes % 16 == 0, "prepare_shape: token bytes must be a multiple of 16");
   KVIP_REQUIRE(s->keyDtype <= KVIP_KEY_BF16 && s->weightDtype <= KVIP_WEIGHT_FP32 && s->scoreMode <= KVIP_SCORE_BF16_AWAY &&
-                   s->liVariant <= 1 && s->headSum <= KVIP_HEAD_SUM_ROWS_AHEAD, "prepare_shape: unknown dtype, score mode, LI variant or head-sum mode");
+                   s->liVariant <= 1, "prepare_shape: unknown dtype, score mode or LI variant");
   s->pagesPerRequest = s->history / 128;
   s->scoreStride = s->history;
   s->finalWorkers = 4;
@@ -194,7 +194,7 @@ extern "C" uint32_t kvip_lifetch_streaming_forward(void* bindings_v, void* updat
   li.block_table = ptr<const int32_t>(bind[7]); li.scores = ptr<float>(bind[12]); li.status = ptr<int32_t>(ws->li_status);
   li.batch = s.batch; li.queries = s.queries; li.heads = s.indexHeads; li.pagesPerRequest = s.pagesPerRequest;
   li.keyRows = s.keyRows; li.scoreStride = s.scoreStride; li.keyDtype = s.keyDtype; li.weightDtype = s.weightDtype;
-  li.scoreMode = s.scoreMode; li.ctas = s.smCount; li.head_sum = s.headSum;
+  li.scoreMode = s.scoreMode; li.ctas = s.smCount;
   KVIP_REQUIRE(li.query && li.keys && li.weights && li.key_lengths && li.query_ends && li.block_table && li.scores && li.status,
                "forward: an LI operand is unbound");
   const bool run_li = select_phase && !(ws->options & KVIP_OPTION_SCORES_READY);

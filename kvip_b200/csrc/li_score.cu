@@ -21,14 +21,6 @@
 //     accumulators, and the number of units reduced at once divides the number of accumulators, so
 //     every use of one stage or accumulator is waited for by the same thread, in order: a
 //     parity wait by a thread that runs a whole phase ahead of the barrier would pass at once;
-//   * two ways to read an accumulator back for the reduction over heads. ROWS: a thread owns one token row and
-//     walks its columns (tcgen05.ld 32x32b); every head weight is then the same for all lanes of a warp and
-//     comes from shared memory, one 16-byte broadcast load per four columns. At 64 columns per key page that
-//     hides under the HBM time of the page; at 128 or more it is what sets the pace (a 16-byte load by 32 lanes
-//     costs four shared-memory wavefronts whatever the addresses). QUADS: tcgen05.ld 16x256b hands a thread two
-//     adjacent columns out of every eight, for four token rows; a lane then needs only a quarter of the head
-//     weights (16 of 64), which it loads once per query slot, and the four lanes that share a row add their
-//     partial sums with two shuffles. Same arithmetic in fp32, a quarter of the shared-memory traffic;
 //   * every mbarrier wait is bounded: when a wait gives up the CTA sets
 //     KVIP_ERR_PIPELINE in the status word, all roles leave their loops, tensor memory
 //     is released and the kernel returns.
@@ -159,39 +151,6 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
-// 16 lanes x 64 columns of fp32 in the fragment layout of an MMA accumulator: with g = lane / 4 and t = lane % 4,
-// registers 4k .. 4k+3 hold (row g, columns 8k + 2t and 8k + 2t + 1) and (row g + 8, the same two columns).
-__device__ __forceinline__ void tmem_ld_16x256_x8(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_16x256_x4(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -228,16 +187,12 @@ __device__ __forceinline__ float load_weight(const KvipLiArgs& a, uint32_t index
   return w;
 }
 
-// kEpilogue: how accumulators are read back (see the header comment): kRows, kQuads, or kRowsAhead = kRows with the
-// tensor-memory load of the next 16 columns in flight while the current 16 are reduced.
-constexpr int kRows = 0, kQuadsLayout = 1, kRowsAhead = 2;
-template <bool kBf16, int kEpilogue>
+template <bool kBf16>
 __global__ void __launch_bounds__(kLiThreads, 1)
 li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap query_map,
                  const __grid_constant__ KvipLiArgs a, const uint32_t S) {
   using Cfg = LiCfg<kBf16>;
   extern __shared__ uint8_t smem_raw[];
-  constexpr bool kQuads = kEpilogue == kQuadsLayout;
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -452,9 +407,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
     // far longer than the time the next key page needs to arrive, so several units are reduced concurrently.
     const uint32_t group = (warp - kFirstEpilogueWarp) >> 2;
     const uint32_t quad = warp & 3u;              // tensor-memory lane quadrant of this warp
-    // the token row (inside the page) whose score this thread scales and stores. ROWS: the row it reduced. QUADS: the
-    // four lanes of a group reduce rows g, g + 8, g + 16, g + 24 of the quadrant together; lane t of them keeps row g + 8t
-    const uint32_t row = quad * 32u + (kQuads ? (lane >> 2) + 8u * (lane & 3u) : lane);
+    const uint32_t row = quad * 32u + lane;       // token row inside the page
     float* w_warp = w_smem + (warp - kFirstEpilogueWarp) * n_max;  // private copy: no cross-warp barrier needed
     TileCursor cur(prefix, a.batch), ahead(prefix, a.batch);
     uint32_t live_mask = 0;
@@ -487,15 +440,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       page_next = page_of(tile_of(u + 2 * G));
       if (static_cast<int32_t>(b) != bound) {
         __syncwarp();
-        if constexpr (kQuads) {
-          // lane t of a group needs heads 8k + 2t and 8k + 2t + 1: stored as H / 4 consecutive floats per (slot, t)
-          for (uint32_t i = lane; i < nq * H; i += 32u) {
-            const uint32_t q = i / H, head = i % H;
-            w_warp[q * H + ((head >> 1) & 3u) * (H / 4u) + (head >> 3) * 2u + (head & 1u)] = load_weight(a, b * Q * H + i);
-          }
-        } else {
-          for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
-        }
+        for (uint32_t i = lane; i < nq * H; i += 32u) w_warp[i] = load_weight(a, b * Q * H + i);
         live_mask = 0;
         for (uint32_t q = 0; q < nq; ++q) live_mask |= (a.query_ends[b * Q + q] > 0 ? 1u : 0u) << q;
         __syncwarp();
@@ -507,97 +452,6 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * acc_stride;
       const uint32_t q_first = h * unit_queries, q_last = min(nq, q_first + unit_queries);
-      if constexpr (kQuads) {
-        const uint32_t t4 = lane & 3u;
-        for (uint32_t q = q_first; q < q_last; ++q) {
-          // this lane's quarter of the slot's head weights (16 of 64, or 8 of 32)
-          float w[16];
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + t4 * (H / 4u));
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            const float4 x = j * 4u < H / 4u ? w4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-            w[4 * j] = x.x; w[4 * j + 1] = x.y; w[4 * j + 2] = x.z; w[4 * j + 3] = x.w;
-          }
-          float sums[4];
-#pragma unroll
-          for (uint32_t half = 0; half < 2; ++half) {   // rows g, g + 8 of lanes 0-15, then of lanes 16-31 of the quadrant
-            float even0 = 0.f, odd0 = 0.f, even1 = 0.f, odd1 = 0.f;
-            const uint32_t at = taddr + ((half * 16u) << 16) + (q - q_first) * H;
-            if (H == 64u) {
-              uint32_t v[32];
-              tmem_ld_16x256_x8(at, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (uint32_t k = 0; k < 8; ++k) {
-                even0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 0]), 0.f), w[2 * k], even0);
-                odd0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 1]), 0.f), w[2 * k + 1], odd0);
-                even1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 2]), 0.f), w[2 * k], even1);
-                odd1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 3]), 0.f), w[2 * k + 1], odd1);
-              }
-            } else {
-              uint32_t v[16];
-              tmem_ld_16x256_x4(at, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (uint32_t k = 0; k < 4; ++k) {
-                even0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 0]), 0.f), w[2 * k], even0);
-                odd0 = fmaf(fmaxf(__uint_as_float(v[4 * k + 1]), 0.f), w[2 * k + 1], odd0);
-                even1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 2]), 0.f), w[2 * k], even1);
-                odd1 = fmaf(fmaxf(__uint_as_float(v[4 * k + 3]), 0.f), w[2 * k + 1], odd1);
-              }
-            }
-            sums[2 * half] = even0 + odd0;
-            sums[2 * half + 1] = even1 + odd1;
-          }
-          // the four lanes of a group hold the four quarters of every row's sum
-#pragma unroll
-          for (uint32_t r = 0; r < 4; ++r) {
-            sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], 1);
-            sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], 2);
-          }
-          if ((live_mask >> q) & 1u) {
-            // sums[r] is row g + 8r: lane t keeps r = t
-            float score = (t4 == 0u ? sums[0] : (t4 == 1u ? sums[1] : (t4 == 2u ? sums[2] : sums[3]))) * kscale;
-            if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
-            a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
-          }
-        }
-      } else if constexpr (kEpilogue == kRowsAhead) {
-        // the unit's columns in pieces of 16, two register buffers: while one piece is reduced the load of the next
-        // is in flight, so a warp does not sit out a tensor-memory round trip per piece
-        const uint32_t pieces = (q_last - q_first) * H / 16u;   // H is 32 or 64: a piece never straddles two query slots
-        uint32_t even[16], odd[16];   // two named buffers: indexed statically, they stay in registers
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        auto reduce = [&](const uint32_t(&v)[16], uint32_t piece) {
-          const uint32_t column = piece * 16u, q = q_first + column / H;
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q_first * H + column);
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            const float4 w = w4[j];
-            s0 = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, s0);
-            s1 = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, s1);
-            s2 = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, s2);
-            s3 = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, s3);
-          }
-          if ((column + 16u) % H == 0u) {   // the slot's last piece
-            if ((live_mask >> q) & 1u) {
-              float score = ((s0 + s2) + (s1 + s3)) * kscale;
-              if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
-              a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
-            }
-            s0 = s1 = s2 = s3 = 0.f;
-          }
-        };
-        tmem_ld_32x16(taddr, even);
-        for (uint32_t piece = 0; piece < pieces; piece += 2u) {   // `pieces` is even: a slot is 32 or 64 columns
-          tmem_ld_wait();
-          tmem_ld_32x16(taddr + (piece + 1u) * 16u, odd);
-          reduce(even, piece);
-          tmem_ld_wait();
-          if (piece + 2u < pieces) tmem_ld_32x16(taddr + (piece + 2u) * 16u, even);
-          reduce(odd, piece + 1u);
-        }
-      } else
       for (uint32_t q = q_first; q < q_last; ++q) {
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
         // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
@@ -736,11 +590,10 @@ uint32_t validate(const KvipLiArgs* a) {
                "li_score: unknown dtype or score mode");
   KVIP_REQUIRE((reinterpret_cast<uintptr_t>(a->keys) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a->query) & 15u) == 0,
                "li_score: keys and query must be 16-byte aligned");
-  KVIP_REQUIRE(a->head_sum <= KVIP_HEAD_SUM_ROWS_AHEAD, "li_score: unknown head-sum mode");
   return 0;
 }
 
-template <bool kBf16, int kEpilogue>
+template <bool kBf16>
 uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   using Cfg = LiCfg<kBf16>;
   CUtensorMap key_map, query_map;
@@ -749,8 +602,8 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
     set_error("li_score: cuTensorMapEncodeTiled failed");
     return KVIP_BAD_ARGUMENT;
   }
-  constexpr KernelSlot slot = static_cast<KernelSlot>(kSlotLi + 2 * kEpilogue + (kBf16 ? 1 : 0));
-  if (uint32_t bad = raise_dynamic_smem(slot, reinterpret_cast<const void*>(li_score_tcgen05<kBf16, kEpilogue>),
+  if (uint32_t bad = raise_dynamic_smem(kBf16 ? kSlotLiBf16 : kSlotLiFp8,
+                                        reinterpret_cast<const void*>(li_score_tcgen05<kBf16>),
                                         static_cast<int>(Cfg::kSmemLimit), "li_score attribute"))
     return bad;
   const uint32_t n_max = a.queries * a.heads;
@@ -759,7 +612,7 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
   const uint32_t smem_bytes = Cfg::fixed_bytes(n_max) + stages * Cfg::kTileBytes;
   uint32_t ctas = a.ctas;
   if (!ctas) ctas = device_sm_count();
-  li_score_tcgen05<kBf16, kEpilogue><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
+  li_score_tcgen05<kBf16><<<ctas, kLiThreads, smem_bytes, stream>>>(key_map, query_map, a, stages);
   count_launch();
   return check_launch("li_score_tcgen05");
 }
@@ -767,17 +620,7 @@ uint32_t launch_tcgen05(const KvipLiArgs& a, cudaStream_t stream) {
 }  // namespace
 
 uint32_t launch_li_score(const KvipLiArgs& a, cudaStream_t stream) {
-  const bool wide = a.queries * a.heads >= 128u;
-  const uint32_t mode = a.head_sum != KVIP_HEAD_SUM_AUTO ? a.head_sum : (wide ? KVIP_HEAD_SUM_ROWS_AHEAD : KVIP_HEAD_SUM_ROWS);
-  const bool bf16 = a.keyDtype == KVIP_KEY_BF16;
-  switch (mode) {
-    case KVIP_HEAD_SUM_QUADS:
-      return bf16 ? launch_tcgen05<true, kQuadsLayout>(a, stream) : launch_tcgen05<false, kQuadsLayout>(a, stream);
-    case KVIP_HEAD_SUM_ROWS_AHEAD:
-      return bf16 ? launch_tcgen05<true, kRowsAhead>(a, stream) : launch_tcgen05<false, kRowsAhead>(a, stream);
-    default:
-      return bf16 ? launch_tcgen05<true, kRows>(a, stream) : launch_tcgen05<false, kRows>(a, stream);
-  }
+  return a.keyDtype == KVIP_KEY_BF16 ? launch_tcgen05<true>(a, stream) : launch_tcgen05<false>(a, stream);
 }
 
 uint32_t launch_li_score_simt(const KvipLiArgs& a, cudaStream_t stream) {

@@ -170,7 +170,7 @@ class CudaBinding:
     def __init__(self, torch, arguments, lease, output, *, batch, history, resident, query_ends, hot_valid,
                  token_addresses, row_owners=None, tail_bounds=None, output_stride=None, scratch=None,
                  token_bytes=None, queries=None, score_mode=_lib.SCORE_FP32, sm_count=0, gather_output=None,
-                 li_variant=0, prefetch_limit=0, source=None, library=None, head_sum=_lib.HEAD_SUM_AUTO):
+                 li_variant=0, prefetch_limit=0, source=None, library=None):
         self.torch, self.lease = torch, lease
         self.library = _lib.load_library(library)
         if len(arguments) != 14:
@@ -200,8 +200,7 @@ class CudaBinding:
             queries=queries, keyDtype=_lib.KEY_BF16 if keys.dtype == torch.bfloat16 else _lib.KEY_FP8,
             weightDtype=_lib.WEIGHT_FP32 if weights.dtype == torch.float32 else _lib.WEIGHT_BF16,
             scoreMode=score_mode, outputStride=output_stride, owners=owners, tokenBytes=token_bytes,
-            keyRows=keys.numel() // 128, gatherRows=int(gather_output is not None), liVariant=li_variant,
-            headSum=head_sum)
+            keyRows=keys.numel() // 128, gatherRows=int(gather_output is not None), liVariant=li_variant)
         self.shape = self.runtime_shape
         self.shape_pointer = ctypes.byref(self.runtime_shape)
         self.prefetch_limit = prefetch_limit

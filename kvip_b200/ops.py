@@ -32,7 +32,7 @@ def _require(tensor, name, dtype=None, device=None):
 
 def li_score(query, keys, weights, query_scale, key_scale, key_lengths, query_ends, block_table, scores=None, *,
              status=None, score_mode=_lib.SCORE_FP32, ctas=0, stages=0, simt=False, withhold_tile=0,
-             wait_kilocycles=0, head_sum=_lib.HEAD_SUM_AUTO):
+             wait_kilocycles=0):
     """scores[t, s] = kscale[s] * sum_h W[t,h] * relu(q[t,h,:] . k[s,:]) over the paged Index cache.
 
     query [B*Q, H, 128] float8_e4m3fn/uint8 or bfloat16; keys [rows, 128] same element type;
@@ -65,7 +65,7 @@ def li_score(query, keys, weights, query_scale, key_scale, key_lengths, query_en
         keyDtype=_lib.KEY_BF16 if bf16 else _lib.KEY_FP8,
         weightDtype=_lib.WEIGHT_FP32 if weights.dtype == torch.float32 else _lib.WEIGHT_BF16,
         scoreMode=score_mode, ctas=ctas, stages=stages, withhold_tile=withhold_tile,
-        wait_kilocycles=wait_kilocycles, head_sum=head_sum)
+        wait_kilocycles=wait_kilocycles)
     lib = _lib.load_library()
     fn = lib.kvip_b200_li_score_simt if simt else lib.kvip_b200_li_score
     _lib.check(fn(ctypes.byref(args), _stream(device)), "li_score")

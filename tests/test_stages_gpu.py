@@ -54,18 +54,13 @@ def test_li_simt_matches_c_oracle_bit_exact(spec, device):
     assert np.array_equal(got[mask].view(np.uint32), expected[mask].view(np.uint32))
 
 
-HEAD_SUMS = [_lib.HEAD_SUM_ROWS, _lib.HEAD_SUM_QUADS, _lib.HEAD_SUM_ROWS_AHEAD]
-
-
 @pytest.mark.parametrize("spec", LI_CASES, ids=lambda s: f"seed{s['seed']}")
 @pytest.mark.parametrize("score_mode", [0, 1])
-@pytest.mark.parametrize("head_sum", HEAD_SUMS, ids=["rows", "quads", "rows_ahead"])
-def test_li_tcgen05_within_tolerance(spec, score_mode, head_sum, device):
-    """Against the NumPy golden formula, for both ways the epilogue reads an accumulator back (one token row per
-    thread; the MMA fragment layout with a quarter of the head weights per lane)."""
+def test_li_tcgen05_within_tolerance(spec, score_mode, device):
+    """Against the NumPy golden formula."""
     case = workloads.li_case(**spec)
     expected = workloads.oracle_scores(case, score_mode=score_mode)
-    scores, _ = _li(case, device, score_mode=score_mode, head_sum=head_sum)
+    scores, _ = _li(case, device, score_mode=score_mode)
     got = scores.cpu().numpy()
     mask = _valid_mask(case, expected.shape[1])
     allowed = workloads.li_tolerance(case, np.where(mask, expected, 0))
@@ -91,10 +86,8 @@ def test_li_tcgen05_rings_wrap(queries, heads, key_dtype, stages, device):
     expected = expected.cpu().numpy()
     mask = _valid_mask(case, expected.shape[1])
     allowed = workloads.li_tolerance(case, np.where(mask, expected, 0))
-    for head_sum in HEAD_SUMS:
-        scores, _ = _li(case, device, ctas=2, stages=stages, head_sum=head_sum)
-        got = scores.cpu().numpy()
-        assert (np.abs(got - expected)[mask] <= allowed[mask]).all(), (queries, heads, stages, head_sum)
+    scores, _ = _li(case, device, ctas=2, stages=stages)
+    assert (np.abs(scores.cpu().numpy() - expected)[mask] <= allowed[mask]).all(), (queries, heads, stages)
 
 
 @pytest.mark.parametrize("key_dtype", ["fp8", "bf16"])
@@ -108,11 +101,9 @@ def test_li_tcgen05_ragged_query_slots_two_units(key_dtype, device):
     expected = expected.cpu().numpy()
     mask = _valid_mask(case, expected.shape[1])
     allowed = workloads.li_tolerance(case, np.where(mask, expected, 0))
-    for head_sum in HEAD_SUMS:
-        for kw in (dict(), dict(ctas=2), dict(ctas=3, stages=3)):
-            scores, _ = _li(case, device, head_sum=head_sum, **kw)
-            got = scores.cpu().numpy()
-            assert (np.abs(got - expected)[mask] <= allowed[mask]).all(), (kw, head_sum)
+    for kw in (dict(), dict(ctas=2), dict(ctas=3, stages=3)):
+        scores, _ = _li(case, device, **kw)
+        assert (np.abs(scores.cpu().numpy() - expected)[mask] <= allowed[mask]).all(), kw
 
 
 def test_li_bounded_wait_gives_up_and_reports(device):
@@ -151,8 +142,6 @@ def test_chunked_prefill_li_and_topk(device):
     mask = _valid_mask(case, expected.shape[1])
     allowed = workloads.li_tolerance(case, np.where(mask, expected, 0))
     assert (np.abs(got - expected)[mask] <= allowed[mask]).all()
-    rows, _ = _li(case, device, head_sum=_lib.HEAD_SUM_ROWS)   # the default read four 64-head slots in the fragment layout
-    assert (np.abs(rows.cpu().numpy() - expected)[mask] <= allowed[mask]).all()
     ends = case["query_ends"].reshape(-1, 1)
     picked = ops.topk(scores, t["key_lengths"], t["query_ends"])
     torch.cuda.synchronize()
@@ -181,9 +170,8 @@ def test_li_exact_binary_fraction_fixture(device):
     for mode in (0, 1):
         expected = workloads.oracle_scores(case, score_mode=mode)
         mask = _valid_mask(case, expected.shape[1])
-        for head_sum in HEAD_SUMS:   # every partial sum is exact: the order of the additions cannot show
-            scores, _ = _li(case, device, score_mode=mode, head_sum=head_sum)
-            assert np.array_equal(scores.cpu().numpy()[mask], expected[mask]), (mode, head_sum)
+        scores, _ = _li(case, device, score_mode=mode)
+        assert np.array_equal(scores.cpu().numpy()[mask], expected[mask]), mode
 
 
 def _topk_check(scores_np, key_lengths, query_ends, device, base_index=0):
