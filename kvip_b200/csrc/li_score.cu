@@ -34,7 +34,11 @@ namespace {
 
 constexpr uint32_t kEpilogueGroups = 4;
 constexpr uint32_t kMmaWarps = 4;          // MMA issuers: warps 1..4 (one thread each)
-constexpr uint32_t kFirstEpilogueWarp = 5; // any four consecutive warps cover the four tensor-memory lane quadrants
+// Warps 0-7 are two "control" warpgroups (producer, four issuers, three idle warps), warps 8-23 four epilogue
+// warpgroups: register budgets are moved between whole warpgroups (setmaxnreg), from the control warps, which need
+// few, to the epilogue warps, which keep 64 accumulator columns in registers at a time.
+constexpr uint32_t kFirstEpilogueWarp = 8; // any four consecutive warps cover the four tensor-memory lane quadrants
+constexpr uint32_t kControlRegisters = 40, kEpilogueRegisters = 96;
 constexpr uint32_t kLiThreads = 32 * kFirstEpilogueWarp + 128 * kEpilogueGroups;
 constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (512 columns / stride)
 constexpr uint32_t kMaxBatch = 1024;
@@ -282,6 +286,10 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t tile_begin = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * blockIdx.x) / gridDim.x);
   const uint32_t tile_end = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * (blockIdx.x + 1)) / gridDim.x);
 
+  // 768 threads start with 80 registers each; the control warpgroups give 2 x 128 x 40 back and the epilogue
+  // warpgroups take 4 x 128 x 16 of them
+  if (warp < kFirstEpilogueWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegisters));
   if (warp == 0) {
     // ================= TMA producer =================
     // The whole warp stays in the loop: each lane looks up the page of one of the next 32 tiles (one
@@ -401,7 +409,9 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         ++seq;
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegisters));
     // ================= epilogue: groups of 4 warps, one token row per thread =================
     // One unit's reduction is a long dependent chain (tensor-memory load, 64 max+fma pairs per query, store),
     // far longer than the time the next key page needs to arrive, so several units are reduced concurrently.
@@ -456,10 +466,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
         // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        for (uint32_t c = 0; c < H; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + (q - q_first) * H + c, v);
-          tmem_ld_wait();
+        auto reduce = [&](const uint32_t(&v)[32], uint32_t c) {
           const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j) {
@@ -469,6 +476,21 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
             s2 = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, s2);
             s3 = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, s3);
           }
+        };
+        if (H == 64u) {
+          // both halves of the slot's columns behind ONE wait: a tensor-memory load takes about a third of a
+          // microsecond to come back here, and a warp has nothing else to do meanwhile
+          uint32_t lower[32], upper[32];
+          tmem_ld_32x32(taddr + (q - q_first) * 64u, lower);
+          tmem_ld_32x32(taddr + (q - q_first) * 64u + 32u, upper);
+          tmem_ld_wait();
+          reduce(lower, 0u);
+          reduce(upper, 32u);
+        } else {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + (q - q_first) * 32u, v);
+          tmem_ld_wait();
+          reduce(v, 0u);
         }
         if ((live_mask >> q) & 1u) {
           float score = ((s0 + s2) + (s1 + s3)) * kscale;   // (even heads) + (odd heads)
