@@ -929,14 +929,19 @@ def run_seqshard(args):
         step()
         launches = (lib.kvip_b200_launch_count() - before) * args.steps
         stream.synchronize()
-        # One rank: the step is replayed from a CUDA graph. Several ranks: issued eagerly; capturing the NCCL
-        # all-gather made a two-rank run of this bench stop responding, so it stays outside graphs.
+        # One rank: the step is replayed from one CUDA graph. Several ranks: two graphs of this library's kernels
+        # (LI + local TopK, merge) with the NCCL all-gather issued eagerly between them; capturing the all-gather
+        # itself made a two-rank run of this bench stop responding, so it stays outside graphs.
         graph, replay = None, step
         if world == 1:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
             replay = graph.replay
+        else:
+            sharded.capture(lambda: ops.li_score(query, keys, weights, query_scale, key_scale, lengths, ends, table,
+                                                 scores, status=status), scores, lengths, ends, begin)
+            replay = sharded.replay
 
         def e2e_step():  # noqa: F811 - same name on purpose: the graph version replaces the eager one
             query.view(torch.uint8).copy_(host_query, non_blocking=True)
@@ -970,7 +975,7 @@ def run_seqshard(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
             "config": {"workload": args.workload, "context": total, "keys_per_rank": keys_here, "index_heads": heads,
                        "topk": 2048, "exchange": "one all-gather of 2048 x (f32, i32) per rank, then merge",
-                       "cuda_graph": graph is not None,
+                       "cuda_graph": True if graph is not None else "kernels on either side of the eager all-gather",
                        "l2": "shard keys %.0f MB per step" % (keys_here * 132 / 1e6)},
             "e2e": {"value": args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": host_query.numel(),
                     "d2h_bytes_per_step": host_merged.numel() * 4, "ms_per_step": e2e_elapsed / args.steps * 1e3},

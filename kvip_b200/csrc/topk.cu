@@ -63,30 +63,65 @@ __global__ void __launch_bounds__(kThreads) topk_select(const KvipTopkArgs a) {
 // memory once; the 2048th largest key is found by radix select over them (three passes over shared memory), ties
 // at that key are settled towards the lower index by a second radix select over the tied indices, the 2048
 // winners are compacted and only they are sorted (by "is a tie", then index): the canonical order. Sorting all
-// candidates instead cost 105 block-wide compare-exchange rounds over 16384 entries; this takes 66 over 2048.
+// candidates instead cost 105 block-wide compare-exchange rounds over 16384 entries; this takes 66 over 2048, of
+// which only the 15 with a partner distance of 64 or more go through shared memory and a block barrier.
 constexpr uint32_t kMergeMax = 8u * kTop;
 
-__device__ __forceinline__ void bitonic_sort(uint32_t* data, uint32_t n) {   // ascending; n a power of two
-  for (uint32_t k = 2; k <= n; k <<= 1) {
-    for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-      for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const uint32_t partner = i ^ j;
-        if (partner > i) {
-          const uint32_t x = data[i], y = data[partner];
-          const bool ascending = (i & k) == 0;
-          if ((x > y) == ascending) { data[i] = y; data[partner] = x; }
-        }
-      }
+// Ascending bitonic sort of data[0..2048) by the 1024 threads of the block. Thread t keeps elements 2t and 2t+1 in
+// registers, so a warp owns 64 consecutive elements: compare-exchange rounds with a partner distance below 64 are
+// register moves and warp shuffles, the others work on shared memory between block barriers.
+__device__ __forceinline__ void bitonic_sort_2048(uint32_t* data) {
+  const uint32_t t = threadIdx.x, e0 = 2u * t;
+  uint32_t x0 = data[e0], x1 = data[e0 + 1u];
+  auto in_warp = [&](uint32_t k, uint32_t j_from) {   // rounds j_from, j_from / 2, ..., 1 of merge width k
+    const bool ascending = (e0 & k) == 0;
+    for (uint32_t j = j_from; j >= 2u; j >>= 1) {
+      const bool keep_min = ((e0 & j) == 0) == ascending;
+      const uint32_t y0 = __shfl_xor_sync(0xffffffffu, x0, j >> 1), y1 = __shfl_xor_sync(0xffffffffu, x1, j >> 1);
+      x0 = keep_min ? min(x0, y0) : max(x0, y0);
+      x1 = keep_min ? min(x1, y1) : max(x1, y1);
+    }
+    const uint32_t low = min(x0, x1), high = max(x0, x1);
+    x0 = ascending ? low : high;
+    x1 = ascending ? high : low;
+  };
+  for (uint32_t k = 2; k <= 64u; k <<= 1) in_warp(k, k >> 1);
+  for (uint32_t k = 128; k <= kTop; k <<= 1) {
+    data[e0] = x0;
+    data[e0 + 1u] = x1;
+    __syncthreads();
+    for (uint32_t j = k >> 1; j >= 64u; j >>= 1) {
+      const uint32_t e = (t / j) * (2u * j) + (t % j);   // the lower element of this thread's pair
+      const uint32_t x = data[e], y = data[e + j];
+      if ((x > y) == ((e & k) == 0)) { data[e] = y; data[e + j] = x; }
       __syncthreads();
     }
+    x0 = data[e0];
+    x1 = data[e0 + 1u];
+    in_warp(k, 32u);
+  }
+  data[e0] = x0;
+  data[e0 + 1u] = x1;
+  __syncthreads();
+}
+
+// Histogram add for candidates that mostly share their leading digits (the best scores of every shard lie close
+// together): lanes with the same bin are found with a match vote and one of them adds for all, so a warp issues one
+// shared-memory atomic per DISTINCT bin instead of up to 32 serialised ones on the same word.
+__device__ __forceinline__ void hist_add_matched(uint32_t* hist, bool valid, uint32_t bin) {
+  const uint32_t active = __ballot_sync(0xffffffffu, valid);
+  if (valid) {
+    const uint32_t peers = __match_any_sync(active, bin);
+    if ((threadIdx.x & 31u) == static_cast<uint32_t>(__ffs(static_cast<int>(peers)) - 1)) atomicAdd(hist + bin, __popc(peers));
   }
 }
 
 // The `want`-th largest of the values value(i), i < n with member(i) (12 + 12 + 8 bit radix select, all threads of
-// the block call). Returns the value; *take = how many entries EQUAL to it belong to the `want` largest.
+// the block call). Returns the value; *take = how many entries EQUAL to it belong to the `want` largest, *equal = how
+// many entries equal it in all.
 template <typename Value, typename Member>
 __device__ uint32_t kth_largest(uint32_t n, uint32_t want, Value value, Member member, uint32_t* hist, uint32_t* scan_scratch,
-                                uint32_t* found, uint32_t* take) {
+                                uint32_t* found, uint32_t* take, uint32_t* equal) {
   const uint32_t tid = threadIdx.x;
   uint32_t prefix = 0, prefix_mask = 0, remaining = want;
 #pragma unroll 1
@@ -95,13 +130,13 @@ __device__ uint32_t kth_largest(uint32_t n, uint32_t want, Value value, Member m
     const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
     const uint32_t bins = 1u << bits;
     for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
-    if (tid == 0) { found[0] = 0; found[1] = 0; }
+    if (tid == 0) { found[0] = 0; found[1] = 0; found[2] = 0; }
     __syncthreads();
-    for (uint32_t r = 0; r * kThreads < n; ++r) {   // block-uniform trip count: hist_add votes per warp
+    for (uint32_t r = 0; r * kThreads < n; ++r) {   // block-uniform trip count: the add votes per warp
       const uint32_t i = r * kThreads + tid;
       const bool in = i < n && member(i);
       const uint32_t v = in ? value(i) : 0u;
-      hist_add(hist, in && (v & prefix_mask) == prefix, (v >> shift) & (bins - 1u));
+      hist_add_matched(hist, in && (v & prefix_mask) == prefix, (v >> shift) & (bins - 1u));
     }
     __syncthreads();
     const uint32_t per = bins / kThreads ? bins / kThreads : 1u;  // 4, 4, then 1 (256 bins)
@@ -117,6 +152,7 @@ __device__ uint32_t kth_largest(uint32_t n, uint32_t want, Value value, Member m
         if (above < remaining && above + count >= remaining) {
           found[0] = group * per + static_cast<uint32_t>(j);
           found[1] = remaining - above;
+          found[2] = count;
         }
         above += count;
       }
@@ -125,6 +161,7 @@ __device__ uint32_t kth_largest(uint32_t n, uint32_t want, Value value, Member m
     prefix |= found[0] << shift;
     prefix_mask |= (bins - 1u) << shift;
     remaining = found[1];
+    *equal = found[2];   // of the last pass: the entries that match in every digit
     __syncthreads();
   }
   *take = remaining;
@@ -135,7 +172,7 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
   extern __shared__ uint32_t merge_smem[];   // [n] keys, [n] indices, [2048] winners
   __shared__ uint32_t hist[4096];
   __shared__ uint32_t scan_scratch[33];
-  __shared__ uint32_t found[2];
+  __shared__ uint32_t found[3];
   const uint32_t row = blockIdx.x, tid = threadIdx.x, n = a.shards * kTop;
   uint32_t* keys = merge_smem;
   int32_t* index = reinterpret_cast<int32_t*>(merge_smem + n);
@@ -155,14 +192,17 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
   // the cut: key of the 2048th largest candidate, how many candidates tied at it are taken, and below which index
   uint32_t cut_key = 0, ties_taken = 0, tie_index_limit = 0xffffffffu;   // defaults: every valid candidate wins
   if (valid > kTop) {   // block-uniform
+    uint32_t tied = 0;
     cut_key = kth_largest(n, kTop, [&](uint32_t i) { return keys[i]; }, [&](uint32_t i) { return index[i] >= 0; }, hist,
-                          scan_scratch, found, &ties_taken);
-    // lower index first among the tied: the ties_taken smallest indices = the ties_taken largest of ~index
-    uint32_t unused;
-    const uint32_t inverted = kth_largest(n, ties_taken, [&](uint32_t i) { return ~static_cast<uint32_t>(index[i]); },
-                                          [&](uint32_t i) { return index[i] >= 0 && keys[i] == cut_key; }, hist,
-                                          scan_scratch, found, &unused);
-    tie_index_limit = ~inverted;   // indices are distinct: exactly ties_taken tied candidates lie at or below it
+                          scan_scratch, found, &ties_taken, &tied);
+    if (ties_taken < tied) {   // block-uniform; with distinct scores at the cut there is nothing to settle
+      // lower index first among the tied: the ties_taken smallest indices = the ties_taken largest of ~index
+      uint32_t unused, unused_too;
+      const uint32_t inverted = kth_largest(n, ties_taken, [&](uint32_t i) { return ~static_cast<uint32_t>(index[i]); },
+                                            [&](uint32_t i) { return index[i] >= 0 && keys[i] == cut_key; }, hist,
+                                            scan_scratch, found, &unused, &unused_too);
+      tie_index_limit = ~inverted;   // indices are distinct: exactly ties_taken tied candidates lie at or below it
+    }
   }
   // winners, compacted in input order (a thread owns a contiguous run of candidates), as (is a tie, index). With a
   // cut they are then sorted: keys above the cut by ascending index, the tied ones after them by ascending index.
@@ -187,7 +227,7 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
       ++at;
     }
   __syncthreads();
-  if (valid > kTop) bitonic_sort(winners, kTop);   // block-uniform
+  if (valid > kTop) bitonic_sort_2048(winners);   // block-uniform
   int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
   for (uint32_t i = tid; i < kTop; i += kThreads)
     out[i] = winners[i] == 0xffffffffu ? -1 : static_cast<int32_t>(winners[i] & 0x7fffffffu);

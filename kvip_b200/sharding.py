@@ -63,6 +63,8 @@ class ShardedTopk:
         self.merged = torch.empty((rows, TOPK), dtype=torch.int32, device=device)
         self.local_scores, self.local_index = self.send[0].view(torch.float32), self.send[1]
 
+        self._before = self._after = None
+
     def __call__(self, scores, lengths, ends, base_index):
         import torch.distributed as dist
 
@@ -70,6 +72,41 @@ class ShardedTopk:
         ops.topk(scores, lengths, ends, self.local_index, out_scores=self.local_scores, base_index=base_index)
         dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
         return ops.topk_merge_gathered(self.gathered, self.merged)
+
+    def capture(self, score_step, scores, lengths, ends, base_index, warmup=3):
+        """Capture this rank's launches on either side of the exchange into two CUDA graphs: `score_step()` (the
+        caller's LI launch into `scores`) with the local TopK before it, the merge after it. Only kernels of this
+        library are captured; the all-gather stays an eager NCCL call between the two replays (`replay`). On a step
+        this short the host's launch cost is what the graphs remove."""
+        from . import ops
+
+        def before():
+            score_step()
+            ops.topk(scores, lengths, ends, self.local_index, out_scores=self.local_scores, base_index=base_index)
+
+        def after():
+            ops.topk_merge_gathered(self.gathered, self.merged)
+
+        for _ in range(max(warmup, 1)):
+            before()
+            after()
+        torch.cuda.current_stream().synchronize()
+        self._before, self._after = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._before, stream=torch.cuda.current_stream()):
+            before()
+        with torch.cuda.graph(self._after, stream=torch.cuda.current_stream()):
+            after()
+
+    def replay(self):
+        """One step of the captured form: graph (LI + local TopK), eager all-gather, graph (merge)."""
+        import torch.distributed as dist
+
+        if self._before is None:
+            raise RuntimeError("ShardedTopk.replay() before capture()")
+        self._before.replay()
+        dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
+        self._after.replay()
+        return self.merged
 
 
 def sequence_sharded_topk(local_scores, local_length, base_index, *, queries=1, group=None, local_topk=None,

@@ -321,6 +321,15 @@ def test_topk_merge_equals_unsharded(device):
     got = ops.topk_merge_gathered(torch.from_numpy(gathered).to(device))
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy(), expected)
+    # fewer shards (other candidate counts, odd ones included): the leading shards against the TopK of their keys
+    for fewer in (2, 3, 5):
+        keys_here = fewer * per
+        part = np.ascontiguousarray(whole[:, :keys_here])
+        expected_part = oracle_c.topk(part, np.full(2, keys_here, np.int32), np.full(2, keys_here, np.int32))
+        got = ops.topk_merge(torch.from_numpy(np.ascontiguousarray(cand_scores[:, :fewer * TOPK])).to(device),
+                             torch.from_numpy(np.ascontiguousarray(cand_index[:, :fewer * TOPK])).to(device))
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy(), expected_part), fewer
     # one shard alone: its list is the answer and comes back unchanged (ties at the cut stay behind the rest)
     single = oracle_c.topk(whole[:, :per].copy(), np.full(2, per, np.int32), np.full(2, per, np.int32))
     got = ops.topk_merge(torch.from_numpy(np.take_along_axis(whole, single, 1)).to(device), torch.from_numpy(single).to(device))
