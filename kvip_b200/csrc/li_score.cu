@@ -90,6 +90,26 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0u;
 }
+// Up to 64 tries in one tight loop (four instructions per try): waiting threads share their schedulers with the
+// epilogue warps, so every instruction a wait loop issues is taken from them.
+__device__ __forceinline__ bool mbar_try_64(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 64;\n\t"
+      "TRY_AGAIN:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra TRY_DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 q, n, 0;\n\t"
+      "@q bra TRY_AGAIN;\n\t"
+      "TRY_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0u;
+}
 struct WaitControl {
   volatile uint32_t* abort_flag;   // set by the first wait of the CTA that gives up; read by all the others
   long long limit;                 // SM clock cycles a wait may take
@@ -97,15 +117,23 @@ struct WaitControl {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitControl& control) {
   if (mbar_try(bar, parity)) return true;  // the common case costs one instruction
   const long long start = clock64();
-  for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try(bar, parity)) return true;
-    if ((spin & 63u) == 0u) {
-      if (*control.abort_flag) return false;
-      if (clock64() - start > control.limit) break;
-    }
+  for (;;) {
+    if (mbar_try_64(bar, parity)) return true;
+    if (*control.abort_flag) return false;
+    if (clock64() - start > control.limit) break;
   }
   *control.abort_flag = 1u;
   return false;
+}
+// Two fp32 fused multiply-adds in one instruction (packed pairs in 64-bit registers): the epilogue is bound by
+// the instructions it issues per accumulator column, and this halves the fma count. Each lane rounds like fmaf.
+__device__ __forceinline__ uint64_t pack_f32x2(float low, float high) {
+  uint64_t packed;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(low), "f"(high));
+  return packed;
+}
+__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t x, uint64_t w) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(x), "l"(w));
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y,
                                             uint32_t bar) {
@@ -465,16 +493,14 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       for (uint32_t q = q_first; q < q_last; ++q) {
         // four independent accumulation chains (heads 0,4,8.. / 1,5,.. / 2,6,.. / 3,7,..): the sum over heads
         // is compared with a tolerance, so its order is free, and the chains give the FMA pipe work to overlap
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        uint64_t s01 = 0ull, s23 = 0ull;   // (s0, s1) and (s2, s3) as packed pairs
         auto reduce = [&](const uint32_t(&v)[32], uint32_t c) {
-          const float4* w4 = reinterpret_cast<const float4*>(w_warp + q * H + c);
+          const ulonglong2* w4 = reinterpret_cast<const ulonglong2*>(w_warp + q * H + c);
 #pragma unroll
           for (uint32_t j = 0; j < 8; ++j) {
-            const float4 w = w4[j];
-            s0 = fmaf(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), w.x, s0);
-            s1 = fmaf(fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), w.y, s1);
-            s2 = fmaf(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), w.z, s2);
-            s3 = fmaf(fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), w.w, s3);
+            const ulonglong2 w = w4[j];   // (w0, w1), (w2, w3)
+            fma_f32x2(s01, pack_f32x2(fmaxf(__uint_as_float(v[4 * j + 0]), 0.f), fmaxf(__uint_as_float(v[4 * j + 1]), 0.f)), w.x);
+            fma_f32x2(s23, pack_f32x2(fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), fmaxf(__uint_as_float(v[4 * j + 3]), 0.f)), w.y);
           }
         };
         if (H == 64u) {
@@ -493,6 +519,8 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
           reduce(v, 0u);
         }
         if ((live_mask >> q) & 1u) {
+          const float s0 = __uint_as_float(static_cast<uint32_t>(s01)), s1 = __uint_as_float(static_cast<uint32_t>(s01 >> 32));
+          const float s2 = __uint_as_float(static_cast<uint32_t>(s23)), s3 = __uint_as_float(static_cast<uint32_t>(s23 >> 32));
           float score = ((s0 + s2) + (s1 + s3)) * kscale;   // (even heads) + (odd heads)
           if (a.scoreMode == KVIP_SCORE_BF16_AWAY) score = bf16_away(score);
           a.scores[static_cast<uint64_t>(b * Q + q) * a.scoreStride + token] = score;
