@@ -38,7 +38,7 @@ constexpr uint32_t kMmaWarps = 4;          // MMA issuers: warps 1..4 (one threa
 // warpgroups: register budgets are moved between whole warpgroups (setmaxnreg), from the control warps, which need
 // few, to the epilogue warps, which keep 64 accumulator columns in registers at a time.
 constexpr uint32_t kFirstEpilogueWarp = 8; // any four consecutive warps cover the four tensor-memory lane quadrants
-constexpr uint32_t kControlRegisters = 40, kEpilogueRegisters = 96;
+constexpr uint32_t kControlRegisters = 48, kEpilogueRegisters = 96;
 constexpr uint32_t kLiThreads = 32 * kFirstEpilogueWarp + 128 * kEpilogueGroups;
 constexpr uint32_t kMaxAcc = 8;       // accumulator buffers in tensor memory (512 columns / stride)
 constexpr uint32_t kMaxBatch = 1024;
@@ -314,7 +314,7 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   const uint32_t tile_begin = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * blockIdx.x) / gridDim.x);
   const uint32_t tile_end = static_cast<uint32_t>((static_cast<uint64_t>(total_tiles) * (blockIdx.x + 1)) / gridDim.x);
 
-  // 768 threads start with 80 registers each; the control warpgroups give 2 x 128 x 40 back and the epilogue
+  // 768 threads start with 80 registers each; the control warpgroups give 2 x 128 x 32 back and the epilogue
   // warpgroups take 4 x 128 x 16 of them
   if (warp < kFirstEpilogueWarp) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegisters));
