@@ -410,7 +410,10 @@ def measure_miss_path(torch, ops, p, stream, args):
            "commit_phase": "overlapped (LIFetch(overlap_fetch=True)): outputs, Index exchange and the gather of hit "
                            "entries on a side stream beside the fetch",
            "serial_commit_phase": {"ms_per_step": serial_seconds / steps * 1e3,
-                                   "misses_per_step": sum(serial_misses) / steps},
+                                   "misses_per_step": sum(serial_misses) / steps,
+                                   "note": "the two variants run consecutive pieces of one drifting stream, so their miss "
+                                           "counts differ; --workload decode_128k_b32_zipf compares them on identical "
+                                           "selections"},
            "query_drift": "AR(1), rho = 0.95, new bf16 k_I row per token quantised to FP8; eager launches"}
     if p.host_pool is not None:
         # host link alone: 16384 rows per request from distinct host rows into the resident slots
@@ -984,7 +987,7 @@ def run_seqshard(args):
                                              "events keep the launches from overlapping, so the sum exceeds the step"),
             "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": None, "peak": peaks()[0],
                          "unit": "GB/s", "frac": None, "traffic": None,
-                         "note": "latency-bound step: about 7 key pages per CTA; see ms_per_step"},
+                         "note": "latency-bound step: about %d key pages per CTA; see ms_per_step" % round(keys_here / 128 / 148)},
             "clocks": clocks,
         }), flush=True)
     dist.destroy_process_group()
