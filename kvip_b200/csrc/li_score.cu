@@ -15,7 +15,8 @@
 //     request's keys and scales are streamed from HBM exactly once for all of its
 //     query rows;
 //   * warp 0 = TMA producer, warps 1-4 = MMA issuers that take tiles round-robin (warp 1 owns
-//     tensor memory), warps 5-20 = four epilogue groups that take tiles round-robin; key
+//     tensor memory), warps 5-7 idle (they pad the control roles to two whole warpgroups), warps 8-23 = four
+//     epilogue groups that take tiles round-robin; key
 //     stages and a ring of up to eight accumulator buffers in tensor memory are handed over
 //     with mbarriers. The number of issuers divides the number of key stages and of
 //     accumulators, and the number of units reduced at once divides the number of accumulators, so
@@ -504,8 +505,9 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
           }
         };
         if (H == 64u) {
-          // both halves of the slot's columns behind ONE wait: a tensor-memory load takes about a third of a
-          // microsecond to come back here, and a warp has nothing else to do meanwhile
+          // both halves of the slot's columns behind ONE wait: alone a tensor-memory load comes back in tens of
+          // cycles, but here it queues behind the MMAs in flight and takes hundreds, and a warp has nothing else
+          // to do meanwhile
           uint32_t lower[32], upper[32];
           tmem_ld_32x32(taddr + (q - q_first) * 64u, lower);
           tmem_ld_32x32(taddr + (q - q_first) * 64u + 32u, upper);
