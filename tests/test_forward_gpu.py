@@ -732,3 +732,50 @@ def test_prefetch_windows_replay_from_a_graph(device):
             assert torch.equal(spec.gather_out, plain.gather_out)
             assert torch.equal(spec.lru.order, plain.lru.order)
     assert int(spec.forward.prefetch.staged_rows.sum()) > 0
+
+
+_SHARDED_WORKER = r"""
+import os, sys
+import torch, torch.distributed as dist
+sys.path.insert(0, {root!r})
+from kvip_b200 import ops
+from kvip_b200.sharding import ShardedTopk
+device = torch.device("cuda", 0)
+torch.cuda.set_device(device)
+dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+g = torch.Generator(device=device)
+g.manual_seed(11)
+keys_here, rows = 40960, 2
+scores = torch.randn((rows, keys_here), generator=g, device=device)
+scores[0, ::7] = 0.5                      # ties across the cut
+lengths = torch.full((1,), keys_here, dtype=torch.int32, device=device)
+ends = torch.full((1, rows), keys_here, dtype=torch.int32, device=device)
+expected = ops.topk(scores, lengths, ends)
+sharded = ShardedTopk(rows, device)
+eager = sharded(scores, lengths, ends, 0).clone()
+calls = []
+sharded.capture(lambda: calls.append(1), scores, lengths, ends, 0)
+sharded.merged.fill_(-7)
+replayed = sharded.replay().clone()
+torch.cuda.synchronize()
+assert torch.equal(eager, expected), "eager sharded TopK differs from the unsharded one"
+assert torch.equal(replayed, expected), "captured sharded TopK differs from the unsharded one"
+assert calls, "the score step was not captured"
+dist.destroy_process_group()
+print("ok")
+"""
+
+
+@pytest.mark.gpu
+def test_sharded_topk_eager_and_captured_forms_on_one_rank(tmp_path):
+    """ShardedTopk over NCCL with one rank: local TopK -> all-gather -> merge equals the plain TopK, eagerly and as two
+    graph replays around the eager all-gather. A child process, so that the process group does not outlive the test."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    script = tmp_path / "sharded_worker.py"
+    script.write_text(_SHARDED_WORKER.format(root=str(Path(__file__).resolve().parents[1])))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29641", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
