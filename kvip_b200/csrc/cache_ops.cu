@@ -41,7 +41,8 @@ __device__ __forceinline__ bool descriptor_ok(const KvipFetchArgs& a, int64_t so
 __global__ void __launch_bounds__(256) publish_residency(const KvipFetchArgs a) {
   const uint32_t b = blockIdx.y;
   if (a.row_status[b * 32u] != 0) return;
-  const uint32_t count = static_cast<uint32_t>(a.query_counts[b * 8u + 4]);
+  // the descriptor lists hold kSlots entries per request: a count outside that range is not followed
+  const uint32_t count = static_cast<uint32_t>(min(max(a.query_counts[b * 8u + 4], 0), static_cast<int32_t>(kSlots)));
   const uint32_t owner = a.row_owners ? static_cast<uint32_t>(a.row_owners[b]) : b;
   for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < count; i += gridDim.x * 256u) {
     const int64_t source = a.fetch_sources[static_cast<uint64_t>(b) * kSlots + i];
@@ -63,7 +64,9 @@ __global__ void __launch_bounds__(kFetchThreads) fetch_rows(const KvipFetchArgs 
 #pragma unroll
   for (uint32_t j = 0; j < kPer; ++j) {
     const uint32_t b = tid * kPer + j;
-    mine[j] = b < a.batch && a.row_status[b * 32u] == 0 ? static_cast<uint32_t>(max(a.query_counts[b * 8u + 4], 0)) : 0u;
+    mine[j] = b < a.batch && a.row_status[b * 32u] == 0
+                  ? static_cast<uint32_t>(min(max(a.query_counts[b * 8u + 4], 0), static_cast<int32_t>(kSlots)))   // list capacity
+                  : 0u;
     sum += mine[j];
   }
   uint32_t total;

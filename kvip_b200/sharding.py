@@ -77,8 +77,13 @@ class ShardedTopk:
         """Capture this rank's launches on either side of the exchange into two CUDA graphs: `score_step()` (the
         caller's LI launch into `scores`) with the local TopK before it, the merge after it. Only kernels of this
         library are captured; the all-gather stays an eager NCCL call between the two replays (`replay`). On a step
-        this short the host's launch cost is what the graphs remove."""
+        this short the host's launch cost is what the graphs remove. Call it, and `replay`, under the same non-default
+        stream."""
         from . import ops
+
+        if torch.cuda.current_stream() == torch.cuda.default_stream():
+            raise ValueError("ShardedTopk.capture() must run under a non-default stream (torch.cuda.stream(...)): "
+                             "CUDA graphs cannot be captured on the default stream")
 
         def before():
             score_step()

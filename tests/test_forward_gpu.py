@@ -754,9 +754,16 @@ expected = ops.topk(scores, lengths, ends)
 sharded = ShardedTopk(rows, device)
 eager = sharded(scores, lengths, ends, 0).clone()
 calls = []
-sharded.capture(lambda: calls.append(1), scores, lengths, ends, 0)
-sharded.merged.fill_(-7)
-replayed = sharded.replay().clone()
+try:
+    sharded.capture(lambda: calls.append(1), scores, lengths, ends, 0)
+    raise SystemExit("capture on the default stream must be refused")
+except ValueError:
+    pass
+torch.cuda.synchronize()
+with torch.cuda.stream(torch.cuda.Stream(device)):
+    sharded.capture(lambda: calls.append(1), scores, lengths, ends, 0)
+    sharded.merged.fill_(-7)
+    replayed = sharded.replay().clone()
 torch.cuda.synchronize()
 assert torch.equal(eager, expected), "eager sharded TopK differs from the unsharded one"
 assert torch.equal(replayed, expected), "captured sharded TopK differs from the unsharded one"
