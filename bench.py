@@ -872,7 +872,7 @@ def run_seqshard(args):
     table = torch.arange(keys_here // 128, dtype=torch.int32, device=device).view(1, -1)
     scores = torch.zeros((1, keys_here), dtype=torch.float32, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
-    sharded = ShardedTopk(1, device)
+    sharded = ShardedTopk(1, device, transport=args.transport)
     merged = sharded.merged
     host_merged = torch.empty((1, 2048), dtype=torch.int32).pin_memory()
     host_query = query.view(torch.uint8).cpu().pin_memory()
@@ -886,7 +886,7 @@ def run_seqshard(args):
     def phases(rounds=50):
         """Device time of the four phases of the eager step, from CUDA events between them (mean of `rounds`)."""
         import torch.distributed as dist
-        names = ("shard_li_score", "local_topk", "all_gather", "merge")
+        names = ("shard_li_score", "local_topk", "exchange", "merge")
         total = dict.fromkeys(names, 0.0)
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         for _ in range(rounds):
@@ -895,9 +895,9 @@ def run_seqshard(args):
             marks[1].record(stream)
             ops.topk(scores, lengths, ends, sharded.local_index, out_scores=sharded.local_scores, base_index=begin)
             marks[2].record(stream)
-            dist.all_gather_into_tensor(sharded.gathered, sharded.send)
+            sharded._exchange()
             marks[3].record(stream)
-            ops.topk_merge_gathered(sharded.gathered, sharded.merged)
+            sharded._merge()   # with the peer transport this includes the wait for the other ranks' candidates
             marks[4].record(stream)
             marks[4].synchronize()
             for i, name in enumerate(names):
@@ -932,11 +932,11 @@ def run_seqshard(args):
         step()
         launches = (lib.kvip_b200_launch_count() - before) * args.steps
         stream.synchronize()
-        # One rank: the step is replayed from one CUDA graph. Several ranks: two graphs of this library's kernels
-        # (LI + local TopK, merge) with the NCCL all-gather issued eagerly between them; capturing the all-gather
-        # itself made a two-rank run of this bench stop responding, so it stays outside graphs.
+        # One rank, or the peer-memory exchange: the step is replayed from one CUDA graph. Several ranks over NCCL: two
+        # graphs of this library's kernels (LI + local TopK, merge) with the all-gather issued eagerly between them;
+        # capturing the all-gather itself made a two-rank run of this bench stop responding, so it stays outside graphs.
         graph, replay = None, step
-        if world == 1:
+        if world == 1 or args.transport == "peer":
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
@@ -977,12 +977,17 @@ def run_seqshard(args):
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
             "config": {"workload": args.workload, "context": total, "keys_per_rank": keys_here, "index_heads": heads,
-                       "topk": 2048, "exchange": "one all-gather of 2048 x (f32, i32) per rank, then merge",
+                       "topk": 2048,
+                       "exchange": ("one NCCL all-gather of 2048 x (f32, i32) per rank, then merge" if args.transport == "nccl"
+                                    else "this library's kernel: every rank stores its 2048 x (f32, i32) into every rank's "
+                                         "exchange block over NVLink peer memory; the merge waits for the flags"),
+                       "transport": args.transport,
                        "cuda_graph": True if graph is not None else "kernels on either side of the eager all-gather",
                        "l2": "shard keys %.0f MB per step" % (keys_here * 132 / 1e6)},
             "e2e": {"value": args.steps / e2e_elapsed, "unit": "tokens/s", "h2d_bytes_per_step": host_query.numel(),
                     "d2h_bytes_per_step": host_merged.numel() * 4, "ms_per_step": e2e_elapsed / args.steps * 1e3},
             "gpu_launches": launches, "verified_against_unsharded_topk": failed == 0.0,
+            "peer_status": int(sharded.status.item()),
             "phases_us": dict(phase_us, note="eager launches, CUDA events between the phases, slowest rank of each; the "
                                              "events keep the launches from overlapping, so the sum exceeds the step"),
             "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": None, "peak": peaks()[0],
@@ -990,6 +995,7 @@ def run_seqshard(args):
                          "note": "latency-bound step: about %d key pages per CTA; see ms_per_step" % round(keys_here / 128 / 148)},
             "clocks": clocks,
         }), flush=True)
+    sharded.close()
     dist.destroy_process_group()
 
 
@@ -1148,6 +1154,8 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch",
                                                        "decode_128k_b32_zipf"], default="decode_128k_b64")
+    parser.add_argument("--transport", choices=("peer", "nccl"), default="peer",
+                        help="seqshard_1m: how the ranks exchange their TopK candidates")
     parser.add_argument("--quick", action="store_true",
                         help="warm-up and timed replays only (for profiler captures): no stage timings, no end-to-end leg")
     parser.add_argument("--reuse", type=float, default=0.75,

@@ -57,6 +57,7 @@ extern "C" {
 #define KVIP_ERR_EXCHANGE 16u        /* Index exchange plan invalid (shadow_exchange_parallel.h:40) */
 #define KVIP_ERR_PIPELINE 32u        /* a bounded mbarrier wait inside the LI kernel gave up */
 #define KVIP_ERR_SOURCE 64u          /* a missing row's source address lies outside the host pool (streaming.cpp:399-400) */
+#define KVIP_ERR_PEER 128u           /* a bounded wait for another GPU's candidates gave up (sequence-sharded TopK) */
 
 enum { KVIP_KEY_FP8_E4M3 = 0, KVIP_KEY_BF16 = 1 };
 enum { KVIP_WEIGHT_BF16 = 0, KVIP_WEIGHT_FP32 = 1 };
@@ -164,8 +165,47 @@ typedef struct KvipMergeArgs {
   uint32_t row_stride;        /* elements between two rows of one shard; 0 = shards * 2048. The buffer an all-gather of
                                  per-rank [2, rows, 2048] (scores, indices) blocks fills is read in place with
                                  shard_stride = 2 * rows * 2048 and row_stride = 2048. */
+  /* Candidates delivered by kvip_b200_peer_exchange instead of the three pointers above (all optional, NULL / 0 =
+   * unused): `peer_block` is this rank's exchange block. The kernel reads the block's step counter, waits (bounded) until
+   * the flags of `wait_ranks` ranks have reached it, and merges the candidates of that step's half of the block. A wait
+   * that runs out ORs KVIP_ERR_PEER into *status and the rows come back as -1. */
+  const void* peer_block;
+  int32_t* status;
+  uint32_t wait_ranks;        /* = shards when peer_block is set */
+  uint32_t wait_kilocycles;   /* limit of the wait in units of 1024 SM clock cycles; 0 = about one second */
 } KvipMergeArgs;
 uint32_t kvip_b200_topk_merge(const KvipMergeArgs* args, void* stream);
+
+/* ---- exchange of the per-rank TopK candidates over NVLink peer memory --------------------------
+ * The one exchange step of a sequence-sharded request (every rank's 2048 (score, index) candidates per row to every
+ * rank) written as a kernel of this library instead of an NCCL all-gather: 16 KiB per rank is pure latency, a
+ * collective library's launch and synchronisation cost several times the transfer, and a plain kernel can live in the
+ * same CUDA graph as the score and TopK kernels on either side. One process per GPU; no two ranks may share a GPU
+ * (the merge kernel of one rank waits for the exchange kernel of the others).
+ *
+ * Every rank owns one exchange block (kvip_b200_peer_alloc; cudaMalloc'ed, zeroed, with an IPC handle that the other
+ * ranks open with kvip_b200_peer_open):
+ *   bytes    0..255   step counter (u32) of this rank: the number of exchanges it has made
+ *   bytes  256..511   flags[8] (u32): flags[r] = last step whose candidates rank r has delivered HERE
+ *   bytes  512..      two halves (step parity) x world x block_bytes: the candidate blocks, in rank order
+ * kvip_b200_peer_exchange (one CTA): step s = counter + 1; copies `send` (block_bytes, a multiple of 16) into slot
+ * [s & 1][rank] of every rank's block with plain peer stores, fences system-wide, then writes s into flags[rank] of
+ * every rank and into its own counter. Two halves suffice: a rank starts exchange s + 2 only after its merge of step
+ * s + 1, which has seen every rank's flag s + 1, which every rank wrote after its own merge of step s. */
+#define KVIP_PEER_HEADER_BYTES 512u
+typedef struct KvipPeerExchangeArgs {
+  const void* send;           /* this rank's candidates: [2, rows, 2048] int32 (score bits, indices) */
+  uint64_t peer_block[8];     /* exchange block of every rank as mapped in THIS process (own block at [rank]) */
+  uint32_t block_bytes;       /* bytes of `send` */
+  uint32_t rank, world, reserved0;
+} KvipPeerExchangeArgs;
+uint32_t kvip_b200_peer_exchange(const KvipPeerExchangeArgs* args, void* stream);
+/* Exchange block of `bytes` (>= 512 + 2 * world * block_bytes) on the current device, zeroed; `handle` receives the
+ * 64-byte CUDA IPC handle that other processes pass to kvip_b200_peer_open. */
+uint32_t kvip_b200_peer_alloc(uint64_t bytes, void** block, uint8_t* handle);
+uint32_t kvip_b200_peer_open(const uint8_t* handle, void** block);   /* maps another rank's block (enables peer access) */
+uint32_t kvip_b200_peer_close(void* block);                           /* a mapping made by kvip_b200_peer_open */
+uint32_t kvip_b200_peer_free(void* block);                            /* a block made by kvip_b200_peer_alloc */
 
 /* ---- QueryInputs.pack / bind_positions ---------------------------------------------------
  * Row r of the bound input buffers takes token gather_indices[r] of the caller's tensors; query_ends[r] =

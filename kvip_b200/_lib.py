@@ -14,7 +14,8 @@ OPTION_DIAGNOSTICS, OPTION_DEFERRED_FETCH = 0x80000000, 0x40000000
 OPTION_LEGACY_LAYOUT, OPTION_SCHEDULING_HINTS = 0x20000000, 0x1C000000
 OPTION_SELECT_ONLY, OPTION_COMMIT_ONLY, OPTION_SCORES_READY = 0x02000000, 0x01000000, 0x00800000
 TOPK_SPLIT_WORDS = 20544
-ERR_TOKEN_RANGE, ERR_NO_SLOT, ERR_HASH, ERR_EXCHANGE, ERR_PIPELINE, ERR_SOURCE = 1, 4, 8, 16, 32, 64
+ERR_TOKEN_RANGE, ERR_NO_SLOT, ERR_HASH, ERR_EXCHANGE, ERR_PIPELINE, ERR_SOURCE, ERR_PEER = 1, 4, 8, 16, 32, 64, 128
+PEER_HEADER_BYTES = 512
 # boundaries of KvipWorkspace.times (KVIP_TIME_*)
 TIME_STAGES = ("li_score", "topk", "resolve", "outputs", "exchange", "fetch", "gather")
 BAD_ARGUMENT = 100000
@@ -62,7 +63,15 @@ ColdArgs = _struct("ColdArgs", ("scores", "key_lengths", "query_ends", "prefix_t
                    [(n, u32) for n in ("rows", "queries", "scoreStride", "resident", "bitmap_words", "reserved0")])
 
 MergeArgs = _struct("MergeArgs", ("cand_scores", "cand_index", "topk"),
-                    [("rows", u32), ("shards", u32), ("shard_stride", u32), ("row_stride", u32)])
+                    [("rows", u32), ("shards", u32), ("shard_stride", u32), ("row_stride", u32),
+                     ("peer_block", vp), ("status", vp), ("wait_ranks", u32), ("wait_kilocycles", u32)])
+
+
+class PeerExchangeArgs(ctypes.Structure):
+    """KvipPeerExchangeArgs: this rank's candidates and every rank's exchange block as mapped here."""
+
+    _fields_ = [("send", vp), ("peer_block", u64 * 8), ("block_bytes", u32), ("rank", u32), ("world", u32),
+                ("reserved0", u32)]
 
 ResolveArgs = _struct("ResolveArgs", (
     "topk", "row_owners", "hot_valid", "reserved_hot", "lru_slots", "tail_bounds", "logical_ids", "addresses",
@@ -157,7 +166,7 @@ _STAGES = {
     "kvip_b200_topk_merge": MergeArgs, "kvip_b200_cold_predicate": ColdArgs,
     "kvip_b200_pack_inputs": PackArgs, "kvip_b200_resolve": ResolveArgs, "kvip_b200_fetch": FetchArgs,
     "kvip_b200_gather": GatherArgs, "kvip_b200_publish_residency": FetchArgs, "kvip_b200_exchange": ExchangeArgs, "kvip_b200_ingest": IngestArgs,
-    "kvip_b200_ingest_spans": IngestSpanArgs,
+    "kvip_b200_ingest_spans": IngestSpanArgs, "kvip_b200_peer_exchange": PeerExchangeArgs,
     "kvip_b200_lru_commit": LruArgs, "kvip_b200_lidu": LiduArgs, "kvip_b200_publish_pages": PagesArgs,
     "kvip_b200_window_bounds": WindowArgs, "kvip_b200_resident_threshold": ThresholdArgs,
     "kvip_b200_speculate_window": SpeculateArgs,
@@ -167,7 +176,8 @@ EXPORTS = tuple(_STAGES) + (
     "kvip_b200_update_abc", "kvip_b200_lidu_scratch_words", "kvip_lifetch_streaming_forward", "kvip_prepare_shape",
     "kvip_streaming_resolver_cores", "kvip_streaming_flag_count", "kvip_b200_abi_version",
     "kvip_b200_context_bytes", "kvip_b200_workspace_bytes", "kvip_b200_launch_count", "kvip_b200_last_error",
-    "kvip_b200_host_register", "kvip_b200_host_unregister")
+    "kvip_b200_host_register", "kvip_b200_host_unregister", "kvip_b200_peer_alloc", "kvip_b200_peer_open",
+    "kvip_b200_peer_close", "kvip_b200_peer_free")
 
 _library = None
 
@@ -200,6 +210,11 @@ def load_library(path=None):
     lib.kvip_b200_host_register.argtypes = [vp, u64, ctypes.POINTER(u64)]
     lib.kvip_b200_host_register.restype = u32
     lib.kvip_b200_host_unregister.argtypes, lib.kvip_b200_host_unregister.restype = [vp], u32
+    lib.kvip_b200_peer_alloc.argtypes = [u64, ctypes.POINTER(vp), ctypes.c_char_p]
+    lib.kvip_b200_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    lib.kvip_b200_peer_close.argtypes = lib.kvip_b200_peer_free.argtypes = [vp]
+    for name in ("kvip_b200_peer_alloc", "kvip_b200_peer_open", "kvip_b200_peer_close", "kvip_b200_peer_free"):
+        getattr(lib, name).restype = u32
     if path is None:
         _library = lib
     return lib

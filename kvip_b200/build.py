@@ -11,7 +11,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libkvip_b200.so"
-SOURCES = ("api.cu", "li_score.cu", "topk.cu", "topk_pivot.cu", "topk_split.cu", "cold_predicate.cu", "resolve.cu", "exchange.cu", "cache_ops.cu", "lidu.cu", "speculate.cu")
+SOURCES = ("api.cu", "li_score.cu", "topk.cu", "topk_pivot.cu", "topk_split.cu", "cold_predicate.cu", "resolve.cu", "exchange.cu", "cache_ops.cu", "lidu.cu", "speculate.cu", "peer_exchange.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",

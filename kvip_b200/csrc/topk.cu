@@ -174,6 +174,40 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
   __shared__ uint32_t scan_scratch[33];
   __shared__ uint32_t found[3];
   const uint32_t row = blockIdx.x, tid = threadIdx.x, n = a.shards * kTop;
+  const float* cand_scores = a.cand_scores;
+  const int32_t* cand_index = a.cand_index;
+  if (a.peer_block) {
+    // Candidates delivered by peer_exchange: wait until every rank's flag in this rank's exchange block has reached the
+    // block's step counter (this rank's own exchange kernel, earlier on this stream, set the counter and its own flag;
+    // the other flags are written from other GPUs). The wait is bounded; when it runs out the rows come back as -1.
+    __shared__ uint32_t gave_up;
+    const uint8_t* block = static_cast<const uint8_t*>(a.peer_block);
+    const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(block);
+    if (tid == 0) gave_up = 0;
+    __syncthreads();
+    if (tid < a.wait_ranks) {
+      const volatile uint32_t* flag = reinterpret_cast<const volatile uint32_t*>(block + 256) + tid;
+      const long long limit = static_cast<long long>(a.wait_kilocycles ? a.wait_kilocycles : 2000000u) << 10;
+      const long long start = clock64();
+      // flags only grow, and a later step overwrites the other half of the block: "reached" is >=, compared as a
+      // signed difference so that the counter may wrap
+      while (static_cast<int32_t>(*flag - step) < 0) {
+        if (clock64() - start > limit) { gave_up = 1u; break; }
+      }
+    }
+    __threadfence_system();   // the candidates behind a flag are read after the flag
+    __syncthreads();
+    if (gave_up) {
+      if (tid == 0 && a.status) atomicOr(a.status, static_cast<int32_t>(KVIP_ERR_PEER));
+      for (uint32_t i = tid; i < kTop; i += kThreads) a.topk[static_cast<uint64_t>(row) * kTop + i] = -1;
+      return;   // block-uniform
+    }
+    const uint64_t block_bytes = static_cast<uint64_t>(a.rows) * 2u * kTop * 4u;
+    const int32_t* half = reinterpret_cast<const int32_t*>(block + KVIP_PEER_HEADER_BYTES +
+                                                           static_cast<uint64_t>(step & 1u) * a.shards * block_bytes);
+    cand_scores = reinterpret_cast<const float*>(half);
+    cand_index = half + static_cast<uint64_t>(a.rows) * kTop;
+  }
   uint32_t* keys = merge_smem;
   int32_t* index = reinterpret_cast<int32_t*>(merge_smem + n);
   uint32_t* winners = merge_smem + 2u * n;
@@ -182,9 +216,9 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
   uint32_t mine = 0;
   for (uint32_t i = tid; i < n; i += kThreads) {
     const uint64_t at = row_offset + (i / kTop) * shard_stride + (i % kTop);
-    const int32_t candidate = a.cand_index[at];
+    const int32_t candidate = __ldcg(cand_index + at);   // L2 loads: the lists may have been written by another GPU
     index[i] = candidate;
-    keys[i] = candidate >= 0 ? sortable_key(a.cand_scores[at]) : 0u;
+    keys[i] = candidate >= 0 ? sortable_key(__ldcg(cand_scores + at)) : 0u;
     mine += candidate >= 0 ? 1u : 0u;
   }
   uint32_t valid;
@@ -310,7 +344,9 @@ extern "C" uint32_t kvip_b200_topk_static(const KvipTopkArgs* a, void* stream) {
 }
 
 extern "C" uint32_t kvip_b200_topk_merge(const KvipMergeArgs* a, void* stream) {
-  KVIP_REQUIRE(a && a->cand_scores && a->cand_index && a->topk, "topk_merge: null pointer");
+  KVIP_REQUIRE(a && a->topk && ((a->cand_scores && a->cand_index) || a->peer_block), "topk_merge: null pointer");
+  KVIP_REQUIRE(!a->peer_block || (a->wait_ranks == a->shards && (reinterpret_cast<uintptr_t>(a->peer_block) & 255) == 0),
+               "topk_merge: a peer exchange block is waited for by all of its ranks");
   KVIP_REQUIRE(a->rows >= 1 && a->shards >= 1 && a->shards <= 8, "topk_merge: 1..8 shards");
   const size_t smem = (2u * a->shards + 1u) * KVIP_TOPK * sizeof(uint32_t);   // keys, indices, winners
   if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotTopkMerge, reinterpret_cast<const void*>(kvip::topk_merge),

@@ -152,6 +152,30 @@ def topk_merge_gathered(gathered, out=None):
     return out
 
 
+def peer_exchange(send, peer_blocks, rank):
+    """Deliver this rank's candidate block (`send`, int32 [2, rows, 2048]) into every rank's exchange block over peer
+    memory and raise this rank's flag there. `peer_blocks`: device addresses of all ranks' blocks as mapped in this
+    process (kvip_b200.sharding.PeerBlocks)."""
+    device = send.device
+    _require(send, "send", torch.int32, device)
+    args = _lib.PeerExchangeArgs(send=_ptr(send), block_bytes=send.numel() * 4, rank=rank, world=len(peer_blocks))
+    for r, address in enumerate(peer_blocks):
+        args.peer_block[r] = address
+    _lib.check(_lib.load_library().kvip_b200_peer_exchange(ctypes.byref(args), _stream(device)), "peer_exchange")
+
+
+def topk_merge_peer(own_block, rows, world, out, status, wait_kilocycles=0):
+    """Global top-2048 of the candidates the ranks delivered into this rank's exchange block (device address
+    `own_block`) with `peer_exchange`; waits, bounded, for every rank's flag of the current step."""
+    device = out.device
+    _require(out, "out", torch.int32, device)
+    _require(status, "status", torch.int32, device)
+    args = _lib.MergeArgs(topk=_ptr(out), rows=rows, shards=world, shard_stride=2 * rows * TOPK, row_stride=TOPK,
+                          peer_block=own_block, status=_ptr(status), wait_ranks=world, wait_kilocycles=wait_kilocycles)
+    _lib.check(_lib.load_library().kvip_b200_topk_merge(ctypes.byref(args), _stream(device)), "topk_merge")
+    return out
+
+
 class ResolveState:
     """Per-launch resolver scratch and outputs (shapes of operators/lifetch/workspace.py:9-32)."""
 

@@ -49,36 +49,119 @@ def gather_candidates(local_scores, local_index, group=None):
     return scores, index
 
 
-class ShardedTopk:
-    """Preallocated buffers of the sequence-sharded TopK of `rows` score rows: the local TopK writes its scores and
-    global indices straight into this rank's send block, ONE all-gather fills [world, 2, rows, 2048], and the merge
-    kernel reads that buffer in place. Per step: local TopK, all-gather, merge - three launches, no repacking."""
+class PeerBlocks:
+    """Exchange blocks for `kvip_b200_peer_exchange`: one per rank, allocated by the library on this rank's GPU and
+    mapped into every other rank's process through CUDA IPC handles (exchanged once over `torch.distributed`).
+    `addresses[r]` is rank r's block as seen from this process. One process per GPU: two ranks on one GPU would have
+    one rank's merge kernel wait for another's exchange kernel on the same device, which nothing guarantees to run."""
 
     def __init__(self, rows, device, group=None):
+        import ctypes
+
         import torch.distributed as dist
 
-        self.group, self.world = group, dist.get_world_size(group)
+        from . import _lib
+        self.lib = _lib.load_library()
+        self.group, self.rank, self.world = group, dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("the candidate exchange block has flags for at most 8 ranks")
+        self.block_bytes = 2 * rows * TOPK * 4
+        self.bytes = _lib.PEER_HEADER_BYTES + 2 * self.world * self.block_bytes
+        with torch.cuda.device(device):
+            own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            _lib.check(self.lib.kvip_b200_peer_alloc(self.bytes, ctypes.byref(own), handle), "peer_alloc")
+            self.own = own.value
+            identity = str(torch.cuda.get_device_properties(device).uuid)
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, (handle.raw, identity), group=group)
+            if len({uuid for _, uuid in everyone}) != self.world:
+                self.lib.kvip_b200_peer_free(self.own)
+                raise ValueError("the peer exchange needs one GPU per rank")
+            self.addresses, self._opened = [], []
+            for r, (raw, _) in enumerate(everyone):
+                if r == self.rank:
+                    self.addresses.append(self.own)
+                    continue
+                mapped = ctypes.c_void_p()
+                _lib.check(self.lib.kvip_b200_peer_open(raw, ctypes.byref(mapped)), "peer_open")
+                self.addresses.append(mapped.value)
+                self._opened.append(mapped.value)
+        dist.barrier(group=group)   # every block is mapped everywhere before the first exchange
+
+    def close(self):
+        import torch.distributed as dist
+
+        if self.own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)   # nobody is still writing into a block that is about to go
+        for mapped in self._opened:
+            self.lib.kvip_b200_peer_close(mapped)
+        dist.barrier(group=self.group)
+        self.lib.kvip_b200_peer_free(self.own)
+        self.own, self._opened = None, []
+
+
+class ShardedTopk:
+    """Preallocated buffers of the sequence-sharded TopK of `rows` score rows: the local TopK writes its scores and
+    global indices straight into this rank's send block, one exchange delivers every rank's block to every rank, and
+    the merge kernel reads the delivered blocks in place. Per step: local TopK, exchange, merge - no repacking.
+
+    `transport="nccl"`: the exchange is ONE `all_gather_into_tensor` (eager; the kernels on either side of it may be
+    captured, `capture` / `replay`). `transport="peer"`: the exchange is this library's kernel over NVLink peer memory
+    (`PeerBlocks`): no collective call, the merge waits (bounded) for the other ranks' flags, and the whole step -
+    score, local TopK, exchange, merge - captures into ONE graph per rank."""
+
+    def __init__(self, rows, device, group=None, transport="nccl"):
+        import torch.distributed as dist
+
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
+        self.group, self.world, self.rows, self.transport = group, dist.get_world_size(group), rows, transport
         self.send = torch.zeros((2, rows, TOPK), dtype=torch.int32, device=device)
-        self.gathered = torch.zeros((self.world, 2, rows, TOPK), dtype=torch.int32, device=device)
         self.merged = torch.empty((rows, TOPK), dtype=torch.int32, device=device)
         self.local_scores, self.local_index = self.send[0].view(torch.float32), self.send[1]
-
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)   # KVIP_ERR_PEER: a wait for a rank ran out
         self._before = self._after = None
+        self.peers = self.gathered = None
+        if transport == "peer":
+            self.peers = PeerBlocks(rows, device, group)
+        else:
+            self.gathered = torch.zeros((self.world, 2, rows, TOPK), dtype=torch.int32, device=device)
 
-    def __call__(self, scores, lengths, ends, base_index):
+    def close(self):
+        """Unmap and free the exchange blocks (peer transport); collective: every rank calls it."""
+        if self.peers is not None:
+            self.peers.close()
+            self.peers = None
+
+    def _merge(self, wait_kilocycles=0):
+        from . import ops
+        if self.peers is not None:
+            return ops.topk_merge_peer(self.peers.own, self.rows, self.world, self.merged, self.status, wait_kilocycles)
+        return ops.topk_merge_gathered(self.gathered, self.merged)
+
+    def _exchange(self):
         import torch.distributed as dist
 
         from . import ops
+        if self.peers is not None:
+            ops.peer_exchange(self.send, self.peers.addresses, self.peers.rank)
+        else:
+            dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
+
+    def __call__(self, scores, lengths, ends, base_index, wait_kilocycles=0):
+        from . import ops
         ops.topk(scores, lengths, ends, self.local_index, out_scores=self.local_scores, base_index=base_index)
-        dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
-        return ops.topk_merge_gathered(self.gathered, self.merged)
+        self._exchange()
+        return self._merge(wait_kilocycles)
 
     def capture(self, score_step, scores, lengths, ends, base_index, warmup=3):
-        """Capture this rank's launches on either side of the exchange into two CUDA graphs: `score_step()` (the
-        caller's LI launch into `scores`) with the local TopK before it, the merge after it. Only kernels of this
-        library are captured; the all-gather stays an eager NCCL call between the two replays (`replay`). On a step
-        this short the host's launch cost is what the graphs remove. Call it, and `replay`, under the same non-default
-        stream."""
+        """Capture the step into CUDA graphs: `score_step()` (the caller's LI launch into `scores`) with the local TopK,
+        then the exchange and the merge. With the peer transport everything is one graph. With NCCL only kernels of
+        this library are captured, in two graphs, and the all-gather stays an eager call between the two replays
+        (`replay`): on a step this short the host's launch cost is what the graphs remove. Call it, and `replay`, under
+        the same non-default stream. The warm-up steps exchange candidates, so every rank must make the same calls."""
         from . import ops
 
         if torch.cuda.current_stream() == torch.cuda.default_stream():
@@ -89,28 +172,31 @@ class ShardedTopk:
             score_step()
             ops.topk(scores, lengths, ends, self.local_index, out_scores=self.local_scores, base_index=base_index)
 
-        def after():
-            ops.topk_merge_gathered(self.gathered, self.merged)
-
         for _ in range(max(warmup, 1)):
             before()
-            after()
+            self._exchange()
+            self._merge()
         torch.cuda.current_stream().synchronize()
-        self._before, self._after = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        self._before, self._after = torch.cuda.CUDAGraph(), None
         with torch.cuda.graph(self._before, stream=torch.cuda.current_stream()):
             before()
-        with torch.cuda.graph(self._after, stream=torch.cuda.current_stream()):
-            after()
+            if self.peers is not None:
+                self._exchange()
+                self._merge()
+        if self.peers is None:
+            self._after = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._after, stream=torch.cuda.current_stream()):
+                self._merge()
 
     def replay(self):
-        """One step of the captured form: graph (LI + local TopK), eager all-gather, graph (merge)."""
-        import torch.distributed as dist
-
+        """One step of the captured form: one graph (peer transport), or graph (LI + local TopK), eager all-gather,
+        graph (merge)."""
         if self._before is None:
             raise RuntimeError("ShardedTopk.replay() before capture()")
         self._before.replay()
-        dist.all_gather_into_tensor(self.gathered, self.send, group=self.group)
-        self._after.replay()
+        if self._after is not None:
+            self._exchange()
+            self._after.replay()
         return self.merged
 
 

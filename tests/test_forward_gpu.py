@@ -768,8 +768,73 @@ torch.cuda.synchronize()
 assert torch.equal(eager, expected), "eager sharded TopK differs from the unsharded one"
 assert torch.equal(replayed, expected), "captured sharded TopK differs from the unsharded one"
 assert calls, "the score step was not captured"
+# the same over this library's peer-memory exchange (one rank: the block is its own), eagerly and as ONE graph
+peer = ShardedTopk(rows, device, transport="peer")
+assert torch.equal(peer(scores, lengths, ends, 0), expected), "peer transport, eager"
+with torch.cuda.stream(torch.cuda.Stream(device)):
+    peer.capture(lambda: None, scores, lengths, ends, 0)
+    for _ in range(3):                      # odd and even steps: both halves of the block
+        peer.merged.fill_(-7)
+        assert torch.equal(peer.replay(), expected), "peer transport, graph replay"
+torch.cuda.synchronize()
+assert int(peer.status.item()) == 0
+# bounded wait: a block that claims two ranks, of which only rank 0 ever delivers
+import ctypes
+from kvip_b200 import _lib
+lib = _lib.load_library()
+block, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+_lib.check(lib.kvip_b200_peer_alloc(_lib.PEER_HEADER_BYTES + 2 * 2 * peer.send.numel() * 4, ctypes.byref(block), handle), "alloc")
+ops.peer_exchange(peer.send, [block.value, block.value], 0)
+out = torch.zeros((rows, 2048), dtype=torch.int32, device=device)
+status = torch.zeros(1, dtype=torch.int32, device=device)
+ops.topk_merge_peer(block.value, rows, 2, out, status, wait_kilocycles=2000)    # about a millisecond
+torch.cuda.synchronize()
+assert int(status.item()) == _lib.ERR_PEER and bool((out == -1).all()), "the wait for the absent rank must give up"
+assert torch.equal(peer(scores, lengths, ends, 0), expected), "the context stays usable after a wait ran out"
+_lib.check(lib.kvip_b200_peer_free(block), "free")
+peer.close()
 dist.destroy_process_group()
 print("ok")
+"""
+
+
+_TWO_RANK_WORKER = r"""
+import os, sys
+import torch, torch.distributed as dist
+sys.path.insert(0, {root!r})
+from kvip_b200 import ops
+from kvip_b200.sharding import ShardedTopk, shard_bounds
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+device = torch.device("cuda", rank)
+torch.cuda.set_device(device)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+total, rows = 5 * 16384, 2
+g = torch.Generator(device=device)
+g.manual_seed(5)                                   # the same whole row on every rank
+whole = torch.randn((rows, total), generator=g, device=device)
+whole[0, ::5] = 0.25                               # ties across the shard border and the cut
+begin, end = shard_bounds(total, world, rank)
+scores = whole[:, begin:end].contiguous()
+lengths = torch.full((1,), end - begin, dtype=torch.int32, device=device)
+ends = torch.full((1, rows), end - begin, dtype=torch.int32, device=device)
+whole_len = torch.full((1,), total, dtype=torch.int32, device=device)
+expected = ops.topk(whole, whole_len, torch.full((1, rows), total, dtype=torch.int32, device=device))
+over_nccl = ShardedTopk(rows, device)(scores, lengths, ends, begin).clone()
+peer = ShardedTopk(rows, device, transport="peer")
+eager = peer(scores, lengths, ends, begin).clone()
+with torch.cuda.stream(torch.cuda.Stream(device)):
+    peer.capture(lambda: None, scores, lengths, ends, begin)
+    for _ in range(4):
+        peer.merged.fill_(-7)
+        replayed = peer.replay().clone()
+        assert torch.equal(replayed, expected), "peer transport, graph replay"
+torch.cuda.synchronize()
+assert torch.equal(over_nccl, expected) and torch.equal(eager, expected)
+assert int(peer.status.item()) == 0
+peer.close()
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
 """
 
 
@@ -786,3 +851,24 @@ def test_sharded_topk_eager_and_captured_forms_on_one_rank(tmp_path):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29641", NCCL_NVLS_ENABLE="0")
     out = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
+
+
+@pytest.mark.gpu
+def test_sharded_topk_over_peer_memory_on_two_gpus(tmp_path):
+    """Two ranks on two GPUs: local TopK -> candidates written into the other rank's exchange block over NVLink ->
+    merge behind a bounded wait equals the unsharded TopK and the NCCL transport, eagerly and from one graph per rank.
+    Child processes; NVLS off (plain peer stores only)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "two_rank_worker.py"
+    script.write_text(_TWO_RANK_WORKER.format(root=str(Path(__file__).resolve().parents[1])))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29643", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    for proc in procs:
+        out, _ = proc.communicate(timeout=300)
+        assert proc.returncode == 0, out
