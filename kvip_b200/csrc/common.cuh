@@ -20,7 +20,7 @@ void set_error(const char* message);
 // Per-device host bookkeeping. A function attribute (the dynamic shared-memory limit of a kernel) and the SM
 // count belong to ONE device: a process that drives several GPUs configures every kernel once per device.
 enum KernelSlot : uint32_t {
-  kSlotLiFp8, kSlotLiBf16, kSlotTopkSelect, kSlotTopkMerge, kSlotTopkPivot, kSlotSplitEmit, kSlotSplitFallback,
+  kSlotLiFp8, kSlotLiBf16, kSlotTopkSelect, kSlotTopkMerge, kSlotTopkMergeCluster, kSlotTopkPivot, kSlotSplitEmit, kSlotSplitFallback,
   kSlotResolve, kSlotLidu, kSlotCount
 };
 // Raises the dynamic shared-memory limit of `kernel` on the current device the first time it is asked to there.

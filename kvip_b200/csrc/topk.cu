@@ -14,6 +14,7 @@
 // u32 image of the float) find v exactly; a fourth, ordered pass compacts the winners with
 // block-wide prefix sums (no atomics, so the order is the position order). The row is read
 // from L2 (the LI kernel has just written it) with 16-byte loads.
+#include <cooperative_groups.h>
 #include "common.cuh"
 #include "topk_core.cuh"
 
@@ -267,6 +268,206 @@ __global__ void __launch_bounds__(kThreads) topk_merge(const KvipMergeArgs a) {
     out[i] = winners[i] == 0xffffffffu ? -1 : static_cast<int32_t>(winners[i] & 0x7fffffffu);
 }
 
+// ---- merge of shard candidates on a cluster: one CTA per shard --------------------------------------------------
+// The single-CTA merge above walks shards x 2048 candidates with 1024 threads (16 rounds per radix pass at eight
+// shards) and measured 66 us there, more than the score pass and the local TopK of the same step together. Here a
+// cluster of `shards` CTAs shares the work: CTA c owns shard c's 2048 candidates, two per thread, in registers. The
+// hub (cluster rank 0) owns the histograms, the digit found per pass and the winners' list; the others reach them
+// through distributed shared memory. Per radix pass: every CTA histograms its candidates locally and adds its
+// non-empty bins to the hub's histogram, cluster barrier, the hub scans, cluster barrier, everyone reads the digit.
+// Same result as topk_merge, bit for bit (same cut, same tie rule, same canonical order).
+struct MergeHub {
+  uint32_t hist[2][4096];   // double-buffered: the hub clears the next pass's copy while it scans this one's
+  uint32_t winners[kTop];
+  uint32_t valid[8], won[8], bad[8];
+  uint32_t found[3];        // digit, how many of the wanted still lie in that bin, entries in that bin
+};
+
+namespace cg = cooperative_groups;
+
+__global__ void __launch_bounds__(kThreads, 1) topk_merge_cluster(const KvipMergeArgs a) {
+  extern __shared__ __align__(16) uint8_t hub_raw[];   // one MergeHub; used on rank 0 only (same image in every CTA)
+  MergeHub& hub_here = *reinterpret_cast<MergeHub*>(hub_raw);
+  __shared__ uint32_t local_hist[4096];
+  __shared__ uint32_t scan_scratch[33];
+  __shared__ uint32_t shared_word[4];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t shards = a.shards, shard = cluster.block_rank(), row = blockIdx.x / shards, tid = threadIdx.x;
+  MergeHub* hub = cluster.map_shared_rank(&hub_here, 0);
+
+  const float* cand_scores = a.cand_scores;
+  const int32_t* cand_index = a.cand_index;
+  uint32_t gave_up = 0;
+  if (a.peer_block) {   // CTA c waits for rank c's flag only
+    const uint8_t* block = static_cast<const uint8_t*>(a.peer_block);
+    const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(block);
+    if (tid == 0) {
+      const volatile uint32_t* flag = reinterpret_cast<const volatile uint32_t*>(block + 256) + shard;
+      const long long limit = static_cast<long long>(a.wait_kilocycles ? a.wait_kilocycles : 2000000u) << 10;
+      const long long start = clock64();
+      uint32_t failed = 0;
+      while (static_cast<int32_t>(*flag - step) < 0) {
+        if (clock64() - start > limit) { failed = 1u; break; }
+      }
+      shared_word[0] = failed;
+    }
+    __threadfence_system();
+    __syncthreads();
+    gave_up = shared_word[0];
+    const uint64_t block_bytes = static_cast<uint64_t>(a.rows) * 2u * kTop * 4u;
+    const int32_t* half = reinterpret_cast<const int32_t*>(block + KVIP_PEER_HEADER_BYTES +
+                                                           static_cast<uint64_t>(step & 1u) * shards * block_bytes);
+    cand_scores = reinterpret_cast<const float*>(half);
+    cand_index = half + static_cast<uint64_t>(a.rows) * kTop;
+  }
+  // two consecutive candidates per thread: a thread's pair, and the threads in order, keep the input order
+  const uint64_t shard_stride = a.shard_stride ? a.shard_stride : kTop;
+  const uint64_t at = static_cast<uint64_t>(row) * (a.row_stride ? a.row_stride : shards * kTop) + shard * shard_stride + 2u * tid;
+  int32_t index[2] = {-1, -1};
+  uint32_t key[2] = {0u, 0u};
+  if (!gave_up) {
+    const int2 two_index = __ldcg(reinterpret_cast<const int2*>(cand_index + at));       // L2 loads: another GPU may
+    const float2 two_score = __ldcg(reinterpret_cast<const float2*>(cand_scores + at));  // have written the lists
+    index[0] = two_index.x; index[1] = two_index.y;
+    key[0] = index[0] >= 0 ? sortable_key(two_score.x) : 0u;
+    key[1] = index[1] >= 0 ? sortable_key(two_score.y) : 0u;
+  }
+  uint32_t valid_here;
+  const uint32_t valid_before = block_exclusive_scan((index[0] >= 0 ? 1u : 0u) + (index[1] >= 0 ? 1u : 0u), scan_scratch, &valid_here);
+  if (shard == 0)
+    for (uint32_t i = tid; i < 2u * 4096u; i += kThreads) hub_here.hist[0][i] = 0;
+  if (tid == 0) { hub->valid[shard] = valid_here; hub->bad[shard] = gave_up; }
+  cluster.sync();
+  // every CTA learns all counts (and whether any wait ran out): thread r reads entry r of the hub
+  if (tid < shards) { local_hist[tid] = hub->valid[tid]; local_hist[8 + tid] = hub->bad[tid]; }
+  __syncthreads();
+  uint32_t total_valid = 0, before_me = 0, any_bad = 0;
+  for (uint32_t r = 0; r < shards; ++r) {
+    if (r < shard) before_me += local_hist[r];
+    total_valid += local_hist[r];
+    any_bad |= local_hist[8 + r];
+  }
+  __syncthreads();   // local_hist is reused below
+  int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
+  // A CTA that leaves here must not do so while another one may still be reading the hub's counts: one more cluster
+  // barrier on the two early ways out (both are cluster-uniform decisions).
+  if (any_bad) {
+    cluster.sync();
+    if (shard == 0) {
+      if (tid == 0 && a.status) atomicOr(a.status, static_cast<int32_t>(KVIP_ERR_PEER));
+      for (uint32_t i = tid; i < kTop; i += kThreads) out[i] = -1;
+    }
+    return;
+  }
+  if (total_valid <= kTop) {   // nothing is cut, the input order is the canonical one
+    cluster.sync();
+    uint32_t w = before_me + valid_before;
+    if (index[0] >= 0) out[w++] = index[0];
+    if (index[1] >= 0) out[w++] = index[1];
+    if (shard == 0)
+      for (uint32_t i = total_valid + tid; i < kTop; i += kThreads) out[i] = -1;
+    return;
+  }
+
+  // cluster-wide "want-th largest" of value(j) over the members, j = 0, 1 the thread's two candidates
+  uint32_t select_calls = 0;
+  auto kth_largest_cluster = [&](uint32_t want, const uint32_t (&value)[2], const bool (&member)[2], uint32_t* take,
+                                 uint32_t* equal) -> uint32_t {
+    uint32_t prefix = 0, prefix_mask = 0, remaining = want;
+#pragma unroll 1
+    for (uint32_t pass = 0; pass < 3; ++pass) {
+      const uint32_t bits = pass == 2 ? 8u : 12u;
+      const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
+      const uint32_t bins = 1u << bits;
+      const uint32_t buffer = (select_calls * 3u + pass) & 1u;   // the hub's histogram of this pass (cleared already)
+      for (uint32_t i = tid; i < bins; i += kThreads) local_hist[i] = 0;
+      __syncthreads();
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j)
+        hist_add_matched(local_hist, member[j] && (value[j] & prefix_mask) == prefix, (value[j] >> shift) & (bins - 1u));
+      __syncthreads();
+      for (uint32_t i = tid; i < bins; i += kThreads) {
+        const uint32_t count = local_hist[i];
+        if (count) atomicAdd(&hub->hist[buffer][i], count);
+      }
+      cluster.sync();
+      if (shard == 0) {
+        uint32_t* hist = hub_here.hist[buffer];
+        uint32_t* next = hub_here.hist[buffer ^ 1u];
+        for (uint32_t i = tid; i < 4096u; i += kThreads) next[i] = 0;   // nobody adds to it before the next barrier
+        const uint32_t per = bins / kThreads ? bins / kThreads : 1u;
+        const uint32_t groups = bins / per;
+        const uint32_t group = groups - 1u - tid;   // valid when tid < groups: the highest bins first
+        uint32_t local = 0;
+        if (tid < groups)
+          for (uint32_t j = 0; j < per; ++j) local += hist[group * per + j];
+        if (tid == 0) { hub_here.found[0] = 0; hub_here.found[1] = 0; hub_here.found[2] = 0; }
+        uint32_t above = block_exclusive_scan(local, scan_scratch, nullptr);   // also orders the reset before the writes
+        if (tid < groups) {
+          for (int32_t j = static_cast<int32_t>(per) - 1; j >= 0; --j) {
+            const uint32_t count = hist[group * per + static_cast<uint32_t>(j)];
+            if (above < remaining && above + count >= remaining) {
+              hub_here.found[0] = group * per + static_cast<uint32_t>(j);
+              hub_here.found[1] = remaining - above;
+              hub_here.found[2] = count;
+            }
+            above += count;
+          }
+        }
+      }
+      cluster.sync();
+      if (tid < 3) shared_word[tid] = hub->found[tid];
+      __syncthreads();
+      prefix |= shared_word[0] << shift;
+      prefix_mask |= (bins - 1u) << shift;
+      remaining = shared_word[1];
+      *equal = shared_word[2];
+      __syncthreads();
+    }
+    ++select_calls;
+    *take = remaining;
+    return prefix;
+  };
+
+  const bool is_valid[2] = {index[0] >= 0, index[1] >= 0};
+  uint32_t ties_taken = 0, tied = 0, tie_index_limit = 0xffffffffu;
+  const uint32_t cut_key = kth_largest_cluster(kTop, key, is_valid, &ties_taken, &tied);
+  if (ties_taken < tied) {   // cluster-uniform: some candidates tied at the cut are left out: the lower indices win
+    const uint32_t inverted_index[2] = {~static_cast<uint32_t>(index[0]), ~static_cast<uint32_t>(index[1])};
+    const bool is_tied[2] = {is_valid[0] && key[0] == cut_key, is_valid[1] && key[1] == cut_key};
+    uint32_t unused, unused_too;
+    tie_index_limit = ~kth_largest_cluster(ties_taken, inverted_index, is_tied, &unused, &unused_too);
+  }
+  // winners, compacted in input order into the hub's list as (is a tie, index); the hub sorts and writes them
+  bool wins[2], tie[2];
+#pragma unroll
+  for (uint32_t j = 0; j < 2; ++j) {
+    tie[j] = is_valid[j] && key[j] == cut_key;
+    wins[j] = is_valid[j] && (key[j] > cut_key || (tie[j] && static_cast<uint32_t>(index[j]) <= tie_index_limit));
+  }
+  uint32_t won_here;
+  const uint32_t won_before = block_exclusive_scan((wins[0] ? 1u : 0u) + (wins[1] ? 1u : 0u), scan_scratch, &won_here);
+  if (tid == 0) hub->won[shard] = won_here;
+  if (shard == 0)
+    for (uint32_t i = tid; i < kTop; i += kThreads) hub_here.winners[i] = 0xffffffffu;
+  cluster.sync();
+  if (tid < shards) local_hist[tid] = hub->won[tid];
+  __syncthreads();
+  uint32_t w = won_before;
+  for (uint32_t r = 0; r < shard; ++r) w += local_hist[r];
+#pragma unroll
+  for (uint32_t j = 0; j < 2; ++j)
+    if (wins[j]) {
+      if (w < kTop) hub->winners[w] = (tie[j] ? 0x80000000u : 0u) | static_cast<uint32_t>(index[j]);
+      ++w;
+    }
+  cluster.sync();
+  if (shard != 0) return;
+  bitonic_sort_2048(hub_here.winners);
+  for (uint32_t i = tid; i < kTop; i += kThreads)
+    out[i] = hub_here.winners[i] == 0xffffffffu ? -1 : static_cast<int32_t>(hub_here.winners[i] & 0x7fffffffu);
+}
+
 }  // namespace
 
 uint32_t launch_topk_split(const KvipTopkArgs& a, cudaStream_t stream);
@@ -348,11 +549,35 @@ extern "C" uint32_t kvip_b200_topk_merge(const KvipMergeArgs* a, void* stream) {
   KVIP_REQUIRE(!a->peer_block || (a->wait_ranks == a->shards && (reinterpret_cast<uintptr_t>(a->peer_block) & 255) == 0),
                "topk_merge: a peer exchange block is waited for by all of its ranks");
   KVIP_REQUIRE(a->rows >= 1 && a->shards >= 1 && a->shards <= 8, "topk_merge: 1..8 shards");
+  cudaStream_t where = static_cast<cudaStream_t>(stream);
+  const bool lists_aligned = a->peer_block || (((reinterpret_cast<uintptr_t>(a->cand_scores) | reinterpret_cast<uintptr_t>(a->cand_index)) & 7) == 0 &&
+                                               a->shard_stride % 2 == 0 && a->row_stride % 2 == 0);
+  if ((a->shards == 2 || a->shards == 4 || a->shards == 8) && lists_aligned) {
+    // one CTA per shard on a cluster (needs `shards` free SMs of one GPC per row: rows beyond the first wave queue)
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(a->rows * a->shards, 1, 1);
+    config.blockDim = dim3(kvip::kThreads, 1, 1);
+    config.dynamicSmemBytes = sizeof(kvip::MergeHub);
+    config.stream = where;
+    if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotTopkMergeCluster, reinterpret_cast<const void*>(kvip::topk_merge_cluster),
+                                                static_cast<int>(sizeof(kvip::MergeHub)), "topk_merge_cluster attribute"))
+      return bad;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = a->shards;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    if (cudaLaunchKernelEx(&config, kvip::topk_merge_cluster, *a) != cudaSuccess) return kvip::check_launch("topk_merge_cluster");
+    kvip::count_launch();
+    return kvip::check_launch("topk_merge_cluster");
+  }
   const size_t smem = (2u * a->shards + 1u) * KVIP_TOPK * sizeof(uint32_t);   // keys, indices, winners
   if (uint32_t bad = kvip::raise_dynamic_smem(kvip::kSlotTopkMerge, reinterpret_cast<const void*>(kvip::topk_merge),
                                               (2 * 8 + 1) * 2048 * 4, "topk_merge attribute"))
     return bad;
-  kvip::topk_merge<<<a->rows, kvip::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
+  kvip::topk_merge<<<a->rows, kvip::kThreads, smem, where>>>(*a);
   kvip::count_launch();
   return kvip::check_launch("topk_merge");
 }

@@ -322,7 +322,7 @@ def test_topk_merge_equals_unsharded(device):
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy(), expected)
     # fewer shards (other candidate counts, odd ones included): the leading shards against the TopK of their keys
-    for fewer in (2, 3, 5):
+    for fewer in (2, 3, 4, 5):     # 2, 4 and 8 shards merge on a cluster of CTAs, the others on one CTA
         keys_here = fewer * per
         part = np.ascontiguousarray(whole[:, :keys_here])
         expected_part = oracle_c.topk(part, np.full(2, keys_here, np.int32), np.full(2, keys_here, np.int32))
@@ -345,6 +345,13 @@ def test_topk_merge_equals_unsharded(device):
     torch.cuda.synchronize()
     assert np.array_equal(got.cpu().numpy()[0], np.concatenate((np.arange(1353), np.full(TOPK - 1353, -1))).astype(np.int32))
     assert np.array_equal(oracle.topk_merge(short_scores, short_index)[0], got.cpu().numpy()[0])
+    # the same short context over four shards (the cluster kernel's way out without a cut), the last shard empty
+    wide_index = np.full((1, 4 * TOPK), -1, np.int32)
+    wide_index[0, :3 * TOPK] = short_index[0]
+    wide_scores = rng.standard_normal((1, 4 * TOPK)).astype(np.float32)
+    got = ops.topk_merge(torch.from_numpy(wide_scores).to(device), torch.from_numpy(wide_index).to(device))
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy()[0], np.concatenate((np.arange(1353), np.full(TOPK - 1353, -1))).astype(np.int32))
 
 
 RESOLVER_CASES = [
