@@ -347,7 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_merge_cluster(const KvipMerg
     total_valid += local_hist[r];
     any_bad |= local_hist[8 + r];
   }
-  __syncthreads();   // local_hist is reused below
+  __syncthreads();   // local_hist is reused below: as the per-CTA histogram, all zero between passes
+  for (uint32_t i = tid; i < 4096u; i += kThreads) local_hist[i] = 0;
+  __syncthreads();
   int32_t* out = a.topk + static_cast<uint64_t>(row) * kTop;
   // A CTA that leaves here must not do so while another one may still be reading the hub's counts: one more cluster
   // barrier on the two early ways out (both are cluster-uniform decisions).
@@ -380,17 +382,18 @@ __global__ void __launch_bounds__(kThreads, 1) topk_merge_cluster(const KvipMerg
       const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
       const uint32_t bins = 1u << bits;
       const uint32_t buffer = (select_calls * 3u + pass) & 1u;   // the hub's histogram of this pass (cleared already)
-      for (uint32_t i = tid; i < bins; i += kThreads) local_hist[i] = 0;
-      __syncthreads();
 #pragma unroll
-      for (uint32_t j = 0; j < 2; ++j)
+      for (uint32_t j = 0; j < 2; ++j)   // local_hist is all zero here: cleared below as it is flushed
         hist_add_matched(local_hist, member[j] && (value[j] & prefix_mask) == prefix, (value[j] >> shift) & (bins - 1u));
       __syncthreads();
       for (uint32_t i = tid; i < bins; i += kThreads) {
         const uint32_t count = local_hist[i];
-        if (count) atomicAdd(&hub->hist[buffer][i], count);
+        if (count) {
+          atomicAdd(&hub->hist[buffer][i], count);
+          local_hist[i] = 0;
+        }
       }
-      cluster.sync();
+      cluster.sync();   // also the block barrier between clearing local_hist and the next pass's adds
       if (shard == 0) {
         uint32_t* hist = hub_here.hist[buffer];
         uint32_t* next = hub_here.hist[buffer ^ 1u];
@@ -416,13 +419,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_merge_cluster(const KvipMerg
         }
       }
       cluster.sync();
-      if (tid < 3) shared_word[tid] = hub->found[tid];
-      __syncthreads();
-      prefix |= shared_word[0] << shift;
+      // every thread reads the three words from the hub (warp-uniform addresses); the hub rewrites them only after
+      // the next cluster barrier
+      prefix |= hub->found[0] << shift;
       prefix_mask |= (bins - 1u) << shift;
-      remaining = shared_word[1];
-      *equal = shared_word[2];
-      __syncthreads();
+      remaining = hub->found[1];
+      *equal = hub->found[2];
     }
     ++select_calls;
     *take = remaining;
