@@ -999,6 +999,47 @@ def run_seqshard(args):
     dist.destroy_process_group()
 
 
+def run_merge(args):
+    """`--workload topk_merge`: the merge of shard candidates alone, one row, at 1 to 8 shards (random scores, every
+    list full): `--steps` launches captured in one graph, CUDA events around one replay."""
+    import torch
+
+    from kvip_b200 import ops
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    stream = torch.cuda.Stream(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+    per_shards = {}
+    lib = _load_counter()
+    before = lib.kvip_b200_launch_count()
+    with torch.cuda.stream(stream):
+        for shards in (1, 2, 3, 4, 8):
+            scores = torch.randn((1, shards * 2048), generator=g, device=device)
+            index = torch.arange(shards * 2048, dtype=torch.int32, device=device).view(1, -1).contiguous()
+            out = torch.empty((1, 2048), dtype=torch.int32, device=device)
+            for _ in range(max(args.warmup, 3)):
+                ops.topk_merge(scores, index, out)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(args.steps):
+                    ops.topk_merge(scores, index, out)
+            graph.replay()
+            stream.synchronize()
+            per_shards[shards] = time_region(torch, stream, graph.replay, 1) / args.steps * 1e6
+    launches = lib.kvip_b200_launch_count() - before
+    print(json.dumps({
+        "metric": "topk_merge kernel time at eight shards", "value": per_shards[8], "unit": "us", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_shards[8] / 1e3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 keys, int32 indices", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": 1, "candidates_per_shard": 2048,
+                   "kernels": "2, 4, 8 shards: one CTA per shard on a cluster; 1, 3 shards: one CTA"},
+        "us_by_shards": {str(k): v for k, v in per_shards.items()}, "gpu_launches": launches,
+    }), flush=True)
+
+
 LIDU_PUBLISHED_US = {1: 20.99, 4: 30.70, 8: 36.00, 12: 35.78}   # csrc/operators/lidu/DESIGN_V2_LOW.md:56-63 (V2, Ascend A5)
 
 
@@ -1152,7 +1193,7 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "miss_path_prefetch",
+    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["prefill_16k_128k", "seqshard_1m", "lidu", "topk_merge", "miss_path_prefetch",
                                                        "decode_128k_b32_zipf"], default="decode_128k_b64")
     parser.add_argument("--transport", choices=("peer", "nccl"), default="peer",
                         help="seqshard_1m: how the ranks exchange their TopK candidates")
@@ -1178,6 +1219,8 @@ def main():
         run_seqshard(args)
     elif args.workload == "lidu":
         run_lidu(args)
+    elif args.workload == "topk_merge":
+        run_merge(args)
     elif args.workload == "miss_path_prefetch":
         run_miss_prefetch(args)
     elif args.workload == "decode_128k_b32_zipf":
