@@ -347,12 +347,12 @@ def run_ours(args):
         "roofline": {"kernel": "li_score_tcgen05", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": li_bytes, "us_per_launch": stages["li_score"] * 1e6,
-                     # dram__bytes_read + dram__bytes_write of the ncu capture of decode_128k_b8 (8 x 128k FP8
-                     # pages, 1.014 x its algorithmic bytes), scaled by the pages one launch of this workload streams
-                     "traffic": (int(1.014 * li_bytes) if p.key_dtype == "fp8" and args.workload.startswith("decode_128k")
-                                 else None),
-                     "traffic_kind": "scaled, not measured on this workload: DRAM bytes of an ncu capture of the "
-                                     "8-request case of the same kernel, times the ratio of key pages per launch",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on THIS workload: a one-pass ncu
+                     # capture of three full-size launches (1108.8 MB read + 30.5-34.6 MB written each); other
+                     # workloads have no capture
+                     "traffic": 1140829269 if args.workload == "decode_128k_b64" and p.key_dtype == "fp8" else None,
+                     "traffic_kind": "measured on this workload: dram__bytes_read.sum + dram__bytes_write.sum per launch, "
+                                     "mean of three launches of a one-pass ncu capture (0.9995 x the algorithmic bytes)",
                      "step_frac": step_bytes / stages["step_graph"] / 1e9 / hbm_peak},
         "stages_us": {k: v * 1e6 for k, v in stages.items()},
         "fetch": {"cold_step_reads": cold_reads, "cold_step_ms": cold_s * 1e3,
