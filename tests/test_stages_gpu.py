@@ -734,3 +734,32 @@ def test_ingest_decode(bf16_source, device):
                          queries, history, source_is_bf16=bf16_source)
     assert np.array_equal(keys_t.cpu().numpy(), keys)
     assert np.array_equal(scales_t.cpu().numpy().view(np.uint32), scales.view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_maximum_history_scores_and_topk(device):
+    """The largest history the shape check admits (2^21 keys in one request, random block table): tensor-core scores
+    against the CUDA-core cross-check kernel, then the TopK of those scores against the C oracle, bit for bit."""
+    history, heads, short = 1 << 21, 64, 77
+    g = torch.Generator(device=device)
+    g.manual_seed(3)
+    keys = (torch.randn((history, 128), generator=g, device=device) * 8).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    key_scale = torch.exp(torch.rand((history,), generator=g, device=device) * 4.6052 - 6.9078)
+    query = (torch.randn((1, heads, 128), generator=g, device=device) * 8).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    query_scale = torch.exp(torch.rand((1, heads), generator=g, device=device) * 4.6052 - 6.9078)
+    weights = (torch.randn((1, heads), generator=g, device=device) / 8).to(torch.bfloat16)
+    lengths = torch.full((1,), history - short, dtype=torch.int32, device=device)
+    ends = torch.full((1, 1), history - short, dtype=torch.int32, device=device)
+    table = torch.randperm(history // 128, generator=g, device=device).to(torch.int32).view(1, -1).contiguous()
+    scores, status = ops.li_score(query, keys, weights, query_scale, key_scale, lengths, ends, table)
+    check, _ = ops.li_score(query, keys, weights, query_scale, key_scale, lengths, ends, table, simt=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got, want = scores[0, :history - short].cpu().numpy(), check[0, :history - short].cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
+    top = ops.topk(scores, lengths, ends)
+    torch.cuda.synchronize()
+    host_scores = scores.cpu().numpy()
+    expected = oracle_c.topk(host_scores, lengths.cpu().numpy(), ends.cpu().numpy().reshape(-1))
+    assert np.array_equal(top.cpu().numpy(), expected)
+    assert top.max().item() < history - short   # nothing beyond the valid length
