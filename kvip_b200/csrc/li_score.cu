@@ -201,10 +201,14 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
 
 struct TileCursor {  // walks the flat (request, page) list shared by the three roles
   const uint32_t* prefix;
-  uint32_t batch, request;
-  __device__ TileCursor(const uint32_t* p, uint32_t b) : prefix(p), batch(b), request(0) {}
+  uint32_t batch, request, limit;   // limit: first tile of the next request (kept in a register: the common call
+                                    // is one compare, not a shared-memory round trip)
+  __device__ TileCursor(const uint32_t* p, uint32_t b) : prefix(p), batch(b), request(0), limit(b > 1u ? p[1] : 0xffffffffu) {}
   __device__ uint32_t seek(uint32_t tile) {
-    while (request + 1 < batch && tile >= prefix[request + 1]) ++request;
+    while (tile >= limit) {
+      ++request;
+      limit = request + 1 < batch ? prefix[request + 1] : 0xffffffffu;
+    }
     return request;
   }
 };
@@ -255,6 +259,9 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
   // one unit per tile up to 128 (query, head) columns, two beyond (queries 0-1 and 2-3 at 64 heads). Four units
   // fit tensor memory at 128 columns each, so MMA and reduction overlap even for the widest query tile.
   const uint32_t halves = Q * H > 128u ? 2u : 1u;
+  const uint32_t halves_shift = halves - 1u;   // halves is 1 or 2: unit -> tile is a shift, not a division (a 32-bit
+                                               // division by a run-time value costs about a hundred cycles, and the
+                                               // epilogue did four per unit)
   const uint32_t unit_queries = halves == 2u ? 128u / H : Q;    // query slots per unit
   const uint32_t acc_stride = Q * H <= 32u ? 32u : (Q * H <= 64u ? 64u : 128u);
   const uint32_t acc_count = min(kMaxAcc, 512u / acc_stride);   // 4 or 8
@@ -462,17 +469,17 @@ li_score_tcgen05(const __grid_constant__ CUtensorMap key_map, const __grid_const
       if (t >= tile_end || !a.key_scale) return 1.0f;
       return a.key_scale[static_cast<uint64_t>(page) * kBlockTokens + row];
     };
-    // Group g reduces the units u = g (mod groups); unit u is half (u % halves) of tile u / halves.
+    // Group g reduces the units u = g (mod groups); unit u is half (u mod halves) of tile u / halves.
     const uint32_t G = groups;
     const uint32_t tiles_here = tile_end - tile_begin, units_here = tiles_here * halves;
-    auto tile_of = [&](uint32_t u) { return u < units_here ? tile_begin + u / halves : tile_end; };
+    auto tile_of = [&](uint32_t u) { return u < units_here ? tile_begin + (u >> halves_shift) : tile_end; };
     const uint32_t first = group;
     int32_t page_next = page_of(tile_of(first));
     float kscale = scale_of(tile_of(first), page_next);
     page_next = page_of(tile_of(first + G));
     uint32_t acc = group % acc_count, acc_phase = 0;   // G divides acc_count: a group meets the same accumulators
     for (uint32_t u = first; u < units_here; u += G) {
-      const uint32_t t = tile_begin + u / halves, h = u % halves;
+      const uint32_t t = tile_begin + (u >> halves_shift), h = u & (halves - 1u);
       const uint32_t b = cur.seek(t);
       const uint32_t nq = active_q[b];
       const float kscale_next = scale_of(tile_of(u + G), page_next);   // consumed next iteration
