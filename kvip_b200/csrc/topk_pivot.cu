@@ -236,14 +236,17 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
   __syncthreads();
 
   // ---- 3. exact 2048th key among the kept ---------------------------------------------------------------
+  // Three radix passes (12 + 12 + 8 bits) over the list. The histogram is cleared once; in every pass the thread
+  // that scans a group of bins takes them into registers and clears them for the next pass, so a pass costs four
+  // block barriers: after the adds, two inside the scan, and before the digit is read.
   uint32_t prefix = 0, prefix_mask = 0, remaining = kTop;
+  for (uint32_t i = tid; i < 4096u; i += kThreads) hist[i] = 0;
+  __syncthreads();
 #pragma unroll 1
   for (uint32_t pass = 0; pass < 3; ++pass) {
     const uint32_t bits = pass == 2 ? 8u : 12u;
     const uint32_t shift = pass == 0 ? 20u : (pass == 1 ? 8u : 0u);
     const uint32_t bins = 1u << bits;
-    for (uint32_t i = tid; i < bins; i += kThreads) hist[i] = 0;
-    __syncthreads();
     for (uint32_t r = 0; r * kThreads < kept; ++r) {  // block-uniform trip count: hist_add votes per warp
       const uint32_t i = r * kThreads + tid;
       const uint32_t key = i < kept ? list_key[i] : 0u;
@@ -253,25 +256,32 @@ __global__ void __launch_bounds__(kThreads, 1) topk_pivot(const KvipTopkArgs a) 
     const uint32_t per = bins / kThreads ? bins / kThreads : 1u;  // 4, 4, then 1 (256 bins)
     const uint32_t groups = bins / per;
     const uint32_t group = groups - 1u - tid;  // valid when tid < groups
-    uint32_t local = 0;
-    if (tid < groups)
-      for (uint32_t j = 0; j < per; ++j) local += hist[group * per + j];
+    uint32_t count[4] = {0u, 0u, 0u, 0u}, local = 0;
+    if (tid < groups) {
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j)
+        if (j < per) {
+          count[j] = hist[group * per + j];
+          hist[group * per + j] = 0;   // nobody adds to it before the barrier that ends this pass
+          local += count[j];
+        }
+    }
     uint32_t above = block_exclusive_scan(local, scan_scratch, nullptr);
     if (tid < groups) {
-      for (int32_t j = static_cast<int32_t>(per) - 1; j >= 0; --j) {
-        const uint32_t count = hist[group * per + static_cast<uint32_t>(j)];
-        if (above < remaining && above + count >= remaining) {
-          found[0] = group * per + static_cast<uint32_t>(j);
-          found[1] = remaining - above;
+#pragma unroll
+      for (int32_t j = 3; j >= 0; --j)
+        if (static_cast<uint32_t>(j) < per) {
+          if (above < remaining && above + count[j] >= remaining) {
+            found[0] = group * per + static_cast<uint32_t>(j);
+            found[1] = remaining - above;
+          }
+          above += count[j];
         }
-        above += count;
-      }
     }
     __syncthreads();
-    prefix |= found[0] << shift;
+    prefix |= found[0] << shift;   // rewritten only after the next pass's barriers
     prefix_mask |= (bins - 1u) << shift;
     remaining = found[1];
-    __syncthreads();
   }
   const uint32_t kth = prefix;         // exact key of the 2048th largest element
   const uint32_t need_eq = remaining;  // how many == kth positions are taken
