@@ -332,7 +332,11 @@ uint32_t launch_topk_pivot(const KvipTopkArgs& a, cudaStream_t stream) {
   // two, four or eight CTAs per row while the clusters still fit the GPU in one wave (a cluster of eight
   // 1024-thread CTAs needs eight free SMs of one GPC: about two of them fit per GPC)
   const unsigned sms = device_sm_count();
-  const unsigned ranks = 8u * a.rows <= (sms * 3u) / 4u ? 8u : (4u * a.rows <= (sms * 7u) / 8u ? 4u : (2u * a.rows <= sms ? 2u : 1u));
+  // (a cluster of eight pays for itself only on long rows: its barriers and the hand-over of eight lists cost more
+  // than the shorter filter saves below about 256k scores - one row of 131072: 20.3 us on four CTAs, 22.6 on eight)
+  const unsigned most = a.scoreStride >= 262144u ? 8u : 4u;
+  const unsigned fit = 8u * a.rows <= (sms * 3u) / 4u ? 8u : (4u * a.rows <= (sms * 7u) / 8u ? 4u : (2u * a.rows <= sms ? 2u : 1u));
+  const unsigned ranks = fit < most ? fit : most;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(a.rows * ranks, 1, 1);
   config.blockDim = dim3(kThreads, 1, 1);
