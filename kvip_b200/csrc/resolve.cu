@@ -74,7 +74,6 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
 
   // ---- round init (v9_init_kernel, lifecycle.cpp:32-81): per-request scratch ----------
   for (uint32_t i = tid; i < words; i += kThreads) bitmap[i] = 0;
-  for (uint32_t i = tid; i < kBuckets; i += kThreads) { keys[i] = kEmpty; ranks[i] = kEmpty; }
   for (uint32_t i = tid; i < kChangeCapacity; i += kThreads) {
     changes[i] = -1;
     change_slots[i] = i < kLruSlots ? lru[i] : -1;
@@ -133,12 +132,26 @@ __global__ void __launch_bounds__(kThreads) resolve_requests(const KvipResolveAr
       if (bits) atomicOr(a.miss_mask + (static_cast<uint64_t>(b) * Q + q) * (kTop / 32u) + (tid >> 4), bits << ((tid & 15u) * 2u));
     }
   }
+  // A request whose every selected position is resident (the steady state of a decode loop) needs neither the hash
+  // table nor the per-query rounds below: nothing is unresolved. The vote is also the barrier after the classification.
+  bool unresolved = false;
+#pragma unroll
+  for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q)
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j)
+      unresolved |= q < Q && token[q][j] >= 0 && where[q][j] == kMissing;
+  const bool any_unresolved = __syncthreads_or(unresolved ? 1 : 0) != 0;   // positions beyond the history set ctl[1]
+  if (any_unresolved) {
+    for (uint32_t i = tid; i < kBuckets; i += kThreads) { keys[i] = kEmpty; ranks[i] = kEmpty; }
+  } else if (tid < Q && !ctl[1]) {
+    a.query_counts[b * 8u + tid] = 0;
+  }
   __syncthreads();
 
   // ---- 2. queries in order ---------------------------------------------------------------
 #pragma unroll
   for (uint32_t q = 0; q < KVIP_MAX_QUERIES; ++q) {
-    if (q >= Q || ctl[1]) break;   // block-uniform
+    if (q >= Q || ctl[1] || !any_unresolved) break;   // block-uniform
     const uint32_t begin = q * kTop, old_count = ctl[0];
     // 2a. hash insert, first occurrence by atomicMin on the position
 #pragma unroll
