@@ -622,7 +622,7 @@ uint32_t kvip_b200_host_register(void* host, uint64_t bytes, uint64_t* device_al
 uint32_t kvip_b200_host_unregister(void* host);
 uint32_t kvip_streaming_resolver_cores(void);            /* == 3, streaming.py:41-47 */
 uint32_t kvip_streaming_flag_count(void);                /* == 16 */
-uint32_t kvip_b200_abi_version(void);
+uint32_t kvip_b200_abi_version(void);                    /* == 3: bumped whenever an argument record of this header changes */
 uint32_t kvip_b200_context_bytes(void);
 uint32_t kvip_b200_workspace_bytes(void);
 uint32_t kvip_b200_launch_count(void);                   /* kernels enqueued so far by this library */

@@ -131,7 +131,7 @@ extern "C" uint32_t kvip_streaming_resolver_cores(void) { return 3; }
 extern "C" uint32_t kvip_streaming_flag_count(void) { return 16; }
 // 2: option bits of this build moved off the reference's flag bits; KvipLiArgs, KvipResolveArgs, KvipFetchArgs and
 //    KvipContext grew (wait limit and head-sum mode, source range check and final posts, update status, final posts)
-extern "C" uint32_t kvip_b200_abi_version(void) { return 2; }
+extern "C" uint32_t kvip_b200_abi_version(void) { return 3; }
 extern "C" uint32_t kvip_b200_context_bytes(void) { return sizeof(KvipContext); }
 extern "C" uint32_t kvip_b200_workspace_bytes(void) { return sizeof(KvipWorkspace); }
 extern "C" uint32_t kvip_b200_launch_count(void) { return kvip::g_launches.load(); }

@@ -217,7 +217,7 @@ def test_stage_times_and_option_bits(device):
                   weight_dtype="bf16", token_bytes=1152, seed=9, host_pool=False, fill_payload=True)
     plain, timed = DecodePipeline(device, **config), DecodePipeline(device, **config)
     library = _lib.load_library()
-    assert library.kvip_b200_abi_version() == 2
+    assert library.kvip_b200_abi_version() == 3
     timed.forward.set_options(diagnostics=True)
     timed.forward._options |= _lib.OPTION_SCHEDULING_HINTS      # parallel finalize + prepare metadata + UBmem overlap
     timed.forward._options_word[0] = timed.forward._options

@@ -84,7 +84,7 @@ def test_option_bits_do_not_collide_with_the_reference(library):
     added = (_lib.OPTION_SELECT_ONLY, _lib.OPTION_COMMIT_ONLY, _lib.OPTION_SCORES_READY)
     assert all(bit & reference_bits == 0 for bit in added) and len({*added}) == 3
     assert _lib.OPTION_SCHEDULING_HINTS == 0x10000000 | 0x08000000 | 0x04000000
-    assert library.kvip_b200_abi_version() == 2
+    assert library.kvip_b200_abi_version() == 3
     shape = _lib.RuntimeShape.prepare(library, batch=2, history=8192, resident=4096, indexHeads=64, queries=1, tokenBytes=1152)
     context = _lib.Context(shape=shape)
     workspace = _lib.Workspace(history=8192, resident=4096, max_events=10240, options=_lib.OPTION_LEGACY_LAYOUT | (2 << 16))
